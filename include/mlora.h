@@ -1,0 +1,163 @@
+/* libmlora: C ABI of the B200 (sm_100a) multi-LoRA decode path.
+ *
+ * Every pointer named `d_*` or documented as "device" is a CUDA device pointer
+ * owned by the caller; nothing is allocated or freed by the library.  Every
+ * call is asynchronous on `stream` (a cudaStream_t passed as void*), returns
+ * 0 on success and a negative MLORA_E* code when the arguments are rejected
+ * on the host (mlora_last_error() then holds a message).  bf16 tensors are
+ * row-major with 16-byte aligned rows.  The library keeps no global state.
+ *
+ * The citations name the interface of the reference project
+ * (llm-db/tensor-program-optimization-with-auto-batching) that each entry
+ * point stands in for, by path inside that project.
+ */
+#ifndef MLORA_H_
+#define MLORA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MLORA_OK 0
+#define MLORA_EINVAL (-1) /* argument rejected on the host */
+#define MLORA_ECUDA (-2)  /* a CUDA runtime call or launch failed */
+#define MLORA_ESIZE (-3)  /* workspace too small / size beyond a stated limit */
+
+/* flags of mlora_linear */
+#define MLORA_OUT_F32 1     /* y is float32 (lm_head logits) instead of bf16 */
+#define MLORA_SILU_MUL 2    /* W holds gate/up rows interleaved in blocks of 8 (rows 16j..16j+7 = gate
+                               rows 8j.., rows 16j+8..16j+15 = up rows 8j..); y[t, c] = silu(g)*u, y has
+                               out/2 columns */
+#define MLORA_FORCE_SIMT 4  /* use the CUDA-core warp-per-row kernel whatever the shape */
+
+int mlora_version(void);
+const char* mlora_last_error(void);
+/* Number of kernels this library has launched in this process (for benchmarks' launch counts). */
+uint64_t mlora_launch_count(void);
+
+/* ---- (d) request -> adapter bucketing --------------------------------------------------------
+ * Stable counting sort of n rows by key (has_adapter, tid, wid), rows without adapter
+ * (tid < 0) first.  Replaces LlamaSeqInfo.order_seqs and the per-type position / weight-id
+ * lists of LlamaSeqInfo.get_decode_method (tvm/llama_auto_batcher/llama_seq_info.py:61-75,
+ * 77-104), which the reference recomputes on the host for every token step
+ * (tvm/llama_auto_batcher/llama_exec_graph.py:106,114), and the np.sort of adapter ids in
+ * huggingface/generation/gen_lora.py:78.
+ *   d_tids  [n] int32 or NULL (NULL = every row with wid >= 0 is type 0, wid < 0 = no adapter)
+ *   d_wids  [n] int32, 0 <= wid < n_wids for rows that have an adapter
+ *   by_type_only != 0: key is (has_adapter, tid) only (get_decode_method's grouping: positions
+ *                      stay ascending inside a type)
+ * outputs (device):
+ *   d_perm        [n]   perm[i] = index in the input of the row that lands at sorted position i
+ *   d_sorted_tid  [n], d_sorted_wid [n]   tid / wid of the row at sorted position i (NULL to skip)
+ *   d_seg_offsets [n_keys+1], d_seg_tid [n_keys], d_seg_wid [n_keys]: compacted runs of equal key
+ *                 (only the first *n_seg entries are written, plus seg_offsets[n_seg] = n)
+ *   d_counts      [n_types+2]: counts[0] = n_seg, counts[1] = rows without adapter,
+ *                 counts[2+t] = rows of type t
+ * n_keys = 1 + n_types * n_wids (or n_types+1 when by_type_only), at most 8192.  d_work needs
+ * mlora_bucket_sort_workspace(n, n_types, n_wids) bytes (0 when n <= 1024). */
+size_t mlora_bucket_sort_workspace(int32_t n, int32_t n_types, int32_t n_wids);
+int mlora_bucket_sort(const int32_t* d_tids, const int32_t* d_wids, int32_t n, int32_t n_types,
+                      int32_t n_wids, int32_t by_type_only, int32_t* d_perm, int32_t* d_sorted_tid,
+                      int32_t* d_sorted_wid, int32_t* d_seg_offsets, int32_t* d_seg_tid,
+                      int32_t* d_seg_wid, int32_t* d_counts, void* d_work, size_t work_bytes,
+                      void* stream);
+
+/* ---- (a) LoRA shrink: u[t, m*r_max + j] = sum_k x[t,k] * A_all[slot[t], m*r_max + j, k] --------
+ * First half of the "take_matmul" pair (tvm/custom/fuse_take_matmul.py:78-111; Lora.forward
+ * synthesised at tvm/llama_auto_batcher/compile_tvm.py:106-112) and of the two bmm's of
+ * GatherBMMLinear.forward (huggingface/custom_peft/lora_gatherbmm_linear_layer.py:16-19).
+ *   d_x [T, in] bf16 (row stride ldx elements); d_A_all [N, n_mod*r_max, in] bf16;
+ *   d_ranks [N] int32 (rank of each adapter slot, <= r_max; rows >= rank are never read);
+ *   d_slots [T] int32 (adapter slot of each row, < 0 = none -> u row is zero);
+ *   d_u [T, n_mod*r_max] float32.  n_mod modules share the input (q,k,v or gate,up). */
+int mlora_lora_shrink(const void* d_x, int64_t ldx, const void* d_A_all, const int32_t* d_ranks,
+                      const int32_t* d_slots, int32_t T, int32_t in, int32_t r_max, int32_t n_mod,
+                      float* d_u, void* stream);
+
+/* ---- (a)+(b) base projection with the LoRA expand fused into the output write ----------------
+ *   y[t, o] = sum_k x[t,k] W[o,k]  +  scale[s] * sum_j u[t, m(o)*r_max + j] * B_all[s, o, j]
+ * with s = slot[t] (skipped when s < 0 or d_u == NULL) and m(o) the module that owns output row o
+ * (mod_offsets[m] <= o < mod_offsets[m+1]; with MLORA_SILU_MUL: m = (o >> 3) & 1).
+ * Stands in for base_layer(x) + bmm(bmm(x, A), B*scaling)
+ * (huggingface/custom_peft/lora_gatherbmm_linear_layer.py:15-20) and for nn.Linear followed by
+ * "q += q_ft_proj(h, wids)" (tvm/llama_auto_batcher/compile_tvm.py:126-134, 142-155; the
+ * write_tensor_part scatter of tvm/custom/write_tensor_part.py is subsumed because rows are
+ * addressed directly).
+ *   d_x [T,in] bf16; d_W [out,in] bf16; d_y [T, out or out/2] bf16 (or f32 with MLORA_OUT_F32),
+ *   row stride ldy elements; d_B_all [N, out, r_max] bf16; d_scales [N] float32;
+ *   h_mod_offsets: HOST array of n_mod+1 ints (NULL when n_mod == 1), n_mod <= 8.
+ *   d_work / work_bytes: scratch for split-K partial sums of the tensor-core kernel,
+ *   mlora_linear_workspace(T, in, out) bytes (may be NULL/0: then the CUDA-core kernel runs). */
+size_t mlora_linear_workspace(int32_t T, int32_t in, int32_t out);
+int mlora_linear(const void* d_x, int64_t ldx, const void* d_W, void* d_y, int64_t ldy, int32_t T,
+                 int32_t in, int32_t out, const float* d_u, const void* d_B_all,
+                 const int32_t* d_ranks, const float* d_scales, const int32_t* d_slots,
+                 int32_t r_max, int32_t n_mod, const int32_t* h_mod_offsets, int32_t flags,
+                 void* d_work, size_t work_bytes, void* stream);
+
+/* ---- (b) fused residual add + RMSNorm ----------------------------------------------------------
+ *   res[t,:] += delta[t,:] (skipped when d_delta == NULL);  out[t,:] = res * rsqrt(mean(res^2)+eps) * w
+ * nn.RMSNorm + the "hidden_states += ..." of LlamaDecoderLayer.forward
+ * (tvm/llama_auto_batcher/llama_for_causal_lm.py:76-84,93).
+ *   d_delta [T,H] bf16 or NULL; d_res [T,H] float32 in/out; d_w [H] bf16; d_out [T,H] bf16. */
+int mlora_residual_rmsnorm(const void* d_delta, float* d_res, const void* d_w, float eps,
+                           void* d_out, int32_t T, int32_t H, void* stream);
+
+/* ---- embedding gather: res[t,:] = float(E[ids[t], :]) ------------------------------------------
+ * vm["embed"](input_ids, params) (tvm/llama_auto_batcher/llama_for_causal_lm.py:121-122).
+ * Optionally also writes the gathered rows as bf16 to d_out_bf16 (the reference's return value). */
+int mlora_embed(const int32_t* d_ids, const void* d_E, int32_t T, int32_t H, int32_t vocab,
+                float* d_res, void* d_out_bf16, void* stream);
+
+/* ---- greedy token: tok[t] = first index of the row maximum -------------------------------------
+ * Replaces logits.numpy() + np.argmax per row (tvm/llama_auto_batcher/llama_exec_graph.py:92,134-137). */
+int mlora_argmax(const float* d_logits, int64_t ld, int32_t T, int32_t V, int32_t* d_tok,
+                 void* stream);
+
+/* ---- (c) paged KV cache -------------------------------------------------------------------------
+ * Cache layout per layer: K pages [n_pages, Hkv, page_size, D] bf16 and V pages of the same shape.
+ * Block table [n_slots, max_pages] int32 (page ids of a sequence in order); d_seq_lens [n_slots]
+ * int32 = tokens already stored.  Rows of a step carry d_row_slot[t] (cache slot of the row's
+ * sequence) and d_row_pos[t] (position of the row's token in its sequence).
+ * Together these stand in for paged_kv_cache.attention_with_fused_qkv(layer, qkv, n_q)
+ * (tvm/llama_auto_batcher/llama_for_causal_lm.py:55-64) on a cache made by create_paged_kv_cache
+ * (:148-174: rope INLINE, scale 1, rotary_dim = head_dim, no sliding window).
+ *
+ * mlora_kv_append_rope: rotates q and k of every row (rotate-half pairing), writes q back in
+ * place into d_qkv and stores rotated k and v into the pages (prefill path).
+ *   d_qkv [T, (Hq+2*Hkv)*D] bf16, row stride ld elements. */
+int mlora_kv_append_rope(void* d_qkv, int64_t ld, void* d_k_pages, void* d_v_pages,
+                         const int32_t* d_block_table, int32_t max_pages, const int32_t* d_row_slot,
+                         const int32_t* d_row_pos, int32_t T, int32_t Hq, int32_t Hkv, int32_t D,
+                         int32_t page_size, float rope_theta, void* stream);
+
+/* mlora_paged_attention: out[t, h*D..] = softmax(q_t k^T / sqrt(D)) v over tokens 0..pos_t of the
+ * row's sequence, gathered through the block table.
+ *   fused_append != 0 (decode, one row per sequence): q and the row's new k are rotated here, the
+ *     new k/v are stored into the pages at position pos_t, and d_qkv is left untouched.
+ *   fused_append == 0: d_qkv already holds rotated q and the pages already hold tokens 0..pos_t
+ *     (after mlora_kv_append_rope).
+ *   n_splits > 1 splits every row's context over n_splits CTAs; needs d_work of
+ *   mlora_paged_attention_workspace(T, Hq, D, n_splits) bytes.  n_splits <= 0 lets the library pick. */
+size_t mlora_paged_attention_workspace(int32_t T, int32_t Hq, int32_t D, int32_t n_splits);
+int mlora_paged_attention(const void* d_qkv, int64_t ld, void* d_k_pages, void* d_v_pages,
+                          const int32_t* d_block_table, int32_t max_pages,
+                          const int32_t* d_row_slot, const int32_t* d_row_pos, int32_t T, int32_t Hq,
+                          int32_t Hkv, int32_t D, int32_t page_size, float rope_theta,
+                          int32_t fused_append, void* d_out, int64_t ld_out, int32_t n_splits,
+                          void* d_work, size_t work_bytes, void* stream);
+
+/* ---- decode-step bookkeeping on the device (keeps a whole step inside one CUDA graph) ----------
+ * For each live row b: slot = d_row_slot[b]; d_row_pos[b] = d_seq_lens[slot]; d_seq_lens[slot] += 1.
+ * What kv_state_begin_forward(kv, seq_ids, [1]*B) does on the host in the reference
+ * (tvm/llama_auto_batcher/llama_exec_graph.py:121-125).  Pages must already be reserved. */
+int mlora_kv_begin_decode(const int32_t* d_row_slot, int32_t* d_seq_lens, int32_t* d_row_pos,
+                          int32_t B, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MLORA_H_ */

@@ -1,0 +1,384 @@
+// Paged-KV attention for single-query rows (decode, and prefill rows after their K/V were
+// appended), RoPE + KV append, and the split-KV merge.
+//
+// Cache layout per layer: K pages [n_pages, Hkv, page_size, D] bf16, V pages alike, so one
+// (page, head) holds page_size*D contiguous elements (4 KB at page 16, D 128).  A warp streams a
+// page with 128-bit loads: D/8 lanes cover one token, 32/(D/8) tokens per load instruction; all K
+// and V loads of a page are issued before the first use.  Scores are reduced inside each lane
+// group with xor-shuffles; every lane group keeps its own online-softmax state (m, l, acc[8]);
+// groups, warps and splits are merged at the end.
+#include <cmath>
+
+#include "common.cuh"
+
+namespace mlora {
+namespace {
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct AttnArgs {
+  const bf16* qkv;
+  int64_t ld;
+  bf16* k_pages;
+  bf16* v_pages;
+  const int32_t* block_table;
+  int max_pages;
+  const int32_t* row_slot;
+  const int32_t* row_pos;
+  int T, Hq, Hkv, page_size;
+  float theta;
+  int fused;
+  bf16* out;
+  int64_t ld_out;
+  int n_splits;
+  float* work;
+};
+
+__device__ __forceinline__ uint4 ld_kv(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ float rope_inv_freq(float theta, int i, int D) {
+  // theta^(-2i/D), evaluated in fp32 like the reference frameworks do
+  return powf(theta, -(float)(2 * i) / (float)D);
+}
+
+__device__ __forceinline__ void merge_state(float& m, float& l, float (&acc)[8], float mo, float lo,
+                                            const float (&acco)[8]) {
+  const float mn = fmaxf(m, mo);
+  const float c1 = (m == -INFINITY) ? 0.f : exp2f(m - mn);
+  const float c2 = (mo == -INFINITY) ? 0.f : exp2f(mo - mn);
+  l = l * c1 + lo * c2;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = acc[e] * c1 + acco[e] * c2;
+  m = mn;
+}
+
+// grid (Hq, T, n_splits), 128 threads.  IT = page_size / tokens-per-load.
+template <int D, int IT>
+__global__ void __launch_bounds__(128) paged_attn_kernel(AttnArgs a) {
+  constexpr int LPT = D / 8;    // lanes per token
+  constexpr int TPW = 32 / LPT; // tokens per warp-wide load
+  constexpr int PS = IT * TPW;  // page size
+  __shared__ float sq[D];       // rotated, scaled query
+  __shared__ float sk[D];       // rotated new key (bf16-rounded)
+  __shared__ float sv[D];       // new value
+  __shared__ float wm[4], wl[4];
+  __shared__ float wacc[4][D];
+  __shared__ float s_new;
+
+  const int h = blockIdx.x, t = blockIdx.y, split = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int rep = a.Hq / a.Hkv, kvh = h / rep;
+  const int slot = a.row_slot[t], pos = a.row_pos[t];
+  const int32_t* bt = a.block_table + (size_t)slot * a.max_pages;
+  const bf16* row = a.qkv + (size_t)t * a.ld;
+  const float qscale = rsqrtf((float)D) * kLog2e;
+  const bool last_split = split == a.n_splits - 1;
+  const bool has_new = a.fused && last_split;
+
+  // ---- prologue: rotate q (and the new k), stage the new k/v -----------------------------------
+  if (tid < D / 2) {
+    const int i = tid;
+    float q1 = __bfloat162float(row[h * D + i]), q2 = __bfloat162float(row[h * D + i + D / 2]);
+    if (a.fused) {
+      float sn, cs;
+      sincosf((float)pos * rope_inv_freq(a.theta, i, D), &sn, &cs);
+      const float r1 = q1 * cs - q2 * sn, r2 = q2 * cs + q1 * sn;
+      q1 = r1, q2 = r2;
+    }
+    sq[i] = q1 * qscale;
+    sq[i + D / 2] = q2 * qscale;
+  } else if (tid < D && has_new) {
+    const int i = tid - D / 2;
+    const bf16* kr = row + (size_t)(a.Hq + kvh) * D;
+    const float k1 = __bfloat162float(kr[i]), k2 = __bfloat162float(kr[i + D / 2]);
+    float sn, cs;
+    sincosf((float)pos * rope_inv_freq(a.theta, i, D), &sn, &cs);
+    const bf16 r1 = __float2bfloat16_rn(k1 * cs - k2 * sn), r2 = __float2bfloat16_rn(k2 * cs + k1 * sn);
+    sk[i] = __bfloat162float(r1);
+    sk[i + D / 2] = __bfloat162float(r2);
+    if (h % rep == 0) {
+      const int page = bt[pos / PS];
+      bf16* dst = a.k_pages + (((size_t)page * a.Hkv + kvh) * PS + pos % PS) * D;
+      dst[i] = r1;
+      dst[i + D / 2] = r2;
+    }
+  }
+  if (has_new && tid < D) {
+    const bf16 v = row[(size_t)(a.Hq + a.Hkv + kvh) * D + tid];
+    sv[tid] = __bfloat162float(v);
+    if (h % rep == 0) {
+      const int page = bt[pos / PS];
+      a.v_pages[(((size_t)page * a.Hkv + kvh) * PS + pos % PS) * D + tid] = v;
+    }
+  }
+  __syncthreads();
+
+  const int g = lane / LPT, dl = lane % LPT;
+  float qf[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) qf[e] = sq[dl * 8 + e];
+
+  // tokens read from the pages: [0, n_tok)
+  const int n_tok = a.fused ? pos : pos + 1;
+  const int n_pg = (n_tok + PS - 1) / PS;
+  const int per = (n_pg + a.n_splits - 1) / a.n_splits;
+  const int pg_begin = min(split * per, n_pg), pg_end = min(pg_begin + per, n_pg);
+
+  float m = -INFINITY, l = 0.f, acc[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+
+  for (int pg = pg_begin + warp; pg < pg_end; pg += 4) {
+    const int page = bt[pg];
+    const size_t base = ((size_t)page * a.Hkv + kvh) * PS * D + (size_t)g * D + dl * 8;
+    const bf16* kp = a.k_pages + base;
+    const bf16* vp = a.v_pages + base;
+    uint4 kr[IT], vr[IT];
+#pragma unroll
+    for (int it = 0; it < IT; ++it) kr[it] = ld_kv(kp + (size_t)it * TPW * D);
+#pragma unroll
+    for (int it = 0; it < IT; ++it) vr[it] = ld_kv(vp + (size_t)it * TPW * D);
+    float s[IT];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int it = 0; it < IT; ++it) {
+      float kf[8];
+      unpack8(kr[it], kf);
+      float d = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) d = fmaf(qf[e], kf[e], d);
+#pragma unroll
+      for (int o = LPT / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+      const bool valid = pg * PS + it * TPW + g < n_tok;
+      s[it] = valid ? d : -INFINITY;
+      mx = fmaxf(mx, s[it]);
+    }
+    const float mn = fmaxf(m, mx);
+    if (mn != -INFINITY) {
+      const float corr = (m == -INFINITY) ? 0.f : exp2f(m - mn);
+      l *= corr;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] *= corr;
+#pragma unroll
+      for (int it = 0; it < IT; ++it) {
+        if (s[it] != -INFINITY) {
+          const float p = exp2f(s[it] - mn);
+          float vf[8];
+          unpack8(vr[it], vf);
+          l += p;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[e] = fmaf(p, vf[e], acc[e]);
+        }
+      }
+      m = mn;
+    }
+  }
+
+  // ---- merge the lane groups of the warp -------------------------------------------------------
+#pragma unroll
+  for (int o = LPT; o < 32; o <<= 1) {
+    const float mo = __shfl_xor_sync(0xffffffffu, m, o);
+    const float lo = __shfl_xor_sync(0xffffffffu, l, o);
+    float ao[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ao[e] = __shfl_xor_sync(0xffffffffu, acc[e], o);
+    merge_state(m, l, acc, mo, lo, ao);
+  }
+  if (lane < LPT) {
+    if (lane == 0) {
+      wm[warp] = m;
+      wl[warp] = l;
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) wacc[warp][lane * 8 + e] = acc[e];
+  }
+  if (warp == 0 && has_new) {
+    float d = 0.f;
+    for (int i = lane; i < D; i += 32) d = fmaf(sq[i], sk[i], d);
+    d = warp_sum(d);
+    if (lane == 0) s_new = d;
+  }
+  __syncthreads();
+
+  // ---- merge warps (+ the new token) and write -------------------------------------------------
+  if (tid < D) {
+    float M = has_new ? s_new : -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, wm[w]);
+    float L = 0.f, O = 0.f;
+    if (M != -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float c = (wm[w] == -INFINITY) ? 0.f : exp2f(wm[w] - M);
+        L = fmaf(wl[w], c, L);
+        O = fmaf(wacc[w][tid], c, O);
+      }
+      if (has_new) {
+        const float c = exp2f(s_new - M);
+        L += c;
+        O = fmaf(sv[tid], c, O);
+      }
+    }
+    if (a.n_splits == 1) {
+      a.out[(size_t)t * a.ld_out + h * D + tid] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+    } else {
+      float* w = a.work + (((size_t)t * a.Hq + h) * a.n_splits + split) * (D + 2);
+      w[tid] = O;
+      if (tid == 0) {
+        w[D] = M;
+        w[D + 1] = L;
+      }
+    }
+  }
+}
+
+// grid (Hq, T), D threads: combine the n_splits partial results of one (row, head).
+__global__ void attn_merge_kernel(const float* __restrict__ work, int Hq, int D, int n_splits,
+                                  bf16* __restrict__ out, int64_t ld_out) {
+  const int h = blockIdx.x, t = blockIdx.y, d = threadIdx.x;
+  const float* w = work + ((size_t)t * Hq + h) * n_splits * (D + 2);
+  float M = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) M = fmaxf(M, w[(size_t)s * (D + 2) + D]);
+  float L = 0.f, O = 0.f;
+  if (M != -INFINITY) {
+    for (int s = 0; s < n_splits; ++s) {
+      const float ms = w[(size_t)s * (D + 2) + D];
+      const float c = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
+      L = fmaf(w[(size_t)s * (D + 2) + D + 1], c, L);
+      O = fmaf(w[(size_t)s * (D + 2) + d], c, O);
+    }
+  }
+  out[(size_t)t * ld_out + h * D + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+}
+
+// grid (T), 256 threads: rotate q in place, rotate k into the pages, copy v into the pages.
+__global__ void __launch_bounds__(256) kv_append_rope_kernel(bf16* __restrict__ qkv, int64_t ld,
+                                                             bf16* __restrict__ k_pages, bf16* __restrict__ v_pages,
+                                                             const int32_t* __restrict__ block_table, int max_pages,
+                                                             const int32_t* __restrict__ row_slot,
+                                                             const int32_t* __restrict__ row_pos, int Hq, int Hkv,
+                                                             int D, int PS, float theta) {
+  const int t = blockIdx.x;
+  const int slot = row_slot[t], pos = row_pos[t];
+  const int page = block_table[(size_t)slot * max_pages + pos / PS];
+  bf16* row = qkv + (size_t)t * ld;
+  const int half = D / 2;
+  for (int idx = threadIdx.x; idx < (Hq + Hkv) * half; idx += blockDim.x) {
+    const int head = idx / half, i = idx % half;
+    float sn, cs;
+    sincosf((float)pos * rope_inv_freq(theta, i, D), &sn, &cs);
+    bf16* p = row + (size_t)head * D;
+    const float x1 = __bfloat162float(p[i]), x2 = __bfloat162float(p[i + half]);
+    const bf16 r1 = __float2bfloat16_rn(x1 * cs - x2 * sn), r2 = __float2bfloat16_rn(x2 * cs + x1 * sn);
+    if (head < Hq) {
+      p[i] = r1;
+      p[i + half] = r2;
+    } else {
+      bf16* dst = k_pages + (((size_t)page * Hkv + (head - Hq)) * PS + pos % PS) * D;
+      dst[i] = r1;
+      dst[i + half] = r2;
+    }
+  }
+  const bf16* vsrc = row + (size_t)(Hq + Hkv) * D;
+  for (int idx = threadIdx.x; idx < Hkv * D / 8; idx += blockDim.x) {
+    const int head = (idx * 8) / D, d = (idx * 8) % D;
+    bf16* dst = v_pages + (((size_t)page * Hkv + head) * PS + pos % PS) * D + d;
+    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(vsrc + (size_t)head * D + d);
+  }
+}
+
+int pick_splits(int T, int Hq, int max_pages) {
+  const int base = T * Hq;
+  if (base >= 592) return 1;  // >= 4 CTAs on each of the 148 SMs already
+  int s = (592 + base - 1) / base;
+  s = s > 16 ? 16 : s;
+  const int by_ctx = max_pages / 4 > 0 ? max_pages / 4 : 1;
+  return s < by_ctx ? s : by_ctx;
+}
+
+}  // namespace
+}  // namespace mlora
+
+using namespace mlora;
+
+extern "C" size_t mlora_paged_attention_workspace(int32_t T, int32_t Hq, int32_t D, int32_t n_splits) {
+  if (n_splits <= 0) n_splits = 16;
+  if (n_splits == 1) return 0;
+  return (size_t)T * Hq * n_splits * (D + 2) * sizeof(float);
+}
+
+static int check_kv_common(const char* who, int T, int Hq, int Hkv, int D, int page_size) {
+  MLORA_REQUIRE(T >= 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "%s: bad head counts Hq=%d Hkv=%d", who, Hq, Hkv);
+  MLORA_REQUIRE(D == 64 || D == 128, "%s: head_dim %d not supported (64 or 128)", who, D);
+  MLORA_REQUIRE(page_size == 16 || page_size == 32, "%s: page_size %d not supported (16 or 32)", who, page_size);
+  return MLORA_OK;
+}
+
+extern "C" int mlora_kv_append_rope(void* d_qkv, int64_t ld, void* d_k_pages, void* d_v_pages,
+                                    const int32_t* d_block_table, int32_t max_pages, const int32_t* d_row_slot,
+                                    const int32_t* d_row_pos, int32_t T, int32_t Hq, int32_t Hkv, int32_t D,
+                                    int32_t page_size, float rope_theta, void* stream) {
+  int rc = check_kv_common("kv_append_rope", T, Hq, Hkv, D, page_size);
+  if (rc) return rc;
+  MLORA_REQUIRE(d_qkv && d_k_pages && d_v_pages && d_block_table && d_row_slot && d_row_pos && max_pages > 0,
+                "kv_append_rope: null pointer");
+  MLORA_REQUIRE(ld % 8 == 0 && aligned16(d_qkv) && aligned16(d_v_pages), "kv_append_rope: alignment");
+  if (T == 0) return MLORA_OK;
+  kv_append_rope_kernel<<<T, 256, 0, (cudaStream_t)stream>>>((bf16*)d_qkv, ld, (bf16*)d_k_pages, (bf16*)d_v_pages,
+                                                             d_block_table, max_pages, d_row_slot, d_row_pos, Hq, Hkv,
+                                                             D, page_size, rope_theta);
+  count_launch();
+  MLORA_CHECK_LAUNCH("kv_append_rope_kernel");
+  return MLORA_OK;
+}
+
+extern "C" int mlora_paged_attention(const void* d_qkv, int64_t ld, void* d_k_pages, void* d_v_pages,
+                                     const int32_t* d_block_table, int32_t max_pages, const int32_t* d_row_slot,
+                                     const int32_t* d_row_pos, int32_t T, int32_t Hq, int32_t Hkv, int32_t D,
+                                     int32_t page_size, float rope_theta, int32_t fused_append, void* d_out,
+                                     int64_t ld_out, int32_t n_splits, void* d_work, size_t work_bytes,
+                                     void* stream) {
+  int rc = check_kv_common("paged_attention", T, Hq, Hkv, D, page_size);
+  if (rc) return rc;
+  MLORA_REQUIRE(d_qkv && d_k_pages && d_v_pages && d_block_table && d_row_slot && d_row_pos && d_out && max_pages > 0,
+                "paged_attention: null pointer");
+  MLORA_REQUIRE(aligned16(d_k_pages) && aligned16(d_v_pages), "paged_attention: pages must be 16-byte aligned");
+  if (T == 0) return MLORA_OK;
+  MLORA_REQUIRE(T <= 65535, "paged_attention: T=%d exceeds 65535 rows per call", T);
+  if (n_splits <= 0) {
+    n_splits = pick_splits(T, Hq, max_pages);
+    while (n_splits > 1 && mlora_paged_attention_workspace(T, Hq, D, n_splits) > work_bytes) --n_splits;
+  }
+  MLORA_REQUIRE(n_splits <= 64, "paged_attention: n_splits=%d exceeds 64", n_splits);
+  if (n_splits > 1) {
+    size_t need = mlora_paged_attention_workspace(T, Hq, D, n_splits);
+    if (!d_work || work_bytes < need)
+      return fail(MLORA_ESIZE, "paged_attention: workspace of %zu bytes needed, %zu given", need, work_bytes);
+  }
+  AttnArgs a{(const bf16*)d_qkv, ld, (bf16*)d_k_pages, (bf16*)d_v_pages, d_block_table, max_pages, d_row_slot,
+             d_row_pos, T, Hq, Hkv, page_size, rope_theta, fused_append ? 1 : 0, (bf16*)d_out, ld_out, n_splits,
+             (float*)d_work};
+  dim3 grid(Hq, T, n_splits);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (D == 128 && page_size == 16)
+    paged_attn_kernel<128, 8><<<grid, 128, 0, st>>>(a);
+  else if (D == 128 && page_size == 32)
+    paged_attn_kernel<128, 16><<<grid, 128, 0, st>>>(a);
+  else if (D == 64 && page_size == 16)
+    paged_attn_kernel<64, 4><<<grid, 128, 0, st>>>(a);
+  else
+    paged_attn_kernel<64, 8><<<grid, 128, 0, st>>>(a);
+  count_launch();
+  if (n_splits > 1) {
+    attn_merge_kernel<<<dim3(Hq, T), D, 0, st>>>((const float*)d_work, Hq, D, n_splits, (bf16*)d_out, ld_out);
+    count_launch();
+  }
+  MLORA_CHECK_LAUNCH("paged_attn_kernel");
+  return MLORA_OK;
+}

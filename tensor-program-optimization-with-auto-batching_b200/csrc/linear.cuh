@@ -1,0 +1,72 @@
+// Argument block and epilogue shared by the projection kernels.
+#pragma once
+#include "common.cuh"
+
+namespace mlora {
+
+struct LinearArgs {
+  const bf16* x;
+  int64_t ldx;
+  const bf16* W;
+  void* y;
+  int64_t ldy;
+  int T, in, out;
+  const float* u;        // [T, n_mod*r_max] or nullptr
+  const bf16* B_all;     // [N, out, r_max]
+  const int32_t* ranks;  // [N]
+  const float* scales;   // [N]
+  const int32_t* slots;  // [T]
+  int r_max, n_mod;
+  int mod_off[9];
+  int flags;
+};
+
+// Module (q/k/v, gate/up ...) that owns output row o.
+__device__ __forceinline__ int module_of(const LinearArgs& a, int o) {
+  if (a.flags & MLORA_SILU_MUL) return (o >> 3) & 1;
+  int m = 0;
+#pragma unroll 1
+  while (m + 1 < a.n_mod && o >= a.mod_off[m + 1]) ++m;
+  return m;
+}
+
+// scale[s] * sum_j u[t, m*r_max + j] * B_all[s, o, j]   (0 when the row has no adapter)
+__device__ __forceinline__ float lora_expand(const LinearArgs& a, int t, int o) {
+  if (a.u == nullptr) return 0.f;
+  const int s = a.slots[t];
+  if (s < 0) return 0.f;
+  const int r = a.ranks[s];
+  const int m = module_of(a, o);
+  const float* ur = a.u + (size_t)t * (a.r_max * a.n_mod) + m * a.r_max;
+  const bf16* b = a.B_all + ((size_t)s * a.out + o) * a.r_max;
+  float acc = 0.f;
+  if ((a.r_max & 7) == 0) {
+    for (int j = 0; j < r; j += 8) {
+      float bf[8];
+      unpack8(ld_cached(b + j), bf);
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        if (j + e < r) acc = fmaf(ur[j + e], bf[e], acc);
+    }
+  } else {
+    for (int j = 0; j < r; ++j) acc = fmaf(ur[j], __bfloat162float(b[j]), acc);
+  }
+  return a.scales[s] * acc;
+}
+
+__device__ __forceinline__ float silu_mul(float g, float up) { return g / (1.f + __expf(-g)) * up; }
+
+__device__ __forceinline__ void store_out(const LinearArgs& a, int t, int col, float v) {
+  if (a.flags & MLORA_OUT_F32)
+    reinterpret_cast<float*>(a.y)[(size_t)t * a.ldy + col] = v;
+  else
+    reinterpret_cast<bf16*>(a.y)[(size_t)t * a.ldy + col] = __float2bfloat16_rn(v);
+}
+
+int launch_linear_simt(const LinearArgs& a, cudaStream_t st);
+// Tensor-core (tcgen05) weight-streaming kernel; returns MLORA_OK or an error.
+bool linear_tc_supported(const LinearArgs& a);
+size_t linear_tc_workspace(int T, int in, int out);
+int launch_linear_tc(const LinearArgs& a, void* work, size_t work_bytes, cudaStream_t st);
+
+}  // namespace mlora

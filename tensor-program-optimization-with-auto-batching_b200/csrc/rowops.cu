@@ -1,0 +1,216 @@
+// Row-wise kernels of the decode step: fused residual add + RMSNorm, embedding gather, greedy
+// argmax, and the device-side sequence-length bookkeeping.  One CTA per row, 128-bit accesses,
+// warp-shuffle reductions.
+#include <cfloat>
+
+#include "common.cuh"
+
+namespace mlora {
+namespace {
+
+__device__ __forceinline__ float block_sum(float v, float* sm /*[33]*/) {
+  v = warp_sum(v);
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  if (lane == 0) sm[w] = v;
+  __syncthreads();
+  if (w == 0) {
+    float t = lane < (blockDim.x + 31) / 32 ? sm[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) sm[32] = t;
+  }
+  __syncthreads();
+  float r = sm[32];
+  __syncthreads();
+  return r;
+}
+
+// res += delta; out = res * rsqrt(mean(res^2) + eps) * w.  H % 8 == 0.  The row is kept in
+// registers between the two passes (up to 4 chunks of 8 per thread = H <= 8192 at 256 threads),
+// longer rows re-read the updated residual.
+constexpr int kNormThreads = 256;
+constexpr int kNormChunks = 4;
+
+__global__ void __launch_bounds__(kNormThreads) residual_rmsnorm_kernel(const bf16* __restrict__ delta,
+                                                                        float* __restrict__ res,
+                                                                        const bf16* __restrict__ w, float eps,
+                                                                        bf16* __restrict__ out, int H) {
+  __shared__ float sm[33];
+  const size_t row = blockIdx.x;
+  float* r = res + row * H;
+  const bf16* d = delta ? delta + row * H : nullptr;
+  float keep[kNormChunks][8];
+  float ss = 0.f;
+  // pass 1: add the delta, store the new residual, accumulate the sum of squares
+  auto load_add = [&](int k, float (&v)[8]) {
+    float4 a = *reinterpret_cast<const float4*>(r + k);
+    float4 b = *reinterpret_cast<const float4*>(r + k + 4);
+    v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+    if (d) {
+      float df[8];
+      unpack8(ld_cached(d + k), df);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] += df[i];
+      *reinterpret_cast<float4*>(r + k) = make_float4(v[0], v[1], v[2], v[3]);
+      *reinterpret_cast<float4*>(r + k + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss = fmaf(v[i], v[i], ss);
+  };
+#pragma unroll
+  for (int c = 0; c < kNormChunks; ++c) {
+    const int k = (c * kNormThreads + threadIdx.x) * 8;
+    if (k < H) load_add(k, keep[c]);
+  }
+  for (int k = (kNormChunks * kNormThreads + threadIdx.x) * 8; k < H; k += kNormThreads * 8) {
+    float v[8];
+    load_add(k, v);
+  }
+  ss = block_sum(ss, sm);
+  const float inv = rsqrtf(ss / (float)H + eps);
+  // pass 2: scale and write
+  auto write = [&](int k, const float (&v)[8]) {
+    float wf[8], o[8];
+    unpack8(ld_cached(w + k), wf);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = v[i] * inv * wf[i];
+    *reinterpret_cast<uint4*>(out + row * H + k) = pack8(o);
+  };
+#pragma unroll
+  for (int c = 0; c < kNormChunks; ++c) {
+    const int k = (c * kNormThreads + threadIdx.x) * 8;
+    if (k < H) write(k, keep[c]);
+  }
+  for (int k = (kNormChunks * kNormThreads + threadIdx.x) * 8; k < H; k += kNormThreads * 8) {
+    float4 a = *reinterpret_cast<const float4*>(r + k);
+    float4 b = *reinterpret_cast<const float4*>(r + k + 4);
+    float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    write(k, v);
+  }
+}
+
+__global__ void __launch_bounds__(256) embed_kernel(const int32_t* __restrict__ ids, const bf16* __restrict__ E,
+                                                    int H, int vocab, float* __restrict__ res,
+                                                    bf16* __restrict__ out_bf16) {
+  const size_t row = blockIdx.x;
+  int id = ids[row];
+  id = min(max(id, 0), vocab - 1);  // out-of-range ids are clamped, never dereferenced
+  const bf16* e = E + (size_t)id * H;
+  for (int k = threadIdx.x * 8; k < H; k += blockDim.x * 8) {
+    uint4 raw = ld_cached(e + k);
+    if (res) {
+      float f[8];
+      unpack8(raw, f);
+      *reinterpret_cast<float4*>(res + row * H + k) = make_float4(f[0], f[1], f[2], f[3]);
+      *reinterpret_cast<float4*>(res + row * H + k + 4) = make_float4(f[4], f[5], f[6], f[7]);
+    }
+    if (out_bf16) *reinterpret_cast<uint4*>(out_bf16 + row * H + k) = raw;
+  }
+}
+
+// First index of the maximum (numpy argmax semantics; NaN never wins).
+__global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, int64_t ld, int V,
+                                                      int32_t* __restrict__ tok) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  const float* l = logits + (size_t)blockIdx.x * ld;
+  float best = -FLT_MAX;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    float v = l[i];
+    if (v > best) {  // strided ascending scan: first max per thread
+      best = v;
+      bi = i;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) {
+      best = ov;
+      bi = oi;
+    }
+  }
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  if (lane == 0) {
+    sv[w] = best;
+    si[w] = bi;
+  }
+  __syncthreads();
+  if (w == 0) {
+    best = lane < (blockDim.x >> 5) ? sv[lane] : -FLT_MAX;
+    bi = lane < (blockDim.x >> 5) ? si[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) {
+        best = ov;
+        bi = oi;
+      }
+    }
+    if (lane == 0) tok[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;
+  }
+}
+
+__global__ void kv_begin_decode_kernel(const int32_t* __restrict__ row_slot, int32_t* __restrict__ seq_lens,
+                                       int32_t* __restrict__ row_pos, int B) {
+  int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b < B) {
+    int s = row_slot[b];
+    int p = seq_lens[s];
+    row_pos[b] = p;
+    seq_lens[s] = p + 1;  // one row per sequence in a decode step, so no two threads share s
+  }
+}
+
+}  // namespace
+}  // namespace mlora
+
+using namespace mlora;
+
+extern "C" int mlora_residual_rmsnorm(const void* d_delta, float* d_res, const void* d_w, float eps, void* d_out,
+                                      int32_t T, int32_t H, void* stream) {
+  MLORA_REQUIRE(T >= 0 && H > 0 && H % 8 == 0, "residual_rmsnorm: H must be a positive multiple of 8 (H=%d)", H);
+  MLORA_REQUIRE(d_res && d_w && d_out, "residual_rmsnorm: null pointer");
+  MLORA_REQUIRE(aligned16(d_res) && aligned16(d_w) && aligned16(d_out) && aligned16(d_delta),
+                "residual_rmsnorm: pointers must be 16-byte aligned");
+  if (T == 0) return MLORA_OK;
+  residual_rmsnorm_kernel<<<T, kNormThreads, 0, (cudaStream_t)stream>>>((const bf16*)d_delta, d_res,
+                                                                        (const bf16*)d_w, eps, (bf16*)d_out, H);
+  count_launch();
+  MLORA_CHECK_LAUNCH("residual_rmsnorm_kernel");
+  return MLORA_OK;
+}
+
+extern "C" int mlora_embed(const int32_t* d_ids, const void* d_E, int32_t T, int32_t H, int32_t vocab,
+                           float* d_res, void* d_out_bf16, void* stream) {
+  MLORA_REQUIRE(T >= 0 && H > 0 && H % 8 == 0 && vocab > 0, "embed: bad sizes T=%d H=%d vocab=%d", T, H, vocab);
+  MLORA_REQUIRE(d_ids && d_E && (d_res || d_out_bf16), "embed: null pointer");
+  MLORA_REQUIRE(aligned16(d_E) && aligned16(d_res) && aligned16(d_out_bf16), "embed: pointers must be 16-byte aligned");
+  if (T == 0) return MLORA_OK;
+  embed_kernel<<<T, 256, 0, (cudaStream_t)stream>>>(d_ids, (const bf16*)d_E, H, vocab, d_res, (bf16*)d_out_bf16);
+  count_launch();
+  MLORA_CHECK_LAUNCH("embed_kernel");
+  return MLORA_OK;
+}
+
+extern "C" int mlora_argmax(const float* d_logits, int64_t ld, int32_t T, int32_t V, int32_t* d_tok, void* stream) {
+  MLORA_REQUIRE(T >= 0 && V > 0 && ld >= V, "argmax: bad sizes T=%d V=%d", T, V);
+  MLORA_REQUIRE(d_logits && d_tok, "argmax: null pointer");
+  if (T == 0) return MLORA_OK;
+  argmax_kernel<<<T, 1024, 0, (cudaStream_t)stream>>>(d_logits, ld, V, d_tok);
+  count_launch();
+  MLORA_CHECK_LAUNCH("argmax_kernel");
+  return MLORA_OK;
+}
+
+extern "C" int mlora_kv_begin_decode(const int32_t* d_row_slot, int32_t* d_seq_lens, int32_t* d_row_pos, int32_t B,
+                                     void* stream) {
+  MLORA_REQUIRE(B >= 0 && d_row_slot && d_seq_lens && d_row_pos, "kv_begin_decode: bad arguments");
+  if (B == 0) return MLORA_OK;
+  kv_begin_decode_kernel<<<(B + 127) / 128, 128, 0, (cudaStream_t)stream>>>(d_row_slot, d_seq_lens, d_row_pos, B);
+  count_launch();
+  MLORA_CHECK_LAUNCH("kv_begin_decode_kernel");
+  return MLORA_OK;
+}

@@ -1,0 +1,29 @@
+// Error reporting and launch counter shared by all entry points.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+
+#include "common.cuh"
+
+namespace mlora {
+
+static thread_local char g_err[512] = "";
+std::atomic<uint64_t> g_launches{0};
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+
+}  // namespace mlora
+
+extern "C" {
+int mlora_version(void) { return 100; }
+const char* mlora_last_error(void) { return mlora::g_err; }
+uint64_t mlora_launch_count(void) { return mlora::g_launches.load(std::memory_order_relaxed); }
+}

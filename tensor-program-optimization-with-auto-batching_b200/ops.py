@@ -1,0 +1,192 @@
+"""Operator wrappers: torch CUDA tensors in, C-ABI calls on the current stream.
+
+torch is used for device memory and streams only; every computation below
+happens inside ``libmlora.so``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+from ._lib import check
+
+OUT_F32, SILU_MUL, FORCE_SIMT = 1, 2, 4
+
+
+def _ptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise ValueError("mlora operators need CUDA tensors (there is no CPU path)")
+
+
+_workspaces = {}
+
+
+def workspace(nbytes: int, device, tag="default"):
+    """A cached scratch buffer per (device, tag), grown on demand."""
+    key = (torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device(), tag)
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf
+
+
+# ---------------------------------------------------------------- bucketing
+@dataclass
+class Buckets:
+    perm: torch.Tensor          # [n] int32
+    sorted_tid: torch.Tensor    # [n] int32
+    sorted_wid: torch.Tensor    # [n] int32
+    seg_offsets: torch.Tensor   # [n_keys+1] int32 (first n_seg+1 valid)
+    seg_tid: torch.Tensor       # [n_keys]
+    seg_wid: torch.Tensor       # [n_keys]
+    counts: torch.Tensor        # [n_types+2]: n_seg, rows without adapter, rows per type
+
+
+def bucket_sort(tids, wids, n_types: int, n_wids: int, by_type_only: bool = False) -> Buckets:
+    _need_cuda(tids, wids)
+    n = wids.numel()
+    dev = wids.device
+    nt = max(n_types, 1) if tids is None else n_types
+    n_keys = nt + 1 if by_type_only else 1 + nt * n_wids
+    i32 = dict(dtype=torch.int32, device=dev)
+    out = Buckets(torch.empty(n, **i32), torch.empty(n, **i32), torch.empty(n, **i32),
+                  torch.zeros(n_keys + 1, **i32), torch.full((n_keys,), -2, **i32),
+                  torch.full((n_keys,), -2, **i32), torch.zeros(nt + 2, **i32))
+    wb = _lib.lib().mlora_bucket_sort_workspace(n, nt, n_wids)
+    ws = workspace(wb, dev, "bucket") if wb else None
+    check(_lib.lib().mlora_bucket_sort(
+        _ptr(tids), _ptr(wids), n, n_types, n_wids, int(by_type_only), _ptr(out.perm), _ptr(out.sorted_tid),
+        _ptr(out.sorted_wid), _ptr(out.seg_offsets), _ptr(out.seg_tid), _ptr(out.seg_wid), _ptr(out.counts),
+        _ptr(ws), wb, _stream()), "mlora_bucket_sort")
+    return out
+
+
+# ---------------------------------------------------------------- LoRA + projection
+@dataclass
+class LoraStack:
+    """Packed adapters of one (fused) projection.
+
+    A_all [N, n_mod*r_max, in] bf16, B_all [N, out, r_max] bf16 (module m of
+    adapter s uses rows m*r_max.. of A and its own rows of B), ranks [N] int32,
+    scales [N] float32 (alpha/r), mod_offsets: host list of n_mod+1 output-row
+    offsets.
+    """
+    A_all: torch.Tensor
+    B_all: torch.Tensor
+    ranks: torch.Tensor
+    scales: torch.Tensor
+    r_max: int
+    n_mod: int = 1
+    mod_offsets: tuple = None
+
+
+def lora_shrink(x, stack: LoraStack, slots, out=None):
+    _need_cuda(x, slots)
+    T, K = x.shape
+    r_tot = stack.r_max * stack.n_mod
+    u = out if out is not None else torch.empty(T, r_tot, dtype=torch.float32, device=x.device)
+    check(_lib.lib().mlora_lora_shrink(_ptr(x), x.stride(0), _ptr(stack.A_all), _ptr(stack.ranks), _ptr(slots),
+                                       T, K, stack.r_max, stack.n_mod, _ptr(u), _stream()), "mlora_lora_shrink")
+    return u
+
+
+def linear(x, W, stack: LoraStack = None, slots=None, u=None, flags: int = 0, out=None, use_workspace=True):
+    """y = x W^T (+ LoRA expand of ``u``) ; see ``mlora_linear`` in include/mlora.h."""
+    _need_cuda(x, W)
+    if x.dtype != torch.bfloat16 or W.dtype != torch.bfloat16:
+        raise ValueError("mlora.linear needs bf16 x and W")
+    T, K = x.shape
+    N = W.shape[0]
+    cols = N // 2 if flags & SILU_MUL else N
+    if out is None:
+        out = torch.empty(T, cols, dtype=torch.float32 if flags & OUT_F32 else torch.bfloat16, device=x.device)
+    mod = None
+    if stack is not None and u is None:
+        u = lora_shrink(x, stack, slots)
+    if stack is not None and stack.n_mod > 1 and not flags & SILU_MUL:
+        mod = (C.c_int32 * (stack.n_mod + 1))(*stack.mod_offsets)
+    wb = _lib.lib().mlora_linear_workspace(T, K, N) if use_workspace else 0
+    ws = workspace(wb, x.device, "linear") if wb else None
+    check(_lib.lib().mlora_linear(
+        _ptr(x), x.stride(0), _ptr(W), _ptr(out), out.stride(0), T, K, N,
+        _ptr(u) if stack is not None else None, _ptr(stack.B_all) if stack is not None else None,
+        _ptr(stack.ranks) if stack is not None else None, _ptr(stack.scales) if stack is not None else None,
+        _ptr(slots) if stack is not None else None, stack.r_max if stack is not None else 0,
+        stack.n_mod if stack is not None else 1, mod, flags, _ptr(ws), wb, _stream()), "mlora_linear")
+    return out
+
+
+# ---------------------------------------------------------------- row ops
+def residual_rmsnorm(delta, res, w, eps: float, out=None):
+    _need_cuda(res, w)
+    T, H = res.shape
+    if out is None:
+        out = torch.empty(T, H, dtype=torch.bfloat16, device=res.device)
+    check(_lib.lib().mlora_residual_rmsnorm(_ptr(delta), _ptr(res), _ptr(w), eps, _ptr(out), T, H, _stream()),
+          "mlora_residual_rmsnorm")
+    return out
+
+
+def embed(ids, E, res=None, out_bf16=None):
+    _need_cuda(ids, E)
+    T = ids.numel()
+    V, H = E.shape
+    if res is None and out_bf16 is None:
+        res = torch.empty(T, H, dtype=torch.float32, device=E.device)
+    check(_lib.lib().mlora_embed(_ptr(ids), _ptr(E), T, H, V, _ptr(res), _ptr(out_bf16), _stream()), "mlora_embed")
+    return res if res is not None else out_bf16
+
+
+def argmax(logits, out=None):
+    _need_cuda(logits)
+    T, V = logits.shape
+    if out is None:
+        out = torch.empty(T, dtype=torch.int32, device=logits.device)
+    check(_lib.lib().mlora_argmax(_ptr(logits), logits.stride(0), T, V, _ptr(out), _stream()), "mlora_argmax")
+    return out
+
+
+# ---------------------------------------------------------------- paged KV
+def kv_append_rope(qkv, k_pages, v_pages, block_table, row_slot, row_pos, Hq, Hkv, D, page_size, theta):
+    _need_cuda(qkv, k_pages)
+    T = qkv.shape[0]
+    check(_lib.lib().mlora_kv_append_rope(
+        _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
+        _ptr(row_slot), _ptr(row_pos), T, Hq, Hkv, D, page_size, theta, _stream()), "mlora_kv_append_rope")
+
+
+def paged_attention(qkv, k_pages, v_pages, block_table, row_slot, row_pos, Hq, Hkv, D, page_size, theta,
+                    fused_append: bool, out=None, n_splits: int = 0):
+    _need_cuda(qkv, k_pages)
+    T = qkv.shape[0]
+    if out is None:
+        out = torch.empty(T, Hq * D, dtype=torch.bfloat16, device=qkv.device)
+    wb = _lib.lib().mlora_paged_attention_workspace(T, Hq, D, n_splits)
+    ws = workspace(wb, qkv.device, "attn") if wb else None
+    check(_lib.lib().mlora_paged_attention(
+        _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
+        _ptr(row_slot), _ptr(row_pos), T, Hq, Hkv, D, page_size, theta, int(fused_append), _ptr(out),
+        out.stride(0), n_splits, _ptr(ws), wb, _stream()), "mlora_paged_attention")
+    return out
+
+
+def kv_begin_decode(row_slot, seq_lens, row_pos):
+    check(_lib.lib().mlora_kv_begin_decode(_ptr(row_slot), _ptr(seq_lens), _ptr(row_pos), row_slot.numel(),
+                                           _stream()), "mlora_kv_begin_decode")
+
+
+def launch_count() -> int:
+    return int(_lib.lib().mlora_launch_count())

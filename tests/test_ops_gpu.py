@@ -1,0 +1,305 @@
+"""Parity of each CUDA operator (called through the C ABI) against the CPU oracle."""
+import json
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import bucketing, ops as oops
+
+pytestmark = pytest.mark.gpu
+G = os.path.join(os.path.dirname(__file__), "golden")
+
+# bf16 outputs vs an fp32 oracle fed the same bf16-rounded inputs
+ATOL, RTOL = 2e-2, 1e-2
+
+
+def _i32(a, dev):
+    return torch.as_tensor(np.asarray(a, dtype=np.int32), device=dev)
+
+
+# ----------------------------------------------------------------------------- bucketing
+def _run_bucket(ops, dev, tids, wids, n_types, n_wids, by_type):
+    b = ops.bucket_sort(_i32(tids, dev) if tids is not None else None, _i32(wids, dev), n_types, n_wids, by_type)
+    torch.cuda.synchronize()
+    return b
+
+
+def test_bucket_sort_matches_reference_golden(ops, cuda):
+    with open(os.path.join(G, "bucketing_golden.json")) as f:
+        cases = json.load(f)["order_cases"]
+    for c in cases:
+        nt = c["n_types"]
+        tids = [c["tids"][s] for s in c["batch"]]
+        wids = [c["wids"][s] for s in c["batch"]]
+        n_wids = max(max(wids) + 1, 1)
+        b = _run_bucket(ops, cuda, tids, wids, nt, n_wids, False)
+        perm = b.perm.cpu().tolist()
+        if nt > 0:  # with no adapter type the reference returns the batch unchanged; a stable sort agrees
+            assert perm == c["positions"]
+        assert [c["batch"][p] for p in perm] == c["ordered"]
+        # per-step method selection on the (already ordered, shrinking) live batch
+        for st in c["steps"]:
+            lt = [c["tids"][s] for s in st["live"]]
+            lw = [c["wids"][s] for s in st["live"]]
+            bt = _run_bucket(ops, cuda, lt, lw, nt, n_wids, True)
+            counts = bt.counts.cpu().tolist()
+            p = bt.perm.cpu().tolist()
+            sw = bt.sorted_wid.cpu().tolist()
+            non_empty = [t for t in range(nt) if counts[2 + t] > 0]
+            no_adapter = counts[1] > 0
+            if no_adapter and not non_empty:
+                name, params = "decode_no_adapter", []
+            elif not no_adapter and len(non_empty) == 1:
+                name, params = f"decode_a{non_empty[0]}", [sw]
+            else:
+                name = "mixed_decode_" + "_".join(f"a{t}" for t in non_empty)
+                params, off = [], counts[1]
+                for t in range(nt):
+                    if counts[2 + t]:
+                        params += [p[off:off + counts[2 + t]], sw[off:off + counts[2 + t]]]
+                    off += counts[2 + t]
+            assert name == st["name"]
+            assert params == st["params"]
+
+
+@pytest.mark.parametrize("n", [0, 1, 31, 32, 1024, 1025, 5000, 40000])
+def test_bucket_sort_segments(ops, cuda, n):
+    rng = np.random.default_rng(n)
+    n_ad = 16 if n < 5000 else 64
+    slots = rng.integers(-1, n_ad, n).astype(np.int32)
+    if n == 32:
+        slots[:] = 3  # one giant segment
+    b = _run_bucket(ops, cuda, None, slots, 1, n_ad, False)
+    perm, off, seg = bucketing.segment_sort(slots)
+    n_seg = int(b.counts[0])
+    assert n_seg == len(seg)
+    assert b.perm.cpu().numpy().tolist() == perm.tolist()
+    assert b.seg_offsets[: n_seg + 1].cpu().numpy().tolist() == off.tolist()
+    assert b.seg_wid[:n_seg].cpu().numpy().tolist() == seg.tolist()
+    assert b.sorted_wid.cpu().numpy().tolist() == slots[perm].tolist()
+    assert int(b.counts[1]) == int((slots < 0).sum())
+
+
+# ----------------------------------------------------------------------------- LoRA + projection
+def _stack(ops, A, B, ranks, scales, dev, n_mod=1, mod_offsets=None):
+    return ops.LoraStack(A.to(dev), B.to(dev), _i32(ranks, dev), torch.tensor(scales, dtype=torch.float32, device=dev),
+                         B.shape[2], n_mod, mod_offsets)
+
+
+@pytest.mark.parametrize("T", [1, 8, 32, 128])
+def test_operator_case_against_oracle(ops, synth, cuda, T):
+    """The operator micro-benchmark shapes: y = x W^T + 2 (x A[id]) B[id]."""
+    c = synth.operator_case(T)
+    st = _stack(ops, c["A"], c["B"], [16] * 16, [c["scale"]] * 16, cuda)
+    ids = c["ids"].to(cuda)
+    x, W = c["x"].to(cuda), c["W"].to(cuda)
+    want = oops.multi_lora_linear(c["x"].float(), c["W"].float(), c["A"].float(), c["B"].float(), [16] * 16,
+                                  [c["scale"]] * 16, c["ids"])
+    for flags in (ops.FORCE_SIMT, 0):
+        y = ops.linear(x, W, st, ids, flags=flags)
+        torch.testing.assert_close(y.float().cpu(), want, atol=ATOL, rtol=RTOL)
+    base = ops.linear(x, W)
+    torch.testing.assert_close(base.float().cpu(), c["x"].float() @ c["W"].float().t(), atol=ATOL, rtol=RTOL)
+
+
+def test_lora_layer_golden_through_cuda(ops, cuda):
+    """Reference GatherBMMLinear outputs (fp32) vs the CUDA path on bf16-rounded copies."""
+    z = np.load(os.path.join(G, "lora_layer_golden.npz"))
+    for i in range(int(z["n_cases"])):
+        x = torch.from_numpy(z[f"c{i}_x"]).bfloat16()
+        W = torch.from_numpy(z[f"c{i}_W"]).bfloat16()
+        A = torch.from_numpy(z[f"c{i}_A"]).bfloat16()
+        B = torch.from_numpy(z[f"c{i}_B"]).bfloat16()
+        ids, scale = z[f"c{i}_ids"], float(z[f"c{i}_scale"])
+        Bsz, S, fin = x.shape
+        n, r = A.shape[0], A.shape[1]
+        st = _stack(ops, A, B, [r] * n, [scale] * n, cuda)
+        slots = _i32(np.repeat(ids, S), cuda)
+        y = ops.linear(x.reshape(Bsz * S, fin).to(cuda), W.to(cuda), st, slots).float().cpu().reshape(Bsz, S, -1)
+        # bf16 rounding of inputs and output: compare with the fp32 reference output loosely ...
+        torch.testing.assert_close(y, torch.from_numpy(z[f"c{i}_y"]), atol=5e-2, rtol=5e-2)
+        # ... and tightly with the oracle on the same rounded inputs
+        want = oops.gather_bmm_linear(x.float(), W.float(), list(A.float()), list(B.float()), [scale] * n, ids)
+        torch.testing.assert_close(y, want, atol=ATOL, rtol=RTOL)
+
+
+def test_mixed_ranks_no_adapter_rows_and_modules(ops, cuda):
+    g = torch.Generator().manual_seed(11)
+    T, K, outs = 13, 320, (64, 32, 32)
+    N_out = sum(outs)
+    ranks = [8, 16, 32, 64, 16]
+    r_max, n_mod, n_ad = 64, 3, len(ranks)
+    x = torch.randn(T, K, generator=g).bfloat16()
+    W = (torch.randn(N_out, K, generator=g) * 0.05).bfloat16()
+    A = (torch.randn(n_ad, n_mod * r_max, K, generator=g) * 0.05).bfloat16()
+    B = (torch.randn(n_ad, N_out, r_max, generator=g) * 0.05).bfloat16()
+    scales = [2.0, 1.0, 0.5, 0.25, 4.0]
+    slots = np.array([0, 1, -1, 2, 3, 4, 4, -1, 0, 3, 1, 2, 0], dtype=np.int32)
+    offs = (0, 64, 96, 128)
+    st = _stack(ops, A, B, ranks, scales, cuda, n_mod, offs)
+    y = ops.linear(x.to(cuda), W.to(cuda), st, _i32(slots, cuda)).float().cpu()
+    want = x.float() @ W.float().t()
+    for t in range(T):
+        s = int(slots[t])
+        if s < 0:
+            continue
+        r = ranks[s]
+        for m in range(n_mod):
+            u = A[s, m * r_max:m * r_max + r].float() @ x[t].float()
+            want[t, offs[m]:offs[m + 1]] += scales[s] * (B[s, offs[m]:offs[m + 1], :r].float() @ u)
+    torch.testing.assert_close(y, want, atol=ATOL, rtol=RTOL)
+
+
+@pytest.mark.parametrize("T,K,I", [(3, 256, 688), (32, 512, 1024)])
+def test_gate_up_silu_interleaved(ops, cuda, T, K, I):
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(T, K, generator=g).bfloat16()
+    Wg = (torch.randn(I, K, generator=g) * 0.05).bfloat16()
+    Wu = (torch.randn(I, K, generator=g) * 0.05).bfloat16()
+    Wi = torch.stack([Wg.view(I // 8, 8, K), Wu.view(I // 8, 8, K)], 1).reshape(2 * I, K).contiguous()
+    want = oops.silu_mul(x.float() @ Wg.float().t(), x.float() @ Wu.float().t())
+    for flags in (ops.SILU_MUL | ops.FORCE_SIMT, ops.SILU_MUL):
+        y = ops.linear(x.to(cuda), Wi.to(cuda), flags=flags).float().cpu()
+        torch.testing.assert_close(y, want, atol=ATOL, rtol=RTOL)
+
+
+def test_f32_logits_and_argmax(ops, cuda):
+    g = torch.Generator().manual_seed(4)
+    T, K, V = 5, 256, 32000
+    x = torch.randn(T, K, generator=g).bfloat16()
+    W = (torch.randn(V, K, generator=g) * 0.05).bfloat16()
+    lg = ops.linear(x.to(cuda), W.to(cuda), flags=ops.OUT_F32)
+    assert lg.dtype == torch.float32
+    want = x.float() @ W.float().t()
+    torch.testing.assert_close(lg.cpu(), want, atol=1e-3, rtol=1e-3)
+    tok = ops.argmax(lg).cpu()
+    assert tok.tolist() == lg.cpu().argmax(-1).tolist()
+    # ties resolve to the first index, like numpy
+    tie = torch.zeros(3, 1000, device=cuda)
+    tie[0, [7, 500]] = 1.0
+    tie[1, 999] = 2.0
+    assert ops.argmax(tie).cpu().tolist() == [7, 999, 0]
+
+
+# ----------------------------------------------------------------------------- row ops
+@pytest.mark.parametrize("H", [256, 4096, 5120, 11008])
+def test_residual_rmsnorm(ops, cuda, H):
+    g = torch.Generator().manual_seed(H)
+    T = 7
+    res = torch.randn(T, H, generator=g)
+    delta = torch.randn(T, H, generator=g).bfloat16()
+    w = (1 + 0.1 * torch.randn(H, generator=g)).bfloat16()
+    r = res.clone().to(cuda)
+    out = ops.residual_rmsnorm(delta.to(cuda), r, w.to(cuda), 1e-5)
+    new_res = res + delta.float()
+    assert torch.equal(r.cpu(), new_res)  # one fp32 add per element: bit-exact
+    torch.testing.assert_close(out.float().cpu(), oops.rmsnorm(new_res, w, 1e-5), atol=ATOL, rtol=RTOL)
+    out2 = ops.residual_rmsnorm(None, r, w.to(cuda), 1e-5)
+    assert torch.equal(out2, out)
+
+
+def test_embed(ops, cuda):
+    g = torch.Generator().manual_seed(8)
+    E = torch.randn(1000, 256, generator=g).bfloat16()
+    ids = torch.tensor([0, 999, 5, 5, 17], dtype=torch.int32)
+    res = ops.embed(ids.to(cuda), E.to(cuda))
+    assert torch.equal(res.cpu(), E[ids.long()].float())
+
+
+# ----------------------------------------------------------------------------- paged KV
+def _paged_case(seed, B, Hq, Hkv, D, ps, lens, dev, max_pages=None):
+    """Random cache with shuffled page ids; returns tensors on CPU (bf16) + tables."""
+    g = torch.Generator().manual_seed(seed)
+    need = [(n + 1 + ps - 1) // ps for n in lens]
+    max_pages = max_pages or max(need) + 1
+    n_pages = sum(need) + 3
+    page_ids = torch.randperm(n_pages, generator=g)[: sum(need)].tolist()
+    bt = np.full((B, max_pages), -1, dtype=np.int32)
+    it = iter(page_ids)
+    for b in range(B):
+        for p in range(need[b]):
+            bt[b, p] = next(it)
+    kp = torch.randn(n_pages, Hkv, ps, D, generator=g).bfloat16()
+    vp = torch.randn(n_pages, Hkv, ps, D, generator=g).bfloat16()
+    qkv = torch.randn(B, (Hq + 2 * Hkv) * D, generator=g).bfloat16()
+    return kp, vp, qkv, bt
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,ps", [(4, 4, 64, 16), (32, 32, 128, 16), (8, 2, 128, 16), (4, 2, 64, 32),
+                                         (4, 4, 128, 32)])
+@pytest.mark.parametrize("n_splits", [1, 3, 0])
+def test_paged_attention_decode_fused_append(ops, cuda, Hq, Hkv, D, ps, n_splits):
+    lens = [0, 1, 15, 16, 17, 100, 511]
+    B = len(lens)
+    theta = 10000.0
+    kp, vp, qkv, bt = _paged_case(1, B, Hq, Hkv, D, ps, lens, cuda)
+    kp_d, vp_d = kp.to(cuda), vp.to(cuda)
+    slot = np.arange(B, dtype=np.int32)[::-1].copy()  # rows use slots in reverse order
+    bt_by_slot = np.zeros_like(bt)
+    for b in range(B):
+        bt_by_slot[slot[b]] = bt[b]
+    pos = np.array(lens, dtype=np.int32)
+    out = ops.paged_attention(qkv.to(cuda), kp_d, vp_d, _i32(bt_by_slot, cuda), _i32(slot, cuda), _i32(pos, cuda),
+                              Hq, Hkv, D, ps, theta, True, n_splits=n_splits).float().cpu()
+    # oracle: rotate q and new k, append, attend
+    q = qkv[:, : Hq * D].view(B, Hq, D)
+    k = qkv[:, Hq * D:(Hq + Hkv) * D].view(B, Hkv, D)
+    v = qkv[:, (Hq + Hkv) * D:].view(B, Hkv, D)
+    qr = oops.rope_rotate_half(q, torch.from_numpy(pos), theta)
+    kr = oops.rope_rotate_half(k, torch.from_numpy(pos), theta).bfloat16()
+    kp2, vp2 = kp.clone(), vp.clone()
+    for b in range(B):
+        page = bt[b, lens[b] // ps]
+        kp2[page, :, lens[b] % ps] = kr[b]
+        vp2[page, :, lens[b] % ps] = v[b]
+    want = oops.paged_attention_decode(qr, kp2, vp2, bt, pos + 1).reshape(B, Hq * D)
+    torch.testing.assert_close(out, want, atol=ATOL, rtol=RTOL)
+    # block-table gather / append: the pages now hold exactly the oracle's bytes
+    torch.testing.assert_close(kp_d.cpu().float(), kp2.float(), atol=1e-2, rtol=1e-2)
+    assert torch.equal(vp_d.cpu(), vp2)
+    untouched = torch.ones(kp.shape[0], dtype=torch.bool)
+    untouched[[bt[b, lens[b] // ps] for b in range(B)]] = False
+    assert torch.equal(kp_d.cpu()[untouched], kp[untouched])
+
+
+def test_append_then_attention_prefill_rows(ops, cuda):
+    """Prefill form: a chunk of rows of two sequences appended, then attended causally."""
+    Hq, Hkv, D, ps, theta = 4, 4, 64, 16, 10000.0
+    g = torch.Generator().manual_seed(2)
+    S = [37, 20]
+    T = sum(S)
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, generator=g).bfloat16()
+    slot = np.array([1] * S[0] + [0] * S[1], dtype=np.int32)
+    pos = np.array(list(range(S[0])) + list(range(S[1])), dtype=np.int32)
+    bt = np.array([[5, 2, 7, -1], [0, 6, 1, 3]], dtype=np.int32)  # by slot
+    kp = torch.zeros(8, Hkv, ps, D, dtype=torch.bfloat16, device=cuda)
+    vp = torch.zeros_like(kp)
+    qkv_d = qkv.to(cuda)
+    ops.kv_append_rope(qkv_d, kp, vp, _i32(bt, cuda), _i32(slot, cuda), _i32(pos, cuda), Hq, Hkv, D, ps, theta)
+    out = ops.paged_attention(qkv_d, kp, vp, _i32(bt, cuda), _i32(slot, cuda), _i32(pos, cuda), Hq, Hkv, D, ps,
+                              theta, False).float().cpu()
+    q = qkv[:, : Hq * D].view(T, Hq, D)
+    k = qkv[:, Hq * D:(Hq + Hkv) * D].view(T, Hkv, D)
+    v = qkv[:, (Hq + Hkv) * D:].view(T, Hkv, D)
+    qr = oops.rope_rotate_half(q, torch.from_numpy(pos), theta).bfloat16()
+    kr = oops.rope_rotate_half(k, torch.from_numpy(pos), theta).bfloat16()
+    torch.testing.assert_close(qkv_d[:, : Hq * D].float().cpu(), qr.float().view(T, -1), atol=1e-2, rtol=1e-2)
+    a, want = 0, []
+    for n in S:
+        want.append(oops.causal_attention(qr[a:a + n], kr[a:a + n], v[a:a + n]).reshape(n, Hq * D))
+        a += n
+    torch.testing.assert_close(out, torch.cat(want), atol=ATOL, rtol=RTOL)
+    # gather through the block table returns the appended keys in order
+    got = oops.paged_gather(kp.cpu(), bt[1], S[0])
+    torch.testing.assert_close(got.float(), kr[: S[0]].float(), atol=1e-2, rtol=1e-2)
+
+
+def test_kv_begin_decode(ops, cuda):
+    seq = _i32([5, 0, 9, 3], cuda)
+    rows = _i32([2, 0], cuda)
+    pos = torch.empty(2, dtype=torch.int32, device=cuda)
+    ops.kv_begin_decode(rows, seq, pos)
+    assert pos.cpu().tolist() == [9, 5] and seq.cpu().tolist() == [6, 0, 10, 3]
