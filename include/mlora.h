@@ -90,7 +90,11 @@ int mlora_lora_shrink(const void* d_x, int64_t ldx, const void* d_A_all, const i
  *   row stride ldy elements; d_B_all [N, out, r_max] bf16; d_scales [N] float32;
  *   h_mod_offsets: HOST array of n_mod+1 ints (NULL when n_mod == 1), n_mod <= 8.
  *   d_work / work_bytes: scratch for split-K partial sums of the tensor-core kernel,
- *   mlora_linear_workspace(T, in, out) bytes (may be NULL/0: then the CUDA-core kernel runs). */
+ *   mlora_linear_workspace(T, in, out) bytes (may be NULL/0: then the CUDA-core kernel runs).  The
+ *   buffer must be zero-filled once before its first use (arrival counters; they reset themselves)
+ *   and may be shared by calls of any shape on one stream; concurrent calls need separate buffers.
+ *   Its first int32 is a status word: non-zero after a kernel gave up a bounded wait (bit 0: TMA
+ *   producer, bit 1: MMA issuer, bit 2: epilogue); the output of that call is then undefined. */
 size_t mlora_linear_workspace(int32_t T, int32_t in, int32_t out);
 int mlora_linear(const void* d_x, int64_t ldx, const void* d_W, void* d_y, int64_t ldy, int32_t T,
                  int32_t in, int32_t out, const float* d_u, const void* d_B_all,

@@ -236,7 +236,7 @@ extern "C" int mlora_bucket_sort(const int32_t* d_tids, const int32_t* d_wids, i
                                  size_t work_bytes, void* stream) {
   MLORA_REQUIRE(n >= 0 && n_types >= 0 && n_wids >= 1, "bucket_sort: bad sizes n=%d n_types=%d n_wids=%d", n,
                 n_types, n_wids);
-  MLORA_REQUIRE(d_wids && d_perm && d_seg_offsets && d_seg_tid && d_seg_wid && d_counts,
+  MLORA_REQUIRE((n == 0 || (d_wids && d_perm)) && d_seg_offsets && d_seg_tid && d_seg_wid && d_counts,
                 "bucket_sort: null pointer");
   if (!d_tids && n_types == 0) n_types = 1;
   KeySpec ks{n_types, n_wids, by_type_only ? 1 : 0, key_count(n_types, n_wids, by_type_only)};

@@ -34,11 +34,12 @@ _workspaces = {}
 
 
 def workspace(nbytes: int, device, tag="default"):
-    """A cached scratch buffer per (device, tag), grown on demand."""
+    """A cached scratch buffer per (device, tag), grown on demand.  Zero-filled when created:
+    the split-K arrival counters of ``mlora_linear`` must start at zero (they reset themselves)."""
     key = (torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device(), tag)
     buf = _workspaces.get(key)
     if buf is None or buf.numel() < nbytes:
-        buf = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+        buf = torch.zeros(max(int(nbytes), 256), dtype=torch.uint8, device=device)
         _workspaces[key] = buf
     return buf
 

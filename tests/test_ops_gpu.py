@@ -303,3 +303,27 @@ def test_kv_begin_decode(ops, cuda):
     pos = torch.empty(2, dtype=torch.int32, device=cuda)
     ops.kv_begin_decode(rows, seq, pos)
     assert pos.cpu().tolist() == [9, 5] and seq.cpu().tolist() == [6, 0, 10, 3]
+
+
+@pytest.mark.parametrize("T,K,N", [(1, 64, 128), (16, 256, 256), (32, 4096, 4096), (33, 688, 256), (128, 4096, 512),
+                                   (200, 512, 384), (7, 1024, 200), (32, 11008, 4096), (300, 256, 12288)])
+def test_tensor_core_projection_shapes(ops, cuda, T, K, N):
+    """Ragged K / out / T, several token tiles, split-K and no split: tcgen05 path == CUDA-core path == oracle."""
+    g = torch.Generator().manual_seed(T * 7 + K)
+    x = torch.randn(T, K, generator=g).bfloat16()
+    W = (torch.randn(N, K, generator=g) * 0.05).bfloat16()
+    n_ad, r = 5, 16
+    A = (torch.randn(n_ad, r, K, generator=g) * 0.05).bfloat16()
+    B = (torch.randn(n_ad, N, r, generator=g) * 0.05).bfloat16()
+    slots = torch.randint(-1, n_ad, (T,), generator=g).int()
+    st = _stack(ops, A, B, [r] * n_ad, [1.5] * n_ad, cuda)
+    want = oops.multi_lora_linear(x.float(), W.float(), A.float(), B.float(), [r] * n_ad, [1.5] * n_ad, slots)
+    xd, Wd, sd = x.to(cuda), W.to(cuda), slots.to(cuda)
+    y_tc = ops.linear(xd, Wd, st, sd)
+    y_tc2 = ops.linear(xd, Wd, st, sd)
+    y_simt = ops.linear(xd, Wd, st, sd, flags=ops.FORCE_SIMT)
+    torch.cuda.synchronize()
+    assert int(ops.workspace(4, cuda, "linear")[:4].view(torch.int32)) == 0, "a bounded wait expired"
+    torch.testing.assert_close(y_tc.float().cpu(), want, atol=ATOL, rtol=RTOL)
+    assert torch.equal(y_tc, y_tc2)  # split-K partials are summed in a fixed order
+    torch.testing.assert_close(y_tc.float(), y_simt.float(), atol=ATOL, rtol=RTOL)
