@@ -1,0 +1,338 @@
+"""Llama decoder with per-request LoRA on the libmlora kernels.
+
+The graph is the one of ``tvm/llama_auto_batcher/llama_for_causal_lm.py``
+(``LlamaFFN`` :28-36, ``LlamaAttention`` :38-67, ``LlamaDecoderLayer`` :71-84,
+``LlamaModel`` :86-100, ``get_logits`` :124-128, last-token slice of prefill
+:130-137) with the LoRA application of ``compile_tvm.py:115-161``, lowered by
+hand to this kernel sequence per layer:
+
+    residual_rmsnorm -> lora_shrink(q,k,v) -> linear(W_qkv, +expand)
+    -> paged_attention (RoPE + append fused for decode)
+    -> lora_shrink(o) -> linear(W_o, +expand)
+    -> residual_rmsnorm -> linear(W_gate|W_up, +expand, SiLU*up) -> linear(W_down, +expand)
+
+Weights are packed once at load: q,k,v rows concatenated; gate/up rows
+interleaved in blocks of 8 so SiLU*up happens in the projection epilogue;
+adapters stacked per projection as A_all [N, n_mod*r_max, in] / B_all
+[N, out, r_max] (the stacking ``prepare_model_weights`` does at
+``compile_tvm.py:296-314``, kept K-contiguous instead of transposed).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+from . import ops
+from .kv_cache import PagedKVCache
+from .ops import LoraStack, OUT_F32, SILU_MUL
+
+ATTN_PROJ = ("q_proj", "k_proj", "v_proj", "o_proj")
+MLP_PROJ = ("gate_proj", "up_proj", "down_proj")
+
+
+def interleave_gate_up(g, u):
+    """[I,K],[I,K] -> [2I,K] with rows 16j..16j+7 = gate 8j.., rows 16j+8..16j+15 = up 8j..
+    (works for any trailing shape; used for weights and for LoRA B matrices)."""
+    I = g.shape[0]
+    return torch.stack([g.reshape(I // 8, 8, *g.shape[1:]), u.reshape(I // 8, 8, *u.shape[1:])], 1) \
+        .reshape(2 * I, *g.shape[1:]).contiguous()
+
+
+@dataclass
+class LayerWeights:
+    ln1: torch.Tensor
+    ln2: torch.Tensor
+    w_qkv: torch.Tensor
+    w_o: torch.Tensor
+    w_gu: torch.Tensor
+    w_down: torch.Tensor
+    lora: dict = field(default_factory=dict)  # "qkv" | "o" | "gu" | "down" -> LoraStack
+
+
+class PackedLlama:
+    """Device-resident packed weights.  ``weights`` is an HF-named state dict, ``adapters`` a list
+    of dicts keyed like the reference's adapter files
+    (``layers.{L}.self_attn.q_proj.lora_A.weight`` [r,in] / ``lora_B.weight`` [out,r],
+    ``init_peft_weights/lora_weights.py:18-23``), ``scales[i]`` = alpha/r of adapter i.
+    Adapter ``i`` occupies slot ``i`` of every stack."""
+
+    def __init__(self, cfg, weights, adapters=(), scales=(), device="cuda", n_layers=None):
+        self.cfg = dict(cfg)
+        self.device = torch.device(device)
+        c = self.cfg
+        self.H, self.I, self.V = c["hidden_size"], c["intermediate_size"], c["vocab_size"]
+        self.Hq, self.Hkv, self.D = c["num_attention_heads"], c["num_key_value_heads"], c["head_dim"]
+        self.L = c["num_hidden_layers"] if n_layers is None else n_layers
+        self.eps, self.theta = float(c["rms_norm_eps"]), float(c["rope_theta"])
+        if self.I % 8:
+            raise ValueError("intermediate_size must be a multiple of 8")
+        bf = lambda t: t.to(device=self.device, dtype=torch.bfloat16).contiguous()
+        self.embed = bf(weights["model.embed_tokens.weight"])
+        self.norm = bf(weights["model.norm.weight"])
+        self.lm_head = bf(weights["lm_head.weight"])
+        self.n_adapters = len(adapters)
+        ranks = []
+        for ad in adapters:
+            ka = next(k for k in ad if k.endswith("lora_A.weight"))
+            ranks.append(ad[ka].shape[0])
+        self.ranks_host = ranks
+        self.r_max = max(8, -(-max(ranks) // 8) * 8) if ranks else 0
+        if adapters:
+            self.ranks = torch.tensor(ranks, dtype=torch.int32, device=self.device)
+            self.scales = torch.tensor(list(scales), dtype=torch.float32, device=self.device)
+        self.layers = []
+        for l in range(self.L):
+            p = f"model.layers.{l}."
+            w = lambda n: weights[p + n + ".weight"]
+            lw = LayerWeights(
+                ln1=bf(w("input_layernorm")), ln2=bf(w("post_attention_layernorm")),
+                w_qkv=bf(torch.cat([w("self_attn.q_proj"), w("self_attn.k_proj"), w("self_attn.v_proj")], 0)),
+                w_o=bf(w("self_attn.o_proj")),
+                w_gu=bf(interleave_gate_up(w("mlp.gate_proj"), w("mlp.up_proj"))),
+                w_down=bf(w("mlp.down_proj")))
+            if adapters:
+                self._pack_lora(l, lw, adapters)
+            self.layers.append(lw)
+
+    def _pack_lora(self, l, lw, adapters):
+        N, r_max, dev = len(adapters), self.r_max, self.device
+        qd, kvd = self.Hq * self.D, self.Hkv * self.D
+
+        def get(ad, blk, proj):
+            ka = f"layers.{l}.{blk}.{proj}.lora_A.weight"
+            if ka not in ad:
+                return None
+            return ad[ka], ad[ka.replace("lora_A", "lora_B")]
+
+        def build(blk, projs, outs, in_f, interleave=False):
+            if not any(get(ad, blk, p) is not None for ad in adapters for p in projs):
+                return None
+            n_mod = len(projs)
+            A_all = torch.zeros(N, n_mod * r_max, in_f, dtype=torch.bfloat16)
+            B_parts = [torch.zeros(N, o, r_max, dtype=torch.bfloat16) for o in outs]
+            for s, ad in enumerate(adapters):
+                for m, proj in enumerate(projs):
+                    ab = get(ad, blk, proj)
+                    if ab is None:
+                        continue
+                    A, B = ab
+                    r = A.shape[0]
+                    A_all[s, m * r_max:m * r_max + r] = A.to(torch.bfloat16)
+                    B_parts[m][s, :, :r] = B.to(torch.bfloat16)
+            if interleave:
+                B_all = torch.stack([interleave_gate_up(B_parts[0][s], B_parts[1][s]) for s in range(N)])
+            else:
+                B_all = torch.cat(B_parts, 1)
+            offs = tuple(int(x) for x in np.cumsum([0] + list(outs)))
+            return LoraStack(A_all.to(dev), B_all.contiguous().to(dev), self.ranks, self.scales, r_max, n_mod, offs)
+
+        for key, st in (("qkv", build("self_attn", ("q_proj", "k_proj", "v_proj"), (qd, kvd, kvd), self.H)),
+                        ("o", build("self_attn", ("o_proj",), (self.H,), qd)),
+                        ("gu", build("mlp", ("gate_proj", "up_proj"), (self.I, self.I), self.H, True)),
+                        ("down", build("mlp", ("down_proj",), (self.H,), self.I))):
+            if st is not None:
+                lw.lora[key] = st
+
+    def weight_bytes(self):
+        """Bytes of base weights one decode step streams (all layers + final norm + lm_head)."""
+        n = self.norm.numel() + self.lm_head.numel()
+        for lw in self.layers:
+            n += lw.ln1.numel() + lw.ln2.numel() + lw.w_qkv.numel() + lw.w_o.numel() + lw.w_gu.numel() + lw.w_down.numel()
+        return 2 * n
+
+    def lora_bytes_per_adapter(self):
+        n = 0
+        for lw in self.layers:
+            for st in lw.lora.values():
+                n += st.A_all[0].numel() + st.B_all[0].numel()
+        return 2 * n
+
+
+class Engine:
+    """Runs prefill / decode forwards of a :class:`PackedLlama` over a :class:`PagedKVCache`.
+
+    All activations live in buffers sized for ``max_rows`` rows, allocated once, so a forward does
+    no allocation and can be captured in a CUDA graph."""
+
+    def __init__(self, model: PackedLlama, kv: PagedKVCache, max_rows: int):
+        self.m, self.kv, self.max_rows = model, kv, int(max_rows)
+        m, dev, T = model, model.device, int(max_rows)
+        bf = dict(dtype=torch.bfloat16, device=dev)
+        f32 = dict(dtype=torch.float32, device=dev)
+        qkv_out = (m.Hq + 2 * m.Hkv) * m.D
+        self.res = torch.zeros(T, m.H, **f32)
+        self.xn = torch.zeros(T, m.H, **bf)
+        self.qkv = torch.zeros(T, qkv_out, **bf)
+        self.attn = torch.zeros(T, m.Hq * m.D, **bf)
+        self.y = torch.zeros(T, m.H, **bf)
+        self.act = torch.zeros(T, m.I, **bf)
+        self.u = torch.zeros(T, max(3 * m.r_max, 8), **f32)
+        self.logits = torch.zeros(T, m.V, **f32)
+        self.next_tok = torch.zeros(T, dtype=torch.int32, device=dev)
+        self.tokens = torch.zeros(T, dtype=torch.int32, device=dev)
+        self.slots = torch.full((T,), -1, dtype=torch.int32, device=dev)
+        self.row_slot = torch.zeros(T, dtype=torch.int32, device=dev)
+        self.row_pos = torch.zeros(T, dtype=torch.int32, device=dev)
+        self.last_rows = torch.zeros(T, dtype=torch.int32, device=dev)
+        self.xn_last = torch.zeros(T, m.H, **bf)
+        # scratch sized for the largest projection of this model at max_rows
+        lib = ops._lib.lib()
+        need = max(lib.mlora_linear_workspace(T, k, n) for k, n in
+                   ((m.H, qkv_out), (m.Hq * m.D, m.H), (m.H, 2 * m.I), (m.I, m.H), (m.H, m.V)))
+        ops.workspace(need, dev, "linear")
+        ops.workspace(lib.mlora_paged_attention_workspace(T, m.Hq, m.D, 16), dev, "attn")
+        self._graphs = {}
+
+    # ------------------------------------------------------------------------------------------
+    def _proj(self, x, W, stack, slots, out, flags=0):
+        T = x.shape[0]
+        if stack is not None and slots is not None:
+            r_tot = stack.r_max * stack.n_mod
+            u = self.u.view(-1)[: T * r_tot].view(T, r_tot)
+            ops.lora_shrink(x, stack, slots, out=u)
+            return ops.linear(x, W, stack, slots, u=u, flags=flags, out=out)
+        return ops.linear(x, W, flags=flags, out=out)
+
+    def forward(self, T: int, fused_append: bool, use_lora: bool = True, lm_rows=None, n_lm=None):
+        """One pass over the T rows staged in self.tokens / self.slots / self.row_slot /
+        self.row_pos.  Logits (fp32) land in self.logits[:n_lm], greedy tokens in self.next_tok.
+        ``lm_rows`` (device int32 [n_lm]) selects the rows that get logits (prefill: last token of
+        each sequence); None = every row."""
+        m, kv = self.m, self.kv
+        tok, slots = self.tokens[:T], (self.slots[:T] if (use_lora and m.n_adapters) else None)
+        row_slot, row_pos = self.row_slot[:T], self.row_pos[:T]
+        res, xn, qkv, attn, y, act = self.res[:T], self.xn[:T], self.qkv[:T], self.attn[:T], self.y[:T], self.act[:T]
+        ops.embed(tok, m.embed, res=res)
+        delta = None
+        for l, lw in enumerate(m.layers):
+            ops.residual_rmsnorm(delta, res, lw.ln1, m.eps, out=xn)
+            self._proj(xn, lw.w_qkv, lw.lora.get("qkv"), slots, qkv)
+            kp, vp = kv.k_pages(l), kv.v_pages(l)
+            if not fused_append:
+                ops.kv_append_rope(qkv, kp, vp, kv.block_table, row_slot, row_pos, m.Hq, m.Hkv, m.D, kv.page_size,
+                                   m.theta)
+            ops.paged_attention(qkv, kp, vp, kv.block_table, row_slot, row_pos, m.Hq, m.Hkv, m.D, kv.page_size,
+                                m.theta, fused_append, out=attn)
+            self._proj(attn, lw.w_o, lw.lora.get("o"), slots, y)
+            ops.residual_rmsnorm(y, res, lw.ln2, m.eps, out=xn)
+            self._proj(xn, lw.w_gu, lw.lora.get("gu"), slots, act, flags=SILU_MUL)
+            self._proj(act, lw.w_down, lw.lora.get("down"), slots, y)
+            delta = y
+        ops.residual_rmsnorm(delta, res, m.norm, m.eps, out=xn)
+        if lm_rows is not None:
+            xl = ops.embed(lm_rows[:n_lm], xn, out_bf16=self.xn_last[:n_lm])  # row gather
+        else:
+            n_lm, xl = T, xn
+        ops.linear(xl, m.lm_head, flags=OUT_F32, out=self.logits[:n_lm])
+        ops.argmax(self.logits[:n_lm], out=self.next_tok[:n_lm])
+        return self.logits[:n_lm], self.next_tok[:n_lm]
+
+    # ------------------------------------------------------------------------------------------
+    def _stage(self, dst, values, dtype):
+        t = torch.as_tensor(np.asarray(values), dtype=dtype)
+        dst[: t.numel()].copy_(t.pin_memory(), non_blocking=True)
+
+    def prefill(self, seq_ids, prompts, adapter_slots, use_lora=True):
+        """Prefill whole prompts (lists of token ids) of already-added sequences, chunked to
+        max_rows rows per pass.  Returns (logits [n_seq,V] fp32, next tokens [n_seq] int32)."""
+        kv = self.kv
+        out_logits = torch.empty(len(seq_ids), self.m.V, dtype=torch.float32, device=self.m.device)
+        out_tok = torch.empty(len(seq_ids), dtype=torch.int32, device=self.m.device)
+        # rows: (seq index, position) in sequence order, cut into chunks
+        pending = [(i, 0) for i in range(len(seq_ids))]
+        while pending:
+            rows_left = self.max_rows
+            chunk = []  # (seq index, start, n)
+            nxt = []
+            for i, start in pending:
+                n_total = len(prompts[i])
+                if rows_left == 0:
+                    nxt.append((i, start))
+                    continue
+                n = min(rows_left, n_total - start)
+                chunk.append((i, start, n))
+                rows_left -= n
+                if start + n < n_total:
+                    nxt.append((i, start + n))
+            pending = nxt
+            T = sum(n for _, _, n in chunk)
+            toks = np.concatenate([np.asarray(prompts[i][s:s + n], dtype=np.int32) for i, s, n in chunk])
+            slots = np.concatenate([np.full(n, adapter_slots[i], dtype=np.int32) for i, _, n in chunk])
+            row_slot, row_pos = kv.begin_forward([seq_ids[i] for i, _, _ in chunk], [n for _, _, n in chunk])
+            self._stage(self.tokens, toks, torch.int32)
+            self._stage(self.slots, slots, torch.int32)
+            self.row_slot[:T].copy_(row_slot)
+            self.row_pos[:T].copy_(row_pos)
+            ends, fin, a = [], [], 0
+            for i, s, n in chunk:
+                a += n
+                if s + n == len(prompts[i]):
+                    ends.append(a - 1)
+                    fin.append(i)
+            if ends:
+                self._stage(self.last_rows, ends, torch.int32)
+                lg, tk = self.forward(T, False, use_lora, self.last_rows, len(ends))
+                idx = torch.tensor(fin, device=self.m.device)
+                out_logits[idx] = lg
+                out_tok[idx] = tk
+            else:
+                self._stage(self.last_rows, [T - 1], torch.int32)
+                self.forward(T, False, use_lora, self.last_rows, 1)
+            kv.end_forward()
+        return out_logits, out_tok
+
+    def decode(self, seq_ids, tokens, adapter_slots, use_lora=True):
+        """One eager decode step (host builds the row tables, as the reference's executor does)."""
+        B = len(seq_ids)
+        row_slot, row_pos = self.kv.begin_forward(seq_ids, [1] * B)
+        self._stage(self.tokens, tokens, torch.int32)
+        self._stage(self.slots, adapter_slots, torch.int32)
+        self.row_slot[:B].copy_(row_slot)
+        self.row_pos[:B].copy_(row_pos)
+        out = self.forward(B, True, use_lora)
+        self.kv.end_forward()
+        return out
+
+    # -- CUDA-graph decode: the whole step, including position bookkeeping, is one graph ---------------
+    def capture_decode(self, seq_ids, adapter_slots, use_lora=True, reserve_tokens=0, feed_back=True):
+        """Capture a decode step for this batch.  Rows follow ``seq_ids``; each replay consumes
+        self.tokens[:B] (device) and leaves greedy tokens in self.next_tok[:B]."""
+        B, kv = len(seq_ids), self.kv
+        for sid in seq_ids:
+            kv.reserve(sid, kv.length(sid) + reserve_tokens + 1)
+        self._stage(self.row_slot, [kv.slot(s) for s in seq_ids], torch.int32)
+        self._stage(self.slots, adapter_slots, torch.int32)
+        torch.cuda.synchronize()
+        saved = kv.seq_lens.clone()
+
+        def step():
+            ops.kv_begin_decode(self.row_slot[:B], kv.seq_lens, self.row_pos[:B])
+            self.forward(B, True, use_lora)
+            if feed_back:  # the greedy tokens become the next step's input without leaving the device
+                self.tokens[:B].copy_(self.next_tok[:B])
+
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            step()  # warm-up outside capture (lazy module loading, attribute setting)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            step()
+        kv.seq_lens.copy_(saved)  # warm-up advanced the device lengths; capture itself runs nothing
+        torch.cuda.synchronize()
+        return DecodeGraph(self, g, list(seq_ids), B)
+
+
+class DecodeGraph:
+    def __init__(self, engine, graph, seq_ids, B):
+        self.engine, self.graph, self.seq_ids, self.B = engine, graph, seq_ids, B
+
+    def replay(self):
+        """One token for every row: consumes engine.tokens[:B], leaves greedy tokens in
+        engine.next_tok[:B] (and, when captured with feed_back, back in engine.tokens)."""
+        self.graph.replay()
+        self.engine.kv.note_device_decode(self.seq_ids)

@@ -1,0 +1,159 @@
+"""End-to-end parity of the CUDA decoder (prefill + paged decode + per-request LoRA) with the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import load
+from oracle import llama as ollama
+
+pytestmark = pytest.mark.gpu
+
+# bf16 logits against the fp32 oracle: max-abs 2e-2, relative 1e-2 (the stated parity tolerance)
+ATOL, RTOL = 2e-2, 1e-2
+
+
+def _tiny(synth, n_adapters=4, rank=8, targets=None, ranks=None):
+    cfg = synth.llama_config("tiny")
+    w = {k: v.bfloat16() for k, v in synth.base_weights(cfg).items()}
+    ads = synth.lora_adapters(cfg, n_adapters, ranks or rank, targets=targets or synth.ATTN_PROJ)
+    ads = [{k: v.bfloat16() for k, v in a.items()} for a in ads]
+    return cfg, w, ads
+
+
+def _engine(cfg, w, ads, scales, n_seq, max_len, cuda, max_rows=64):
+    model_mod, kv_mod = load("model"), load("kv_cache")
+    pm = model_mod.PackedLlama(cfg, w, ads, scales, device=cuda)
+    kv = kv_mod.PagedKVCache(pm.L, pm.Hkv, pm.D, n_seq, n_seq * max_len, max_len, 16, cuda, max_seq_len=max_len)
+    return pm, kv, model_mod.Engine(pm, kv, max_rows)
+
+
+def _check_logits(got, want):
+    torch.testing.assert_close(got.float().cpu(), want, atol=ATOL, rtol=RTOL)
+
+
+@pytest.mark.parametrize("targets", ["attn", "all"])
+def test_tiny_model_prefill_and_decode_match_oracle(synth, cuda, targets):
+    """The CPU-runnable plumbing case: 2 layers, hidden 256, 4 heads x 64, 4 rank-8 adapters, ids [0,1,2,3]."""
+    tg = synth.ATTN_PROJ if targets == "attn" else synth.ATTN_PROJ + synth.MLP_PROJ
+    cfg, w, ads = _tiny(synth, targets=tg)
+    scales = [2.0] * 4
+    P = synth.prompts(4, 96, cfg["vocab_size"])
+    ids = [0, 1, 2, 3]
+    gen = 12
+    oracle = ollama.OracleLlama(cfg, w, ads, scales)
+    want_tok, want_logits = oracle.greedy([list(p) for p in P], ids, gen)
+
+    pm, kv, eng = _engine(cfg, w, ads, scales, 4, 96 + gen + 1, cuda, max_rows=80)  # forces chunked prefill
+    for s in range(4):
+        kv.add_sequence(s)
+    lg, tok = eng.prefill([0, 1, 2, 3], [list(p) for p in P], ids)
+    _check_logits(lg, want_logits[0])
+    got = [tok.cpu().tolist()]
+    # teacher-forced decode: feed the oracle's tokens, compare logits and argmax per position
+    agree = int((tok.cpu() == want_tok[:, 0]).sum())
+    for step in range(1, gen):
+        lg, tok = eng.decode([0, 1, 2, 3], want_tok[:, step - 1].tolist(), ids)
+        _check_logits(lg, want_logits[step])
+        agree += int((tok.cpu() == want_tok[:, step]).sum())
+        got.append(tok.cpu().tolist())
+    assert agree >= 0.95 * 4 * gen, f"greedy agreement {agree}/{4 * gen}"
+    # block-table gather: the cache holds exactly the rotated keys the oracle computed (bf16-rounded)
+    for s in range(4):
+        K, V = kv.gather(s, 1)
+        torch.testing.assert_close(K.float().cpu(), oracle.k_cache[(s, 1)], atol=3e-2, rtol=2e-2)
+        torch.testing.assert_close(V.float().cpu(), oracle.v_cache[(s, 1)], atol=3e-2, rtol=2e-2)
+        assert K.shape[0] == 96 + gen - 1
+
+
+def test_free_running_graph_decode_matches_eager_and_oracle(synth, cuda):
+    cfg, w, ads = _tiny(synth)
+    scales = [2.0] * 4
+    P = synth.prompts(4, 40, cfg["vocab_size"])
+    ids = [3, 0, 0, 2]
+    gen = 10
+    oracle = ollama.OracleLlama(cfg, w, ads, scales)
+    want_tok, want_logits = oracle.greedy([list(p) for p in P], ids, gen)
+
+    def run(graph):
+        pm, kv, eng = _engine(cfg, w, ads, scales, 4, 64, cuda)
+        for s in range(4):
+            kv.add_sequence(s)
+        _, tok = eng.prefill([0, 1, 2, 3], [list(p) for p in P], ids)
+        out = [tok.cpu().tolist()]
+        if graph:
+            g = eng.capture_decode([0, 1, 2, 3], ids, reserve_tokens=gen)
+            eng.tokens[:4].copy_(tok)
+            for _ in range(gen - 1):
+                g.replay()
+                out.append(eng.next_tok[:4].cpu().tolist())
+            assert [kv.length(s) for s in range(4)] == [40 + gen - 1] * 4
+            assert kv.seq_lens.cpu().tolist() == [40 + gen - 1] * 4
+        else:
+            for _ in range(gen - 1):
+                _, tok = eng.decode([0, 1, 2, 3], out[-1], ids)
+                out.append(tok.cpu().tolist())
+        return torch.tensor(out).t()
+
+    eager, graph = run(False), run(True)
+    assert torch.equal(eager, graph)  # same kernels, same order: bit-identical tokens
+    # Free-running greedy decode of a random-init model diverges for good after one near-tie flips, so
+    # the per-position >= 95 % gate is checked teacher-forced (test above).  Here: wherever a sequence
+    # first departs from the oracle, the oracle's own margin between the two tokens must be inside
+    # the logit tolerance, i.e. the flip is a tie at bf16 precision and not an error.
+    for s in range(4):
+        diff = (eager[s] != want_tok[s]).nonzero()
+        if len(diff):
+            step = int(diff[0])
+            lg = want_logits[step][s]
+            margin = float(lg[want_tok[s, step]] - lg[eager[s, step]])
+            assert 0 <= margin <= 2 * ATOL, f"sequence {s} step {step}: margin {margin}"
+
+
+def test_mixed_ranks_and_rows_without_adapter(synth, cuda):
+    """Ranks cycling 8,16,32,64 in one batch plus rows with no adapter (slot -1)."""
+    cfg, w, ads = _tiny(synth, n_adapters=4, ranks=[8, 16, 32, 64])
+    scales = [2.0, 1.0, 0.5, 0.25]
+    P = synth.prompts(6, 33, cfg["vocab_size"])
+    ids = [0, -1, 3, 2, 1, -1]
+    oracle = ollama.OracleLlama(cfg, w, ads, scales)
+    want_tok, want_logits = oracle.greedy([list(p) for p in P], ids, 4)
+    pm, kv, eng = _engine(cfg, w, ads, scales, 6, 48, cuda, max_rows=256)
+    for s in range(6):
+        kv.add_sequence(s)
+    lg, tok = eng.prefill(list(range(6)), [list(p) for p in P], ids)
+    _check_logits(lg, want_logits[0])
+    for step in range(1, 4):
+        lg, tok = eng.decode(list(range(6)), want_tok[:, step - 1].tolist(), ids)
+        _check_logits(lg, want_logits[step])
+    # no-adapter run of the same engine == oracle without adapters
+    base = ollama.OracleLlama(cfg, w)
+    lg0 = base.prefill(0, list(P[0]), -1)
+    pm2, kv2, eng2 = _engine(cfg, w, [], [], 1, 48, cuda)
+    kv2.add_sequence(0)
+    lgb, _ = eng2.prefill([0], [list(P[0])], [-1])
+    _check_logits(lgb, lg0)
+
+
+def test_ragged_prompts_and_sequence_removal(synth, cuda):
+    cfg, w, ads = _tiny(synth)
+    scales = [2.0] * 4
+    lens = [1, 17, 50, 31]
+    rng = np.random.default_rng(0)
+    P = [rng.integers(0, cfg["vocab_size"], n).tolist() for n in lens]
+    ids = [1, 1, 0, 3]
+    oracle = ollama.OracleLlama(cfg, w, ads, scales)
+    want = [oracle.prefill(s, P[s], ids[s]) for s in range(4)]
+    pm, kv, eng = _engine(cfg, w, ads, scales, 4, 64, cuda)
+    for s in range(4):
+        kv.add_sequence(s)
+    lg, tok = eng.prefill([0, 1, 2, 3], P, ids)
+    _check_logits(lg, torch.cat(want))
+    free_before = len(kv._free)
+    kv.remove_sequence(2)
+    assert len(kv._free) == free_before + 4  # 50 tokens = 4 pages of 16
+    # the live sequences keep decoding correctly after a removal (rows leave the batch between steps)
+    live = [0, 1, 3]
+    t_in = [int(tok[s]) for s in live]
+    wl = oracle.decode(live, t_in, [ids[s] for s in live])
+    lg2, _ = eng.decode(live, t_in, [ids[s] for s in live])
+    _check_logits(lg2, wl)
