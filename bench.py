@@ -1,0 +1,404 @@
+#!/usr/bin/env python
+"""Benchmark: multi-LoRA decode tokens/s, Llama-2-7B shape, 32 requests / 16 rank-16 adapters per GPU.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" = one decode step (one token for each of the 32 requests of a GPU) at context
+512+ tokens, paged KV (block 16), LoRA on q/k/v/o.  Prints ONE JSON line (rank 0).
+N > 1 is launched with torch.distributed.run, one rank per GPU: requests are sharded by
+adapter id, every rank serves 32 requests of its own 16 adapters (weak scaling), no
+collective on the data path; timing is bracketed by a barrier and reduced with MAX.
+
+All inputs are seeded synthetic data of the named shapes (random-init weights, random
+token ids); nothing is read from outside this repository.
+"""
+from __future__ import annotations
+
+import argparse
+import importlib
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+PKG = "tensor-program-optimization-with-auto-batching_b200"
+
+METRIC = "multi-LoRA decode tokens/s (Llama-7B shape, 32 req/16 adapters)"
+N_REQ, N_ADAPTERS, RANK, ALPHA, PROMPT_LEN, PAGE = 32, 16, 16, 32, 512, 16
+FALLBACK_HBM_GBS = 6650.0
+
+
+def load(sub):
+    return importlib.import_module(f"{PKG}.{sub}")
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ----------------------------------------------------------------------------------------------
+def cpu_reference_step(cfg, synth, steps, warmup):
+    """The reference's HF CPU path on this box's cores: seconds per full-model decode step,
+    from a bounded sample (1- and 3-layer truncations at the same shapes, extrapolated)."""
+    import torch
+    from oracle import hf_path
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    ids = synth.adapter_ids_uniform(N_REQ, N_ADAPTERS)
+    r = hf_path.time_decode_sample(
+        cfg, lambda L: synth.base_weights(cfg, n_layers=L),
+        lambda L: synth.lora_adapters(cfg, N_ADAPTERS, RANK, n_layers=L), [ALPHA / RANK] * N_ADAPTERS, ids,
+        PROMPT_LEN, layer_counts=(1, 3), steps=max(1, min(steps, 3)), warmup=max(1, min(warmup, 1)))
+    sample = (f"HF LlamaForCausalLM fp32 + restated GatherBMMLinear, batch {N_REQ}, ctx {PROMPT_LEN}, timed on "
+              f"1- and 3-layer truncations ({r['samples'][0][1]:.3f}s, {r['samples'][-1][1]:.3f}s per step), "
+              f"extrapolated to {cfg['num_hidden_layers']} layers")
+    return N_REQ / r["full_step_s"], cores, sample, r
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    synth = load("synth")
+    cfg = synth.llama_config("llama2-7b")
+    tps, cores, sample, r = cpu_reference_step(cfg, synth, args.steps, args.warmup)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tps, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * r["full_step_s"],
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_gpus):
+    return {
+        "workload": "llama2-7b-shape multi-LoRA decode: 32 layers, hidden 4096, 32x128 heads, inter 11008, "
+                    "vocab 32000; per GPU 32 requests x 16 rank-16 adapters (alpha 32) on q/k/v/o, 512-token "
+                    "prompts, paged KV block 16, greedy decode",
+        "requests_per_gpu": N_REQ, "adapters_per_gpu": N_ADAPTERS, "global_batch": N_REQ * n_gpus,
+        "prompt_len": PROMPT_LEN, "parallelism": f"adapter-sharded replicas x{n_gpus} (no collective)",
+        "l2": "inputs exceed L2 (13.2 GB of weights + ~9 GB of KV streamed per step)",
+    }
+
+
+# ----------------------------------------------------------------------------------------------
+def run_ours(args, rank, world, local_rank):
+    import numpy as np
+    import torch
+
+    synth, model_mod, kv_mod, ops, sharding = (load(m) for m in ("synth", "model", "kv_cache", "ops", "sharding"))
+    load("build").build()
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+
+    def max_over_ranks(x):
+        if dist is None:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    K, W = args.steps, args.warmup
+    cfg = synth.llama_config("llama2-7b")
+    L = args.layers or cfg["num_hidden_layers"]
+    cfg = dict(cfg, num_hidden_layers=L)
+
+    # ---- the global batch and its shard ---------------------------------------------------------------
+    # rank r owns adapters [16r, 16r+16); its 32 requests draw their adapter uniformly from those
+    ids_global = np.concatenate([
+        N_ADAPTERS * r + np.random.default_rng(synth.SEED_IDS + r).integers(0, N_ADAPTERS, N_REQ) for r in range(world)
+    ]).astype(np.int32)
+    owner, per_rank = sharding.shard_requests(ids_global, world, N_ADAPTERS * world, "block")
+    mine = per_rank[rank]
+    held, slot_of = sharding.local_adapter_slots(ids_global, owner, rank)
+    slots = [slot_of[int(ids_global[i])] for i in mine]
+    B = len(mine)
+    prompts_all = synth.prompts(N_REQ * world, PROMPT_LEN, cfg["vocab_size"])
+    prompts = [prompts_all[i].tolist() for i in mine]
+
+    # ---- model ------------------------------------------------------------------------------------------
+    w = synth.base_weights(cfg, dtype=torch.bfloat16, device=dev)
+    ads = synth.lora_adapters(cfg, len(held), RANK, dtype=torch.bfloat16, device=dev)
+    pm = model_mod.PackedLlama(cfg, w, ads, [ALPHA / RANK] * len(held), device=dev)
+    del w, ads
+    torch.cuda.empty_cache()
+    total_steps = 2 * (K + W) + 8
+    max_len = PROMPT_LEN + total_steps + 1
+    kv = kv_mod.PagedKVCache(pm.L, pm.Hkv, pm.D, B, B * max_len, PROMPT_LEN, PAGE, dev, max_seq_len=max_len)
+    eng = model_mod.Engine(pm, kv, max_rows=max(128, B))
+    sids = list(range(B))
+    for s in sids:
+        kv.add_sequence(s)
+
+    # ---- prefill through the product path (untimed set-up) ---------------------------------------------
+    t0 = time.perf_counter()
+    _, first_tok = eng.prefill(sids, prompts, slots)
+    torch.cuda.synchronize()
+    prefill_s = time.perf_counter() - t0
+
+    launches0 = ops.launch_count()
+    graph = eng.capture_decode(sids, slots, reserve_tokens=total_steps)
+    launches_per_step = (ops.launch_count() - launches0) // 2  # one warm-up run + one capture
+    eng.tokens[:B].copy_(first_tok)
+    len0 = kv.seq_lens.clone()
+    len0_host = kv._len_host.copy()
+
+    def rewind():
+        kv.seq_lens.copy_(len0)
+        kv._len_host[:] = len0_host
+        eng.tokens[:B].copy_(first_tok)
+
+    # ---- timed region 1: inputs resident in HBM ------------------------------------------------------
+    for _ in range(W):
+        graph.replay()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for _ in range(K):
+        graph.replay()
+    ev1.record()
+    barrier()
+    ms_total = max_over_ranks(ev0.elapsed_time(ev1))
+    clocks = sampler.stop() if rank == 0 else None
+    ctx_end = PROMPT_LEN + W + K
+    status = int(ops.workspace(4, dev, "linear")[:4].view(torch.int32))
+
+    # ---- timed region 2: end to end through the public step call, host buffers ---------------------------
+    rewind()
+    tok_host = torch.empty(B, dtype=torch.int32).pin_memory()
+    tok_host.copy_(first_tok.cpu())
+    out_host = torch.empty(B, dtype=torch.int32).pin_memory()
+
+    def step_host():
+        eng.tokens[:B].copy_(tok_host, non_blocking=True)   # H2D of this step's inputs
+        graph.replay()
+        out_host.copy_(eng.next_tok[:B], non_blocking=True)  # D2H of this step's result
+        torch.cuda.current_stream().synchronize()
+        tok_host.copy_(out_host)
+
+    for _ in range(W):
+        step_host()
+    barrier()
+    ev0.record()
+    for _ in range(K):
+        step_host()
+    ev1.record()
+    barrier()
+    ms_e2e = max_over_ranks(ev0.elapsed_time(ev1))
+
+    # ---- kernel-only passes for the roofline: the projection launches, then the attention launches -------
+    peak, peak_src = measured_peak()
+    n_uniq = len(set(slots))
+    rewind()
+    roof = kernel_rooflines(eng, pm, kv, B, slots, ops, torch, ctx=PROMPT_LEN + W + K // 2, n_uniq=n_uniq, peak=peak)
+
+    # ---- algorithmic bytes of one whole step (mean context over the timed region) ------------------------
+    ctx_mean = PROMPT_LEN + W + (K - 1) / 2.0
+    kv_tok_bytes = 2 * pm.Hkv * pm.D * 2 * pm.L
+    step_bytes = (pm.weight_bytes() + n_uniq * pm.lora_bytes_per_adapter() + B * ctx_mean * kv_tok_bytes
+                  + B * kv_tok_bytes + B * pm.H * 2)
+    ms_step = ms_total / K
+    tokens_total = B * K
+    if dist is not None:
+        t = torch.tensor([tokens_total], dtype=torch.float64, device=dev)
+        dist.all_reduce(t)
+        tokens_total = float(t.item())
+    value = tokens_total / (ms_total / 1e3)
+    e2e_value = tokens_total / (ms_e2e / 1e3)
+
+    line = None
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic", "config": dict(workload_config(world), layers=L,
+                                                                  ctx_start=PROMPT_LEN + W, ctx_end=ctx_end),
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B,
+                    "ms_per_step": ms_e2e / K,
+                    "call": "Engine decode step: pinned int32 token ids -> device, CUDA-graph step (bucketing "
+                            "state, 32 layers, lm_head, on-device argmax), int32 next tokens -> pinned host"},
+            "gpu_launches": launches_per_step * K, "launches_per_step": launches_per_step,
+            "roofline": roof["linear"], "roofline_attention": roof["attention"],
+            "step_hbm": {"algorithmic_bytes": step_bytes, "achieved_gbs": step_bytes / (ms_step * 1e6),
+                         "peak_gbs": peak, "peak_source": peak_src,
+                         "frac": step_bytes / (ms_step * 1e6) / peak,
+                         "frac_of_8tbs": step_bytes / (ms_step * 1e6) / 8000.0},
+            "clocks": clocks, "prefill_seconds_untimed": prefill_s, "tc_status_word": status,
+        }
+        if world == 1 and not args.no_cpu:
+            tps, cores, sample, _ = cpu_reference_step(synth.llama_config("llama2-7b"), synth, 2, 1)
+            line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample}
+        else:
+            line["cpu_baseline"] = None
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    if line is not None:
+        print(json.dumps(line), flush=True)
+
+
+def kernel_rooflines(eng, pm, kv, B, slots, ops, torch, ctx, n_uniq, peak, reps=5):
+    """CUDA-event timing of (a) every tensor-core projection launch of one decode step and (b) every
+    paged-attention launch of one step, each captured alone in a graph and replayed back to back.
+    The operands cycle through all layers' weights / KV pages (13 GB / ~9 GB), far beyond L2."""
+    T = B
+    sl = eng.slots[:T]
+    x, act, qkv, attn, y = eng.xn[:T], eng.act[:T], eng.qkv[:T], eng.attn[:T], eng.y[:T]
+    peak_src = "measured" if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else "fallback"
+
+    def u_for(st):
+        r_tot = st.r_max * st.n_mod
+        return eng.u.view(-1)[: T * r_tot].view(T, r_tot)
+
+    def lin_bytes(W, st, out_f32=False, silu=False):
+        out_f, in_f = W.shape
+        b = 2 * out_f * in_f + 2 * T * in_f + (4 if out_f32 else 2) * T * (out_f // 2 if silu else out_f)
+        if st is not None:
+            b += n_uniq * 2 * out_f * st.r_max + 4 * T + 4 * T * st.r_max * st.n_mod
+        return b
+
+    def linears():
+        n, total = 0, 0
+        for lw in pm.layers:
+            for W, key, src, dst, fl in ((lw.w_qkv, "qkv", x, qkv, 0), (lw.w_o, "o", attn, y, 0),
+                                         (lw.w_gu, "gu", x, act, ops.SILU_MUL), (lw.w_down, "down", act, y, 0)):
+                st = lw.lora.get(key)
+                if st is not None:
+                    ops.linear(src, W, st, sl, u=u_for(st), flags=fl, out=dst)
+                else:
+                    ops.linear(src, W, flags=fl, out=dst)
+                n += 1
+                total += lin_bytes(W, st, silu=bool(fl & ops.SILU_MUL))
+        ops.linear(x, pm.lm_head, flags=ops.OUT_F32, out=eng.logits[:T])
+        return n + 1, total + lin_bytes(pm.lm_head, None, out_f32=True)
+
+    def attentions():
+        for l in range(pm.L):
+            ops.paged_attention(qkv, kv.k_pages(l), kv.v_pages(l), kv.block_table, eng.row_slot[:T], eng.row_pos[:T],
+                                pm.Hq, pm.Hkv, pm.D, kv.page_size, pm.theta, True, out=attn)
+        return pm.L, pm.L * (T * (ctx + 1) * 2 * pm.Hkv * pm.D * 2 + T * (pm.Hq + 2 * pm.Hkv) * pm.D * 2
+                             + T * pm.Hq * pm.D * 2)
+
+    eng.row_pos[:T].fill_(ctx)
+    out = {}
+    for name, fn, kernel in (("linear", linears, "linear_tc_kernel"), ("attention", attentions, "paged_attn_kernel")):
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            n, total = fn()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        for _ in range(3):
+            g.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(reps):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / reps
+        achieved = total / (ms * 1e6)
+        out[name] = {"bound": "hbm", "kernel": kernel, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "peak_source": peak_src + " copy bandwidth",
+                     "launches": n, "avg_launch_us": 1e3 * ms / n, "algorithmic_bytes_per_launch": total / n,
+                     "traffic": None}
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=0, help="debug: truncate the model (the number is then not a bench value)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+    else:
+        run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -128,3 +128,53 @@ def forward_logits(model, tokens, adapter_ids):
     """Full-sequence logits [B,S,V] (teacher-forced comparison)."""
     model._mlora_ctx.adapter_ids = None if adapter_ids is None else [int(i) for i in adapter_ids]
     return model(input_ids=tokens, use_cache=False).logits.float()
+
+
+@torch.no_grad()
+def time_decode_sample(cfg, weights_fn, adapters_fn, scales, adapter_ids, ctx_len, layer_counts=(1, 3),
+                       steps=2, warmup=1, dtype=torch.float32):
+    """Times batched single-token decode steps of the HF path on this machine's CPU cores.
+
+    A full 7B fp32 model does not fit a per-commit benchmark, so the step is timed on
+    truncated models of ``layer_counts`` layers (same per-layer shapes, KV cache pre-filled
+    with ``ctx_len`` random tokens through ``DynamicCache.update``) and extrapolated linearly
+    in the layer count: t(L) = t_head + L * t_layer.  ``weights_fn(n_layers)`` /
+    ``adapters_fn(n_layers)`` build the truncated state dict / adapter dicts.
+    Returns dict(per_layer_s, head_s, full_step_s, samples=[(L, seconds)]).
+    """
+    import time
+
+    from torch import nn as _nn
+    from transformers import DynamicCache
+
+    B = len(adapter_ids)
+    l_max = max(layer_counts)
+    c = dict(cfg, num_hidden_layers=l_max)
+    model = build_hf_model(c, weights_fn(l_max), adapters_fn(l_max), scales, dtype=dtype)
+    model._mlora_ctx.adapter_ids = [int(i) for i in adapter_ids]
+    all_layers = list(model.model.layers)
+    g = torch.Generator().manual_seed(0)
+    kv_fill = torch.randn(B, c["num_key_value_heads"], ctx_len, c["head_dim"], generator=g).to(dtype)
+    samples = []
+    for L in layer_counts:  # the same model truncated to its first L layers
+        model.model.layers = _nn.ModuleList(all_layers[:L])
+        model.config.num_hidden_layers = L
+        best = None
+        for it in range(warmup + steps):
+            cache = DynamicCache()
+            for l in range(L):  # the step's own torch.cat makes fresh per-layer buffers; the fill is shared
+                cache.update(kv_fill, kv_fill, l)
+            tok = torch.randint(0, c["vocab_size"], (B, 1), generator=g)
+            pos = torch.full((B, 1), ctx_len, dtype=torch.long)
+            t0 = time.perf_counter()
+            out = model(input_ids=tok, past_key_values=cache, position_ids=pos, use_cache=True)
+            out.logits[:, -1].argmax(-1)
+            dt = time.perf_counter() - t0
+            if it >= warmup:
+                best = dt if best is None else min(best, dt)
+        samples.append((L, best))
+    (l0, t0), (l1, t1) = samples[0], samples[-1]
+    per_layer = max((t1 - t0) / (l1 - l0), 0.0) if l1 != l0 else t0 / l0
+    head = max(t0 - l0 * per_layer, 0.0)
+    full = head + cfg["num_hidden_layers"] * per_layer
+    return dict(per_layer_s=per_layer, head_s=head, full_step_s=full, samples=samples)

@@ -1,16 +1,23 @@
 // Weight-streaming projection kernel on the 5th-generation tensor cores (tcgen05 + TMEM), fed by
 // TMA.  y[T,out] = x[T,in] W[out,in]^T with T small (decode) or tiled (prefill): the weight tile
-// is the 128-row M operand, the token rows are the N operand ("swap-AB"), so the 128 x BN fp32
+// is the 128-row M operand, the token rows are the N operand ("swap-AB"), so a 128 x BN fp32
 // accumulator lives in BN TMEM columns and one thread issues all MMAs.
 //
-// CTA = 128 threads: thread 0 of warp 0 drives TMA, thread 0 of warp 1 issues tcgen05.mma, then
-// all four warps run the epilogue (one TMEM lane = one output row per thread).
-// Grid = (row tiles of 128, token tiles of BN, K splits).  With K splits > 1 each CTA writes its
-// fp32 partial tile to scratch and the last CTA to arrive (atomic ticket) sums the partials in
-// split order -- deterministic -- and runs the epilogue (LoRA expand, SiLU*up, store).
+// Persistent, warp-specialised, stream-K:
+//   * one CTA per SM (grid <= SM count), 192 threads: warp 0 = TMA producer (one thread), warp 1 =
+//     MMA issuer (one thread), warps 2..5 = epilogue (one TMEM lane = one output row per thread);
+//   * the iteration space (tile, k-block) -- tiles = row tiles x token tiles, k-blocks of 64 -- is
+//     cut into equal contiguous ranges, one per CTA, so every SM streams the same number of bytes
+//     whatever the shape; a range covers a tail of one tile, whole tiles, and a head of another;
+//   * two TMEM accumulators: the epilogue of one segment overlaps the MMAs of the next, and the
+//     shared-memory ring keeps filling across segment boundaries;
+//   * a tile whose k-blocks are spread over several CTAs is finished by whichever CTA arrives
+//     last on the tile's ticket: every contributor writes its fp32 partial tile to scratch, the last
+//     one sums the partials in CTA order (deterministic) and runs the epilogue (LoRA expand, SiLU*up,
+//     store).  Nobody waits for another CTA.
 //
-// Every wait on an mbarrier is bounded; on expiry the CTA records a code in the status word at
-// the start of the scratch buffer and leaves without touching the output.
+// Every mbarrier wait is bounded; on expiry the CTA records a code in the status word at the start
+// of the scratch buffer, stops issuing work, and leaves after freeing its TMEM.
 #include <cuda.h>
 
 #include "linear.cuh"
@@ -18,22 +25,24 @@
 namespace mlora {
 namespace {
 
-constexpr int BM = 128;        // weight rows per CTA (MMA M)
-constexpr int BK = 64;         // K elements per stage = one 128-byte swizzle span
+constexpr int BM = 128;            // weight rows per tile (MMA M)
+constexpr int BK = 64;             // K elements per stage = one 128-byte swizzle span
+constexpr int kThreads = 192;
+constexpr int kEpiThreads = 128;
 constexpr int kHeaderBytes = 256;  // status word + padding at the start of the scratch buffer
-constexpr int kMaxTickets = 16384; // split-K arrival counters live in a fixed region after the header, so
-                                   // that calls of different shapes sharing one scratch buffer never
-                                   // overlay partial sums on counters
-constexpr uint32_t kSpinLimit = 1u << 24;
+constexpr int kMaxGrid = 256;      // tickets / partial slots are sized for at most this many CTAs
+constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr int kStageUMax = 16 * 1024;  // shrink outputs are staged in shared memory up to this size
 
 struct TcParams {
   LinearArgs a;
-  int k_blocks;       // ceil(in / BK)
-  int kb_per_split;
-  int n_splits;
-  int32_t* status;    // scratch[0]
-  int32_t* tickets;   // [row_tiles * token_tiles]
-  float* partials;    // [row_tiles * token_tiles][n_splits][BN][BM]
+  int k_blocks;    // ceil(in / BK)
+  int row_tiles;   // ceil(out / BM)
+  int n_tiles;     // row_tiles * token tiles
+  int per_cta;     // iterations (tile, k-block) per CTA
+  int32_t* status;  // scratch[0]
+  int32_t* tickets; // [kMaxGrid], indexed by the first contributing CTA of a split tile
+  float* partials;  // [grid][2][BN][BM]
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------------------
@@ -44,6 +53,9 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 // Bounded wait; false = gave up (or another role raised `abort`).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort) {
@@ -58,7 +70,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
         : "r"(addr), "r"(parity)
         : "memory");
     if (ok) return true;
-    if ((i & 1023) == 1023 && *abort) return false;
+    if ((i & 255) == 255 && *abort) return false;
   }
   return false;
 }
@@ -67,6 +79,9 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
       ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
       : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
 __device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols)
@@ -90,6 +105,7 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 // 32 lanes x 32 columns of fp32: register i of lane l = TMEM[lane_base + l][col + i].
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
@@ -140,30 +156,58 @@ __host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
 template <int BN>
 struct Cfg {
   static constexpr int kStageBytes = BM * BK * 2 + BN * BK * 2;
-  static constexpr int kBudget = BN <= 64 ? 100 * 1024 : 200 * 1024;  // <= 64 tokens: two CTAs per SM
-  static constexpr int kStages = (kBudget / kStageBytes) > 8 ? 8 : (kBudget / kStageBytes);
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
-  static constexpr int kTmemCols = BN < 32 ? 32 : BN;
+  static constexpr int kRing = 176 * 1024;
+  static constexpr int kStages = (kRing / kStageBytes) > 10 ? 10 : (kRing / kStageBytes);
+  static constexpr int kAuxBytes = kStageUMax + BN * 4 /*slots*/ + 512 /*barriers*/;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + kAuxBytes;
+  static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;  // two accumulators
+  static constexpr int kChunk = BN < 32 ? BN : 32;              // columns per TMEM load
 };
 
+// One CTA's share of the iteration space and the walk over its segments.
+struct Range {
+  int it0, it1;
+};
+struct Segment {
+  int tile, kb0, kb1;
+};
+__device__ __forceinline__ Range cta_range(const TcParams& p, int cta) {
+  const long long total = (long long)p.n_tiles * p.k_blocks;
+  long long a = (long long)cta * p.per_cta, b = a + p.per_cta;
+  if (a > total) a = total;
+  if (b > total) b = total;
+  return Range{(int)a, (int)b};
+}
+__device__ __forceinline__ Segment next_segment(const TcParams& p, int& it, int it1) {
+  Segment s;
+  s.tile = it / p.k_blocks;
+  s.kb0 = it - s.tile * p.k_blocks;
+  s.kb1 = min(p.k_blocks, s.kb0 + (it1 - it));
+  it += s.kb1 - s.kb0;
+  return s;
+}
+
 template <int BN>
-__global__ void __launch_bounds__(128) linear_tc_kernel(const __grid_constant__ CUtensorMap map_w,
-                                                        const __grid_constant__ CUtensorMap map_x, TcParams p) {
+__global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                                const __grid_constant__ CUtensorMap map_x,
+                                                                TcParams p) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(tiles + C::kStages * C::kStageBytes);
+  uint8_t* aux = tiles + C::kStages * C::kStageBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(aux);
   uint64_t* empty_bar = full_bar + C::kStages;
-  uint64_t* accum_bar = empty_bar + C::kStages;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
+  uint64_t* acc_full = empty_bar + C::kStages;   // [2]
+  uint64_t* acc_empty = acc_full + 2;            // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  int* s_slots = reinterpret_cast<int*>(aux + 512);                  // [BN]
+  float* s_u = reinterpret_cast<float*>(aux + 512 + BN * 4);        // [BN * r_tot] when it fits
   __shared__ int s_abort;
   __shared__ int s_last;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int row_tile = blockIdx.x, tok_tile = blockIdx.y, split = blockIdx.z;
-  const int kb0 = split * p.kb_per_split;
-  const int kb1 = min(kb0 + p.kb_per_split, p.k_blocks);
-  const int n_kb = kb1 - kb0;  // >= 1 by construction of the grid
+  const Range rg = cta_range(p, blockIdx.x);
+  if (rg.it0 >= rg.it1) return;  // whole CTA idle (uniform)
 
   if (tid == 0) {
     s_abort = 0;
@@ -171,8 +215,13 @@ __global__ void __launch_bounds__(128) linear_tc_kernel(const __grid_constant__ 
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
-    mbar_init(accum_bar, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);  // one arrival per epilogue warp
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    tma_prefetch_desc(&map_w);
+    tma_prefetch_desc(&map_x);
   }
   if (warp == 1) tmem_alloc(tmem_slot, C::kTmemCols);
   tc_fence_before();
@@ -180,131 +229,226 @@ __global__ void __launch_bounds__(128) linear_tc_kernel(const __grid_constant__ 
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 0 && lane == 0) {
+  if (warp == 0) {
     // ---- TMA producer ------------------------------------------------------------------------------
-    for (int i = 0; i < n_kb; ++i) {
-      const int s = i % C::kStages, round = i / C::kStages;
-      if (!mbar_wait(&empty_bar[s], (round & 1) ^ 1, &s_abort)) {
-        s_abort = 1;
-        atomicOr(p.status, 1);
-        break;
-      }
-      uint8_t* st = tiles + s * C::kStageBytes;
-      mbar_expect_tx(&full_bar[s], C::kStageBytes);
-      tma_load_2d(st, &map_w, (kb0 + i) * BK, row_tile * BM, &full_bar[s]);
-      tma_load_2d(st + BM * BK * 2, &map_x, (kb0 + i) * BK, tok_tile * BN, &full_bar[s]);
-    }
-  } else if (warp == 1 && lane == 0) {
-    // ---- MMA issuer --------------------------------------------------------------------------------
-    constexpr uint32_t idesc = make_idesc(BM, BN < 16 ? 16 : BN);
-    bool ok = true;
-    for (int i = 0; i < n_kb && ok; ++i) {
-      const int s = i % C::kStages, round = i / C::kStages;
-      if (!mbar_wait(&full_bar[s], round & 1, &s_abort)) {
-        s_abort = 1;
-        atomicOr(p.status, 2);
-        ok = false;
-        break;
-      }
-      tc_fence_after();
-      const uint32_t wa = smem_u32(tiles + s * C::kStageBytes);
-      const uint64_t adesc = make_smem_desc(wa);
-      const uint64_t bdesc = make_smem_desc(wa + BM * BK * 2);
-#pragma unroll
-      for (int k = 0; k < BK / 16; ++k) {
-        // advancing 16 elements (32 bytes) along K inside the swizzle span = +2 in the address field
-        umma_bf16(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (i | k) != 0);
-      }
-      umma_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
-    }
-    if (ok) umma_commit(accum_bar);
-  }
-
-  // ---- epilogue: all 128 threads -----------------------------------------------------------------------
-  __syncwarp();
-  bool have_acc = mbar_wait(accum_bar, 0, &s_abort);
-  if (!have_acc && !s_abort) {
-    s_abort = 1;
-    atomicOr(p.status, 4);
-  }
-  tc_fence_after();
-  __syncthreads();
-  const bool aborted = s_abort != 0;
-
-  const LinearArgs& a = p.a;
-  const int row = row_tile * BM + tid;        // output feature of this thread
-  const int t0 = tok_tile * BN;
-  const uint32_t t_lane = tmem_base + ((uint32_t)(warp * 32) << 16);
-  const bool silu = (a.flags & MLORA_SILU_MUL) != 0;
-
-  auto finish = [&](const float (&v)[32], int c0, int n) {
-    // v[i] = base projection of (token t0+c0+i, feature row)
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      if (i < n) {
-        const int t = t0 + c0 + i;
-        const bool live = t < a.T && row < a.out;
-        float val = v[i];
-        if (live) val += lora_expand(a, t, row);
-        if (silu) {
-          const float other = __shfl_xor_sync(0xffffffffu, val, 8);
-          if (live && (tid & 8) == 0) store_out(a, t, (row >> 4) * 8 + (row & 7), silu_mul(val, other));
-        } else if (live) {
-          store_out(a, t, row, val);
-        }
-      }
-    }
-  };
-
-  if (!aborted) {
-    if (p.n_splits == 1) {
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        float v[32];
-        if (BN >= 32) tmem_ld32(t_lane + c0, v); else tmem_ld16(t_lane + c0, v);
-        finish(v, c0, BN < 32 ? BN : 32);
-      }
-    } else {
-      const size_t tile_id = (size_t)tok_tile * gridDim.x + row_tile;
-      float* part = p.partials + (tile_id * p.n_splits + split) * (size_t)(BN * BM);
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        float v[32];
-        if (BN >= 32) tmem_ld32(t_lane + c0, v); else tmem_ld16(t_lane + c0, v);
-#pragma unroll
-        for (int i = 0; i < (BN < 32 ? BN : 32); ++i) part[(size_t)(c0 + i) * BM + tid] = v[i];
-      }
-      __threadfence();
-      __syncthreads();
-      if (tid == 0) {
-        const int ticket = atomicAdd(&p.tickets[tile_id], 1);
-        s_last = ticket == p.n_splits - 1;
-        if (s_last) p.tickets[tile_id] = 0;  // ready for the next call
-      }
-      __syncthreads();
-      if (s_last) {
-        __threadfence();
-        const float* base = p.partials + tile_id * p.n_splits * (size_t)(BN * BM);
-#pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-          float v[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = 0.f;
-          for (int s = 0; s < p.n_splits; ++s) {
-            const float* ps = base + (size_t)s * (BN * BM);
-#pragma unroll
-            for (int i = 0; i < (BN < 32 ? BN : 32); ++i) v[i] += __ldcg(ps + (size_t)(c0 + i) * BM + tid);
+    if (lane == 0) {
+      int it = rg.it0, n = 0;
+      bool ok = true;
+      while (it < rg.it1 && ok) {
+        const Segment sg = next_segment(p, it, rg.it1);
+        const int row_tile = sg.tile % p.row_tiles, tok_tile = sg.tile / p.row_tiles;
+        for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++n) {
+          const int s = n % C::kStages, round = n / C::kStages;
+          if (!mbar_wait(&empty_bar[s], (round & 1) ^ 1, &s_abort)) {
+            s_abort = 1;
+            atomicOr(p.status, 1);
+            ok = false;
+            break;
           }
-          finish(v, c0, BN < 32 ? BN : 32);
+          uint8_t* st = tiles + s * C::kStageBytes;
+          mbar_expect_tx(&full_bar[s], C::kStageBytes);
+          tma_load_2d(st, &map_w, kb * BK, row_tile * BM, &full_bar[s]);
+          tma_load_2d(st + BM * BK * 2, &map_x, kb * BK, tok_tile * BN, &full_bar[s]);
         }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer --------------------------------------------------------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(BM, BN);
+      int it = rg.it0, n = 0, j = 0;
+      bool ok = true;
+      while (it < rg.it1 && ok) {
+        const Segment sg = next_segment(p, it, rg.it1);
+        const int buf = j & 1;
+        if (!mbar_wait(&acc_empty[buf], ((j >> 1) & 1) ^ 1, &s_abort)) {
+          s_abort = 1;
+          atomicOr(p.status, 8);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++n) {
+          const int s = n % C::kStages, round = n / C::kStages;
+          if (!mbar_wait(&full_bar[s], round & 1, &s_abort)) {
+            s_abort = 1;
+            atomicOr(p.status, 2);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t wa = smem_u32(tiles + s * C::kStageBytes);
+          const uint64_t adesc = make_smem_desc(wa);
+          const uint64_t bdesc = make_smem_desc(wa + BM * BK * 2);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            // advancing 16 elements (32 bytes) along K inside the swizzle span = +2 in the address field
+            umma_bf16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > sg.kb0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
+        }
+        if (ok) umma_commit(&acc_full[buf]);
+        ++j;
       }
     }
   } else {
+    // ---- epilogue warps: TMEM lane quarter = warp % 4 -------------------------------------------------
+    const LinearArgs& a = p.a;
+    const int q = warp & 3;
+    const int etid = q * 32 + lane;           // 0..127 = row inside the tile
+    const bool silu = (a.flags & MLORA_SILU_MUL) != 0;
+    const int r_tot = a.r_max * a.n_mod;
+    const bool stage_u = a.u != nullptr && (size_t)BN * r_tot * sizeof(float) <= (size_t)kStageUMax;
+    int staged_tok_tile = -1;
+    int it = rg.it0, j = 0;
+    bool ok = true;
+
+    while (it < rg.it1 && ok) {
+      const Segment sg = next_segment(p, it, rg.it1);
+      const int row_tile = sg.tile % p.row_tiles, tok_tile = sg.tile / p.row_tiles;
+      const int row = row_tile * BM + etid;
+      const int t0 = tok_tile * BN;
+      const int buf = j & 1;
+      const bool full_seg = sg.kb0 == 0 && sg.kb1 == p.k_blocks;
+
+      // per-token LoRA operands of this token tile -> shared memory (once per token tile)
+      if (a.u != nullptr && staged_tok_tile != tok_tile) {
+        epi_bar_sync();  // previous users of the staging area are done
+        for (int i = etid; i < BN; i += kEpiThreads) s_slots[i] = (t0 + i < a.T) ? a.slots[t0 + i] : -1;
+        if (stage_u) {
+          const int n_valid = min(BN, a.T - t0) * r_tot;
+          for (int i = etid; i < n_valid; i += kEpiThreads) s_u[i] = a.u[(size_t)t0 * r_tot + i];
+        }
+        epi_bar_sync();
+        staged_tok_tile = tok_tile;
+      }
+
+      // Adds the LoRA expand, applies SiLU*up, stores.  v[i] = projection of (token t0+c0+i, row).
+      auto finish = [&](float (&v)[32], int c0) {
+        if (a.u != nullptr && row < a.out) {
+          const int m = module_of(a, row);
+          int cur = -1, r = 0;
+          float sc = 0.f;
+          uint4 bq[8];
+#pragma unroll
+          for (int i = 0; i < C::kChunk; ++i) {
+            const int s = s_slots[c0 + i];
+            if (s < 0) continue;
+            if (s != cur) {  // rows of one adapter are usually adjacent (ordered batches): reuse B[s, row, :]
+              cur = s;
+              r = a.ranks[s];
+              sc = a.scales[s];
+              const bf16* b = a.B_all + ((size_t)s * a.out + row) * a.r_max;
+#pragma unroll
+              for (int g = 0; g < 8; ++g)
+                if (g * 8 < r) bq[g] = ld_cached(b + g * 8);
+            }
+            const float* ur = stage_u ? s_u + (c0 + i) * r_tot + m * a.r_max
+                                      : a.u + (size_t)(t0 + c0 + i) * r_tot + m * a.r_max;
+            float acc = 0.f;
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              if (g * 8 < r) {
+                float bf[8];
+                unpack8(bq[g], bf);
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                  if (g * 8 + e < r) acc = fmaf(ur[g * 8 + e], bf[e], acc);
+              }
+            }
+            v[i] = fmaf(sc, acc, v[i]);
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < C::kChunk; ++i) {
+          const int t = t0 + c0 + i;
+          const bool live = t < a.T && row < a.out;
+          if (silu) {
+            const float other = __shfl_xor_sync(0xffffffffu, v[i], 8);
+            if (live && (etid & 8) == 0) store_out(a, t, (row >> 4) * 8 + (row & 7), silu_mul(v[i], other));
+          } else if (live) {
+            store_out(a, t, row, v[i]);
+          }
+        }
+      };
+
+      if (!mbar_wait(&acc_full[buf], (j >> 1) & 1, &s_abort)) {
+        if (!s_abort) {
+          s_abort = 1;
+          atomicOr(p.status, 4);
+        }
+        break;
+      }
+      tc_fence_after();
+      const uint32_t t_addr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
+
+      if (full_seg) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          float v[32];
+          if (BN >= 32) tmem_ld32(t_addr + c0, v); else tmem_ld16(t_addr + c0, v);
+          if (c0 + 32 >= BN) {  // accumulator fully read: hand it back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+          }
+          finish(v, c0);
+        }
+      } else {
+        // split tile: this CTA's slot 0 if its range starts inside the tile, else slot 1
+        const bool starts_here = rg.it0 >= sg.tile * p.k_blocks;
+        float* part = p.partials + ((size_t)blockIdx.x * 2 + (starts_here ? 0 : 1)) * (size_t)(BN * BM);
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          float v[32];
+          if (BN >= 32) tmem_ld32(t_addr + c0, v); else tmem_ld16(t_addr + c0, v);
+#pragma unroll
+          for (int i = 0; i < C::kChunk; ++i) part[(size_t)(c0 + i) * BM + etid] = v[i];
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        // contributors of this tile: the CTAs whose ranges meet [tile*k_blocks, (tile+1)*k_blocks)
+        const long long ts = (long long)sg.tile * p.k_blocks, te = ts + p.k_blocks;
+        const int c_first = (int)(ts / p.per_cta), c_last = (int)((te - 1) / p.per_cta);
+        __threadfence();
+        epi_bar_sync();
+        if (etid == 0) {
+          const int ticket = atomicAdd(&p.tickets[c_first], 1);
+          s_last = ticket == c_last - c_first;
+          if (s_last) p.tickets[c_first] = 0;  // ready for the next call
+        }
+        epi_bar_sync();
+        if (s_last) {
+          __threadfence();
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 32) {
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = 0.f;
+            for (int cc = c_first; cc <= c_last; ++cc) {
+              const bool cc_starts_here = (long long)cc * p.per_cta >= ts;
+              const float* ps = p.partials + ((size_t)cc * 2 + (cc_starts_here ? 0 : 1)) * (size_t)(BN * BM);
+#pragma unroll
+              for (int i = 0; i < C::kChunk; ++i) v[i] += __ldcg(ps + (size_t)(c0 + i) * BM + etid);
+            }
+            finish(v, c0);
+          }
+        }
+        epi_bar_sync();  // s_last is reused by the next split segment
+      }
+      ++j;
+    }
+  }
+
+  // ---- teardown -----------------------------------------------------------------------------------------
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (s_abort) {
     // give copies that may still be in flight a bounded time to land before the CTA exits
     for (int i = 0; i < 64; ++i) __nanosleep(1000);
   }
-  tc_fence_before();
-  __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, C::kTmemCols);
 }
 
@@ -342,8 +486,18 @@ int make_map(CUtensorMap* m, const void* ptr, int rows, int cols, int64_t ld, in
 
 int pick_bn(int T) { return T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : 128; }
 
+int sm_count() {
+  static int n = [] {
+    int dev = 0, v = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) return 148;
+    return v > kMaxGrid ? kMaxGrid : v;
+  }();
+  return n;
+}
+
 struct Plan {
-  int bn, row_tiles, tok_tiles, k_blocks, n_splits, kb_per_split;
+  int bn, row_tiles, tok_tiles, k_blocks, grid, per_cta;
 };
 
 Plan make_plan(int T, int in, int out) {
@@ -352,15 +506,13 @@ Plan make_plan(int T, int in, int out) {
   pl.row_tiles = (out + BM - 1) / BM;
   pl.tok_tiles = (T + pl.bn - 1) / pl.bn;
   pl.k_blocks = (in + BK - 1) / BK;
-  // enough CTAs to put two on every SM, but at least 4 K blocks (32 KB of weights) per CTA
-  const int base = pl.row_tiles * pl.tok_tiles;
-  int s = (2 * 148 + base - 1) / base;
-  const int max_s = pl.k_blocks / 4 > 0 ? pl.k_blocks / 4 : 1;
-  if (s > max_s) s = max_s;
-  if (s > 16) s = 16;
-  if (s < 1 || base > kMaxTickets) s = 1;
-  pl.kb_per_split = (pl.k_blocks + s - 1) / s;
-  pl.n_splits = (pl.k_blocks + pl.kb_per_split - 1) / pl.kb_per_split;  // no empty split
+  const long long total = (long long)pl.row_tiles * pl.tok_tiles * pl.k_blocks;
+  long long grid = sm_count();
+  // at least 4 k-blocks (64 KB of weights) per CTA, so tiny problems do not pay for 148 partial tiles
+  if (grid > (total + 3) / 4) grid = (total + 3) / 4;
+  if (grid < 1) grid = 1;
+  pl.per_cta = (int)((total + grid - 1) / grid);
+  pl.grid = (int)((total + pl.per_cta - 1) / pl.per_cta);
   return pl;
 }
 
@@ -375,11 +527,12 @@ int launch(const LinearArgs& a, const Plan& pl, void* work, cudaStream_t st) {
   TcParams p;
   p.a = a;
   p.k_blocks = pl.k_blocks;
-  p.kb_per_split = pl.kb_per_split;
-  p.n_splits = pl.n_splits;
+  p.row_tiles = pl.row_tiles;
+  p.n_tiles = pl.row_tiles * pl.tok_tiles;
+  p.per_cta = pl.per_cta;
   p.status = (int32_t*)work;
   p.tickets = (int32_t*)((uint8_t*)work + kHeaderBytes);
-  p.partials = (float*)((uint8_t*)work + kHeaderBytes + kMaxTickets * 4);
+  p.partials = (float*)((uint8_t*)work + kHeaderBytes + kMaxGrid * 4);
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(linear_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -387,8 +540,7 @@ int launch(const LinearArgs& a, const Plan& pl, void* work, cudaStream_t st) {
     if (e != cudaSuccess) return fail(MLORA_ECUDA, "linear: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     attr_set = true;
   }
-  dim3 grid(pl.row_tiles, pl.tok_tiles, pl.n_splits);
-  linear_tc_kernel<BN><<<grid, 128, C::kSmemBytes, st>>>(mw, mx, p);
+  linear_tc_kernel<BN><<<pl.grid, kThreads, C::kSmemBytes, st>>>(mw, mx, p);
   count_launch();
   MLORA_CHECK_LAUNCH("linear_tc_kernel");
   return MLORA_OK;
@@ -399,17 +551,14 @@ int launch(const LinearArgs& a, const Plan& pl, void* work, cudaStream_t st) {
 bool linear_tc_supported(const LinearArgs& a) {
   // TMA needs 16-byte aligned bases and row pitches; everything else (ragged K, out, T) is handled by
   // zero-filled out-of-bounds boxes and masked stores.
-  return aligned16(a.x) && aligned16(a.W) && (a.ldx * 2) % 16 == 0 && (a.in * 2) % 16 == 0 &&
-         (size_t)((a.out + BM - 1) / BM) <= 2147483647u && ((a.T + 127) / 128) <= 65535;
+  const long long tiles = (long long)((a.out + BM - 1) / BM) * ((a.T + 127) / 128);
+  return aligned16(a.x) && aligned16(a.W) && (a.ldx * 2) % 16 == 0 && (a.in * 2) % 16 == 0 && a.r_max <= 64 &&
+         tiles * ((a.in + BK - 1) / BK) < 2000000000ll;
 }
 
 size_t linear_tc_workspace(int T, int in, int out) {
-  if (T <= 0 || in <= 0 || out <= 0) return kHeaderBytes + kMaxTickets * 4;
-  Plan pl = make_plan(T, in, out);
-  const size_t n_tiles = (size_t)pl.row_tiles * pl.tok_tiles;
-  size_t bytes = kHeaderBytes + kMaxTickets * 4;
-  if (pl.n_splits > 1) bytes += n_tiles * pl.n_splits * (size_t)pl.bn * BM * sizeof(float);
-  return bytes;
+  const int bn = T > 0 ? pick_bn(T) : 16;
+  return kHeaderBytes + kMaxGrid * 4 + (size_t)kMaxGrid * 2 * bn * BM * sizeof(float);
 }
 
 int launch_linear_tc(const LinearArgs& a, void* work, size_t work_bytes, cudaStream_t st) {

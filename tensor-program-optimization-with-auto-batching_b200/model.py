@@ -110,8 +110,8 @@ class PackedLlama:
             if not any(get(ad, blk, p) is not None for ad in adapters for p in projs):
                 return None
             n_mod = len(projs)
-            A_all = torch.zeros(N, n_mod * r_max, in_f, dtype=torch.bfloat16)
-            B_parts = [torch.zeros(N, o, r_max, dtype=torch.bfloat16) for o in outs]
+            A_all = torch.zeros(N, n_mod * r_max, in_f, dtype=torch.bfloat16, device=dev)
+            B_parts = [torch.zeros(N, o, r_max, dtype=torch.bfloat16, device=dev) for o in outs]
             for s, ad in enumerate(adapters):
                 for m, proj in enumerate(projs):
                     ab = get(ad, blk, proj)
@@ -119,14 +119,14 @@ class PackedLlama:
                         continue
                     A, B = ab
                     r = A.shape[0]
-                    A_all[s, m * r_max:m * r_max + r] = A.to(torch.bfloat16)
-                    B_parts[m][s, :, :r] = B.to(torch.bfloat16)
+                    A_all[s, m * r_max:m * r_max + r] = A.to(device=dev, dtype=torch.bfloat16)
+                    B_parts[m][s, :, :r] = B.to(device=dev, dtype=torch.bfloat16)
             if interleave:
                 B_all = torch.stack([interleave_gate_up(B_parts[0][s], B_parts[1][s]) for s in range(N)])
             else:
                 B_all = torch.cat(B_parts, 1)
             offs = tuple(int(x) for x in np.cumsum([0] + list(outs)))
-            return LoraStack(A_all.to(dev), B_all.contiguous().to(dev), self.ranks, self.scales, r_max, n_mod, offs)
+            return LoraStack(A_all, B_all.contiguous(), self.ranks, self.scales, r_max, n_mod, offs)
 
         for key, st in (("qkv", build("self_attn", ("q_proj", "k_proj", "v_proj"), (qd, kvd, kvd), self.H)),
                         ("o", build("self_attn", ("o_proj",), (self.H,), qd)),
