@@ -71,23 +71,26 @@ int mlora_bucket_sort(const int32_t* d_tids, const int32_t* d_wids, int32_t n, i
  * GatherBMMLinear.forward (huggingface/custom_peft/lora_gatherbmm_linear_layer.py:16-19).
  *   d_x [T, in] bf16 (row stride ldx elements); d_A_all [N, n_mod*r_max, in] bf16;
  *   d_ranks [N] int32 (rank of each adapter slot, <= r_max; rows >= rank are never read);
- *   d_slots [T] int32 (adapter slot of each row, < 0 = none -> u row is zero);
+ *   d_slots [T] int32 (adapter slot of each row; < 0 or >= n_adapters = none -> u row is zero);
  *   d_u [T, n_mod*r_max] float32.  n_mod modules share the input (q,k,v or gate,up). */
 int mlora_lora_shrink(const void* d_x, int64_t ldx, const void* d_A_all, const int32_t* d_ranks,
-                      const int32_t* d_slots, int32_t T, int32_t in, int32_t r_max, int32_t n_mod,
-                      float* d_u, void* stream);
+                      const int32_t* d_slots, int32_t n_adapters, int32_t T, int32_t in, int32_t r_max,
+                      int32_t n_mod, float* d_u, void* stream);
 
 /* ---- (a)+(b) base projection with the LoRA expand fused into the output write ----------------
  *   y[t, o] = sum_k x[t,k] W[o,k]  +  scale[s] * sum_j u[t, m(o)*r_max + j] * B_all[s, o, j]
  * with s = slot[t] (skipped when s < 0 or d_u == NULL) and m(o) the module that owns output row o
- * (mod_offsets[m] <= o < mod_offsets[m+1]; with MLORA_SILU_MUL: m = (o >> 3) & 1).
+ * (mod_offsets[m] <= o < mod_offsets[m+1]).  With MLORA_SILU_MUL (n_mod = 2: gate, up) B_all is
+ * [N, out, 2*r_max]: a gate row holds its B in columns [0, r_max) and zeros in [r_max, 2*r_max), an up
+ * row the other way round, so that one dot product against u = [u_gate | u_up] serves both.
+ * Padding of A_all / B_all beyond an adapter's rank must be zero.
  * Stands in for base_layer(x) + bmm(bmm(x, A), B*scaling)
  * (huggingface/custom_peft/lora_gatherbmm_linear_layer.py:15-20) and for nn.Linear followed by
  * "q += q_ft_proj(h, wids)" (tvm/llama_auto_batcher/compile_tvm.py:126-134, 142-155; the
  * write_tensor_part scatter of tvm/custom/write_tensor_part.py is subsumed because rows are
  * addressed directly).
  *   d_x [T,in] bf16; d_W [out,in] bf16; d_y [T, out or out/2] bf16 (or f32 with MLORA_OUT_F32),
- *   row stride ldy elements; d_B_all [N, out, r_max] bf16; d_scales [N] float32;
+ *   row stride ldy elements; d_B_all [N, out, r_max] bf16, r_max a multiple of 8; d_scales [N] float32;
  *   h_mod_offsets: HOST array of n_mod+1 ints (NULL when n_mod == 1), n_mod <= 8.
  *   d_work / work_bytes: scratch for split-K partial sums of the tensor-core kernel,
  *   mlora_linear_workspace(T, in, out) bytes (may be NULL/0: then the CUDA-core kernel runs).  The
@@ -99,8 +102,8 @@ size_t mlora_linear_workspace(int32_t T, int32_t in, int32_t out);
 int mlora_linear(const void* d_x, int64_t ldx, const void* d_W, void* d_y, int64_t ldy, int32_t T,
                  int32_t in, int32_t out, const float* d_u, const void* d_B_all,
                  const int32_t* d_ranks, const float* d_scales, const int32_t* d_slots,
-                 int32_t r_max, int32_t n_mod, const int32_t* h_mod_offsets, int32_t flags,
-                 void* d_work, size_t work_bytes, void* stream);
+                 int32_t n_adapters, int32_t r_max, int32_t n_mod, const int32_t* h_mod_offsets,
+                 int32_t flags, void* d_work, size_t work_bytes, void* stream);
 
 /* ---- (b) fused residual add + RMSNorm ----------------------------------------------------------
  *   res[t,:] += delta[t,:] (skipped when d_delta == NULL);  out[t,:] = res * rsqrt(mean(res^2)+eps) * w

@@ -20,9 +20,9 @@ PROTOTYPES = {
     "mlora_launch_count": (C.c_uint64, []),
     "mlora_bucket_sort_workspace": (_sz, [_i32, _i32, _i32]),
     "mlora_bucket_sort": (C.c_int, [_vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
-    "mlora_lora_shrink": (C.c_int, [_vp, _i64, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp]),
+    "mlora_lora_shrink": (C.c_int, [_vp, _i64, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp]),
     "mlora_linear_workspace": (_sz, [_i32, _i32, _i32]),
-    "mlora_linear": (C.c_int, [_vp, _i64, _vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32,
+    "mlora_linear": (C.c_int, [_vp, _i64, _vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32,
                                C.POINTER(_i32), _i32, _vp, _sz, _vp]),
     "mlora_residual_rmsnorm": (C.c_int, [_vp, _vp, _vp, _f32, _vp, _i32, _i32, _vp]),
     "mlora_embed": (C.c_int, [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp]),

@@ -10,7 +10,8 @@ extern "C" size_t mlora_linear_workspace(int32_t T, int32_t in, int32_t out) {
 extern "C" int mlora_linear(const void* d_x, int64_t ldx, const void* d_W, void* d_y, int64_t ldy, int32_t T,
                             int32_t in, int32_t out, const float* d_u, const void* d_B_all,
                             const int32_t* d_ranks, const float* d_scales, const int32_t* d_slots,
-                            int32_t r_max, int32_t n_mod, const int32_t* h_mod_offsets, int32_t flags,
+                            int32_t n_adapters, int32_t r_max, int32_t n_mod, const int32_t* h_mod_offsets,
+                            int32_t flags,
                             void* d_work, size_t work_bytes, void* stream) {
   MLORA_REQUIRE(T >= 0 && in > 0 && out > 0, "linear: bad sizes T=%d in=%d out=%d", T, in, out);
   MLORA_REQUIRE(in % 8 == 0 && ldx % 8 == 0, "linear: in and ldx must be multiples of 8 (in=%d ldx=%lld)", in,
@@ -32,9 +33,11 @@ extern "C" int mlora_linear(const void* d_x, int64_t ldx, const void* d_W, void*
   a.r_max = 0;
   if (d_u) {
     MLORA_REQUIRE(d_B_all && d_ranks && d_scales && d_slots, "linear: LoRA operands missing");
-    MLORA_REQUIRE(r_max > 0 && n_mod >= 1 && n_mod <= 8, "linear: bad r_max=%d / n_mod=%d", r_max, n_mod);
+    MLORA_REQUIRE(r_max > 0 && n_mod >= 1 && n_mod <= 8 && n_adapters > 0, "linear: bad r_max=%d / n_mod=%d / n_adapters=%d",
+                  r_max, n_mod, n_adapters);
     MLORA_REQUIRE(aligned16(d_B_all), "linear: B_all must be 16-byte aligned");
     if (flags & MLORA_SILU_MUL) MLORA_REQUIRE(n_mod == 2, "linear: SILU_MUL implies n_mod == 2");
+    MLORA_REQUIRE(r_max % 8 == 0, "linear: r_max must be a multiple of 8 (r_max=%d)", r_max);
     a.u = d_u;
     a.B_all = (const bf16*)d_B_all;
     a.ranks = d_ranks;
@@ -42,7 +45,16 @@ extern "C" int mlora_linear(const void* d_x, int64_t ldx, const void* d_W, void*
     a.slots = d_slots;
     a.r_max = r_max;
     a.n_mod = n_mod;
-    if (n_mod > 1 && !(flags & MLORA_SILU_MUL)) {
+    a.n_adapters = n_adapters;
+    if (flags & MLORA_SILU_MUL) {
+      // interleaved gate/up: B rows are [gate half | up half] with the other module's half zero, so the
+      // expand is one dot product of length 2*r_max against u = [u_gate | u_up]
+      a.r_max = 2 * r_max;
+      a.n_mod = 1;
+      a.full_rank = 1;
+      a.mod_off[0] = 0;
+      a.mod_off[1] = out;
+    } else if (n_mod > 1) {
       MLORA_REQUIRE(h_mod_offsets, "linear: n_mod > 1 needs module offsets");
       MLORA_REQUIRE(h_mod_offsets[0] == 0 && h_mod_offsets[n_mod] == out, "linear: module offsets must span [0,out]");
       for (int m = 0; m <= n_mod; ++m) a.mod_off[m] = h_mod_offsets[m];

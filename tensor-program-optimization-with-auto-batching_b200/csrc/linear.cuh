@@ -16,14 +16,15 @@ struct LinearArgs {
   const int32_t* ranks;  // [N]
   const float* scales;   // [N]
   const int32_t* slots;  // [T]
-  int r_max, n_mod;
+  int r_max, n_mod;      // B row pitch / u slice width, number of u slices per row
   int mod_off[9];
   int flags;
+  int n_adapters;        // slots >= n_adapters are treated as "no adapter"
+  int full_rank;         // 1: every row uses all r_max entries (zero-padded), ranks[] is ignored
 };
 
 // Module (q/k/v, gate/up ...) that owns output row o.
 __device__ __forceinline__ int module_of(const LinearArgs& a, int o) {
-  if (a.flags & MLORA_SILU_MUL) return (o >> 3) & 1;
   int m = 0;
 #pragma unroll 1
   while (m + 1 < a.n_mod && o >= a.mod_off[m + 1]) ++m;
@@ -34,8 +35,8 @@ __device__ __forceinline__ int module_of(const LinearArgs& a, int o) {
 __device__ __forceinline__ float lora_expand(const LinearArgs& a, int t, int o) {
   if (a.u == nullptr) return 0.f;
   const int s = a.slots[t];
-  if (s < 0) return 0.f;
-  const int r = a.ranks[s];
+  if (s < 0 || s >= a.n_adapters) return 0.f;
+  const int r = a.full_rank ? a.r_max : a.ranks[s];
   const int m = module_of(a, o);
   const float* ur = a.u + (size_t)t * (a.r_max * a.n_mod) + m * a.r_max;
   const bf16* b = a.B_all + ((size_t)s * a.out + o) * a.r_max;

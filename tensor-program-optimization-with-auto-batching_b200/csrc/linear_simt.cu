@@ -12,15 +12,15 @@ namespace {
 __global__ void __launch_bounds__(256) lora_shrink_kernel(const bf16* __restrict__ x, int64_t ldx,
                                                           const bf16* __restrict__ A_all,
                                                           const int32_t* __restrict__ ranks,
-                                                          const int32_t* __restrict__ slots, int in,
-                                                          int r_max, int r_tot, float* __restrict__ u) {
+                                                          const int32_t* __restrict__ slots, int n_adapters,
+                                                          int in, int r_max, int r_tot, float* __restrict__ u) {
   const int t = blockIdx.y;
   const int j = blockIdx.x * 8 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (j >= r_tot) return;
   const int slot = slots[t];
   float acc = 0.f;
-  if (slot >= 0 && (j % r_max) < ranks[slot]) {
+  if (slot >= 0 && slot < n_adapters && (j % r_max) < ranks[slot]) {
     const bf16* a = A_all + ((size_t)slot * r_tot + j) * in;
     const bf16* xr = x + (size_t)t * ldx;
     for (int k = lane * 8; k < in; k += 256) {
@@ -116,9 +116,9 @@ int launch_linear_simt(const LinearArgs& a, cudaStream_t st) {
 using namespace mlora;
 
 extern "C" int mlora_lora_shrink(const void* d_x, int64_t ldx, const void* d_A_all, const int32_t* d_ranks,
-                                 const int32_t* d_slots, int32_t T, int32_t in, int32_t r_max, int32_t n_mod,
-                                 float* d_u, void* stream) {
-  MLORA_REQUIRE(T >= 0 && in > 0 && r_max > 0 && n_mod > 0, "lora_shrink: bad sizes");
+                                 const int32_t* d_slots, int32_t n_adapters, int32_t T, int32_t in, int32_t r_max,
+                                 int32_t n_mod, float* d_u, void* stream) {
+  MLORA_REQUIRE(T >= 0 && in > 0 && r_max > 0 && n_mod > 0 && n_adapters > 0, "lora_shrink: bad sizes");
   MLORA_REQUIRE(in % 8 == 0 && ldx % 8 == 0, "lora_shrink: in and ldx must be multiples of 8 (in=%d)", in);
   MLORA_REQUIRE(d_x && d_A_all && d_ranks && d_slots && d_u, "lora_shrink: null pointer");
   MLORA_REQUIRE(aligned16(d_x) && aligned16(d_A_all), "lora_shrink: x and A_all must be 16-byte aligned");
@@ -127,7 +127,7 @@ extern "C" int mlora_lora_shrink(const void* d_x, int64_t ldx, const void* d_A_a
   const int r_tot = r_max * n_mod;
   dim3 grid((r_tot + 7) / 8, T);
   lora_shrink_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const bf16*)d_x, ldx, (const bf16*)d_A_all, d_ranks,
-                                                             d_slots, in, r_max, r_tot, d_u);
+                                                             d_slots, n_adapters, in, r_max, r_tot, d_u);
   count_launch();
   MLORA_CHECK_LAUNCH("lora_shrink_kernel");
   return MLORA_OK;

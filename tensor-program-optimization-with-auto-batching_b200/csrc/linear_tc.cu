@@ -40,6 +40,9 @@ struct TcParams {
   int row_tiles;   // ceil(out / BM)
   int n_tiles;     // row_tiles * token tiles
   int per_cta;     // iterations (tile, k-block) per CTA
+  int lora_mode;   // 0 none, 1 expand on CUDA cores in the epilogue, 2 expand on the tensor cores
+  int lora_sub;    // K elements of one LoRA stage (16, 32 or 64 = row bytes 32, 64, 128)
+  int n_sub;       // LoRA stages per adapter segment (r_max / lora_sub)
   int32_t* status;  // scratch[0]
   int32_t* tickets; // [kMaxGrid], indexed by the first contributing CTA of a split tile
   float* partials;  // [grid][2][BN][BM]
@@ -137,14 +140,42 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[32]) {
 // bytes apart.  Field layout of the sm_100 shared-memory matrix descriptor: start address >> 4 in
 // bits [0,14), leading byte offset >> 4 in [16,30) (unused for swizzled K-major, set to 1), stride
 // byte offset >> 4 in [32,46), descriptor version 1 in [46,48), swizzle mode in [61,64) (2 = 128 B).
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t row_bytes = 128) {
+  // swizzle span = row pitch: 128 B -> mode 2, 64 B -> mode 4, 32 B -> mode 6; 8-row groups are
+  // 8 * row_bytes apart
+  const uint64_t mode = row_bytes == 128 ? 2 : row_bytes == 64 ? 4 : 6;
   uint64_t d = 0;
   d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
   d |= (uint64_t)1 << 16;
-  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)((8 * row_bytes) >> 4) << 32;
   d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
+  d |= mode << 61;
   return d;
+}
+
+// Distinct adapter slots among the tokens of one token tile, in order of first appearance.
+// Executed by one full warp; s_tok [BN] receives the tile's slots, s_list [BN] the distinct ones.
+template <int BN>
+__device__ __forceinline__ int distinct_slots(const LinearArgs& a, int t0, int* s_tok, int* s_list) {
+  const int lane = threadIdx.x & 31;
+  for (int n = lane; n < BN; n += 32) {
+    int s = (t0 + n < a.T) ? a.slots[t0 + n] : -1;
+    s_tok[n] = (s >= 0 && s < a.n_adapters) ? s : -1;
+  }
+  __syncwarp();
+  int count = 0;
+#pragma unroll 1
+  for (int base = 0; base < BN; base += 32) {
+    const int n = base + lane;
+    const int s = n < BN ? s_tok[n] : -1;
+    bool first = s >= 0;
+    for (int m = 0; first && m < n; ++m) first = s_tok[m] != s;
+    const unsigned mask = __ballot_sync(0xffffffffu, first);
+    if (first) s_list[count + __popc(mask & ((1u << lane) - 1))] = s;
+    count += __popc(mask);
+  }
+  __syncwarp();
+  return count;
 }
 
 // Instruction descriptor, kind::f16: D fp32 (bits [4,6) = 1), A and B bf16 ([7,10) = [10,13) = 1),
@@ -158,7 +189,8 @@ struct Cfg {
   static constexpr int kStageBytes = BM * BK * 2 + BN * BK * 2;
   static constexpr int kRing = 176 * 1024;
   static constexpr int kStages = (kRing / kStageBytes) > 10 ? 10 : (kRing / kStageBytes);
-  static constexpr int kAuxBytes = kStageUMax + BN * 4 /*slots*/ + 512 /*barriers*/;
+  // barriers | epilogue slots | producer: token slots, distinct list | MMA warp: token slots, distinct list | u
+  static constexpr int kAuxBytes = 512 + 5 * BN * 4 + kStageUMax;
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + kAuxBytes;
   static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;  // two accumulators
   static constexpr int kChunk = BN < 32 ? BN : 32;              // columns per TMEM load
@@ -190,6 +222,7 @@ __device__ __forceinline__ Segment next_segment(const TcParams& p, int& it, int 
 template <int BN>
 __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                 const __grid_constant__ CUtensorMap map_x,
+                                                                const __grid_constant__ CUtensorMap map_b,
                                                                 TcParams p) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
@@ -200,8 +233,12 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
   uint64_t* acc_full = empty_bar + C::kStages;   // [2]
   uint64_t* acc_empty = acc_full + 2;            // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
-  int* s_slots = reinterpret_cast<int*>(aux + 512);                  // [BN]
-  float* s_u = reinterpret_cast<float*>(aux + 512 + BN * 4);        // [BN * r_tot] when it fits
+  int* s_slots = reinterpret_cast<int*>(aux + 512);  // [BN] epilogue warps (CUDA-core expand)
+  int* p_tok = s_slots + BN;                          // [BN] producer warp: slots of the token tile
+  int* p_list = p_tok + BN;                           // [BN] producer warp: distinct slots
+  int* m_tok = p_list + BN;                           // [BN] MMA warp
+  int* m_list = m_tok + BN;                           // [BN] MMA warp
+  float* s_u = reinterpret_cast<float*>(m_list + BN); // [BN * r_tot] when it fits
   __shared__ int s_abort;
   __shared__ int s_last;
 
@@ -222,6 +259,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     tma_prefetch_desc(&map_w);
     tma_prefetch_desc(&map_x);
+    if (p.lora_mode == 2) tma_prefetch_desc(&map_b);
   }
   if (warp == 1) tmem_alloc(tmem_slot, C::kTmemCols);
   tc_fence_before();
@@ -230,15 +268,19 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
-    // ---- TMA producer ------------------------------------------------------------------------------
-    if (lane == 0) {
-      int it = rg.it0, n = 0;
-      bool ok = true;
-      while (it < rg.it1 && ok) {
-        const Segment sg = next_segment(p, it, rg.it1);
-        const int row_tile = sg.tile % p.row_tiles, tok_tile = sg.tile / p.row_tiles;
-        for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++n) {
-          const int s = n % C::kStages, round = n / C::kStages;
+    // ---- TMA producer: lane 0 issues the copies; all lanes build the LoRA operand tiles -----------------
+    const LinearArgs& a = p.a;
+    const int r_tot = a.r_max * a.n_mod;
+    const bool stage_u = p.lora_mode == 2 && (size_t)BN * r_tot * sizeof(float) <= (size_t)kStageUMax;
+    int it = rg.it0, n = 0, cur_tok_tile = -1, n_seg = 0;
+    bool ok = true;
+    while (it < rg.it1 && ok) {
+      const Segment sg = next_segment(p, it, rg.it1);
+      const int row_tile = sg.tile % p.row_tiles, tok_tile = sg.tile / p.row_tiles;
+      if (lane == 0) {
+        int nn = n;
+        for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++nn) {
+          const int s = nn % C::kStages, round = nn / C::kStages;
           if (!mbar_wait(&empty_bar[s], (round & 1) ^ 1, &s_abort)) {
             s_abort = 1;
             atomicOr(p.status, 1);
@@ -251,25 +293,97 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
           tma_load_2d(st + BM * BK * 2, &map_x, kb * BK, tok_tile * BN, &full_bar[s]);
         }
       }
+      n += sg.kb1 - sg.kb0;
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (ok && p.lora_mode == 2 && sg.kb1 == p.k_blocks) {
+        // The tile's last k-block is ours: append one stage per (adapter present in the token tile,
+        // 64-wide slice of the rank): A operand = B_all[slot, rows of the tile, slice] by TMA, B operand
+        // = scale * u of the tokens that use the adapter (zero rows for the others), written here in
+        // the swizzled K-major layout the MMA expects.
+        const int t0 = tok_tile * BN;
+        if (tok_tile != cur_tok_tile) {
+          n_seg = distinct_slots<BN>(a, t0, p_tok, p_list);
+          if (stage_u) {
+            const int n_valid = min(BN, a.T - t0) * r_tot;
+            for (int i = lane; i < n_valid; i += 32) s_u[i] = a.u[(size_t)t0 * r_tot + i];
+            __syncwarp();
+          }
+          cur_tok_tile = tok_tile;
+        }
+        const int u_off = module_of(a, row_tile * BM) * a.r_max;
+        const int rb = p.lora_sub * 2;      // row bytes of a LoRA stage
+        const int chunks = p.lora_sub / 8;  // 16-byte chunks per row
+        for (int sgi = 0; sgi < n_seg && ok; ++sgi) {
+          const int slot = p_list[sgi];
+          const float sc = a.scales[slot];
+          for (int sb = 0; sb < p.n_sub; ++sb, ++n) {
+            const int s = n % C::kStages, round = n / C::kStages;
+            int w = 1;
+            if (lane == 0) w = mbar_wait(&empty_bar[s], (round & 1) ^ 1, &s_abort) ? 1 : 0;
+            w = __shfl_sync(0xffffffffu, w, 0);
+            if (!w) {
+              if (lane == 0) {
+                s_abort = 1;
+                atomicOr(p.status, 1);
+              }
+              ok = false;
+              break;
+            }
+            uint8_t* st = tiles + s * C::kStageBytes;
+            uint8_t* xt = st + BM * BK * 2;
+            for (int idx = lane; idx < BN * chunks; idx += 32) {
+              const int nrow = idx / chunks, c = idx - nrow * chunks;
+              uint4 val = make_uint4(0u, 0u, 0u, 0u);
+              if (p_tok[nrow] == slot) {
+                const float* ur = (stage_u ? s_u + nrow * r_tot : a.u + (size_t)(t0 + nrow) * r_tot) + u_off +
+                                  sb * p.lora_sub + c * 8;
+                float f[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) f[e] = ur[e] * sc;
+                val = pack8(f);
+              }
+              const int sw = rb == 128 ? (nrow & 7) : rb == 64 ? ((nrow >> 1) & 3) : ((nrow >> 2) & 1);
+              *reinterpret_cast<uint4*>(xt + nrow * rb + ((c ^ sw) << 4)) = val;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+              mbar_expect_tx(&full_bar[s], BM * rb);
+              tma_load_2d(st, &map_b, sb * p.lora_sub, slot * a.out + row_tile * BM, &full_bar[s]);
+            }
+          }
+        }
+      }
     }
   } else if (warp == 1) {
-    // ---- MMA issuer --------------------------------------------------------------------------------
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(BM, BN);
-      int it = rg.it0, n = 0, j = 0;
-      bool ok = true;
-      while (it < rg.it1 && ok) {
-        const Segment sg = next_segment(p, it, rg.it1);
-        const int buf = j & 1;
+    // ---- MMA issuer: lane 0 issues; all lanes count the LoRA stages of a token tile ---------------------
+    const LinearArgs& a = p.a;
+    constexpr uint32_t idesc = make_idesc(BM, BN);
+    int it = rg.it0, n = 0, j = 0, cur_tok_tile = -1, n_seg = 0;
+    bool ok = true;
+    while (it < rg.it1 && ok) {
+      const Segment sg = next_segment(p, it, rg.it1);
+      const int tok_tile = sg.tile / p.row_tiles;
+      const int buf = j & 1;
+      const uint32_t d_tmem = tmem_base + buf * BN;
+      int n_lora = 0;
+      if (p.lora_mode == 2 && sg.kb1 == p.k_blocks) {
+        if (tok_tile != cur_tok_tile) {
+          n_seg = distinct_slots<BN>(a, tok_tile * BN, m_tok, m_list);
+          cur_tok_tile = tok_tile;
+        }
+        n_lora = n_seg * p.n_sub;
+      }
+      if (lane == 0) {
+        int nn = n;
         if (!mbar_wait(&acc_empty[buf], ((j >> 1) & 1) ^ 1, &s_abort)) {
           s_abort = 1;
           atomicOr(p.status, 8);
-          break;
+          ok = false;
         }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++n) {
-          const int s = n % C::kStages, round = n / C::kStages;
+        for (int kb = sg.kb0; kb < sg.kb1 && ok; ++kb, ++nn) {
+          const int s = nn % C::kStages, round = nn / C::kStages;
           if (!mbar_wait(&full_bar[s], round & 1, &s_abort)) {
             s_abort = 1;
             atomicOr(p.status, 2);
@@ -287,9 +401,27 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
           }
           umma_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
         }
+        const uint32_t rb = p.lora_sub * 2;
+        for (int l = 0; l < n_lora && ok; ++l, ++nn) {
+          const int s = nn % C::kStages, round = nn / C::kStages;
+          if (!mbar_wait(&full_bar[s], round & 1, &s_abort)) {
+            s_abort = 1;
+            atomicOr(p.status, 2);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t wa = smem_u32(tiles + s * C::kStageBytes);
+          const uint64_t adesc = make_smem_desc(wa, rb);
+          const uint64_t bdesc = make_smem_desc(wa + BM * BK * 2, rb);
+          for (int k = 0; k < p.lora_sub / 16; ++k) umma_bf16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, 1u);
+          umma_commit(&empty_bar[s]);
+        }
         if (ok) umma_commit(&acc_full[buf]);
-        ++j;
       }
+      n += (sg.kb1 - sg.kb0) + n_lora;
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      ++j;
     }
   } else {
     // ---- epilogue warps: TMEM lane quarter = warp % 4 -------------------------------------------------
@@ -298,7 +430,8 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
     const int etid = q * 32 + lane;           // 0..127 = row inside the tile
     const bool silu = (a.flags & MLORA_SILU_MUL) != 0;
     const int r_tot = a.r_max * a.n_mod;
-    const bool stage_u = a.u != nullptr && (size_t)BN * r_tot * sizeof(float) <= (size_t)kStageUMax;
+    const bool simt_lora = p.lora_mode == 1;
+    const bool stage_u = simt_lora && (size_t)BN * r_tot * sizeof(float) <= (size_t)kStageUMax;
     int staged_tok_tile = -1;
     int it = rg.it0, j = 0;
     bool ok = true;
@@ -312,7 +445,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
       const bool full_seg = sg.kb0 == 0 && sg.kb1 == p.k_blocks;
 
       // per-token LoRA operands of this token tile -> shared memory (once per token tile)
-      if (a.u != nullptr && staged_tok_tile != tok_tile) {
+      if (simt_lora && staged_tok_tile != tok_tile) {
         epi_bar_sync();  // previous users of the staging area are done
         for (int i = etid; i < BN; i += kEpiThreads) s_slots[i] = (t0 + i < a.T) ? a.slots[t0 + i] : -1;
         if (stage_u) {
@@ -325,7 +458,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
 
       // Adds the LoRA expand, applies SiLU*up, stores.  v[i] = projection of (token t0+c0+i, row).
       auto finish = [&](float (&v)[32], int c0) {
-        if (a.u != nullptr && row < a.out) {
+        if (simt_lora && row < a.out) {
           const int m = module_of(a, row);
           int cur = -1, r = 0;
           float sc = 0.f;
@@ -333,10 +466,10 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
 #pragma unroll
           for (int i = 0; i < C::kChunk; ++i) {
             const int s = s_slots[c0 + i];
-            if (s < 0) continue;
+            if (s < 0 || s >= a.n_adapters) continue;
             if (s != cur) {  // rows of one adapter are usually adjacent (ordered batches): reuse B[s, row, :]
               cur = s;
-              r = a.ranks[s];
+              r = a.full_rank ? a.r_max : a.ranks[s];
               sc = a.scales[s];
               const bf16* b = a.B_all + ((size_t)s * a.out + row) * a.r_max;
 #pragma unroll
@@ -470,15 +603,18 @@ EncodeTiledFn encode_fn() {
 }
 
 // 2-D bf16 tensor [rows, cols] with row pitch ld elements; box = [box_rows, 64 cols], 128-byte swizzle.
-int make_map(CUtensorMap* m, const void* ptr, int rows, int cols, int64_t ld, int box_rows) {
+int make_map(CUtensorMap* m, const void* ptr, long long rows, int cols, int64_t ld, int box_rows, int box_cols = BK) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return fail(MLORA_ECUDA, "linear: cuTensorMapEncodeTiled is not available from this driver");
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+  const CUtensorMapSwizzle swz = box_cols * 2 == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                 : box_cols * 2 == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                                      : CU_TENSOR_MAP_SWIZZLE_32B;
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(MLORA_ECUDA, "linear: cuTensorMapEncodeTiled failed with %d", (int)r);
   return MLORA_OK;
@@ -526,6 +662,27 @@ int launch(const LinearArgs& a, const Plan& pl, void* work, cudaStream_t st) {
   if (rc) return rc;
   TcParams p;
   p.a = a;
+  // LoRA expand: on the tensor cores when the rank pitch is 16/32/64/128 and every module boundary
+  // is a multiple of the 128-row tile; else on CUDA cores in the epilogue (needs pitch <= 64)
+  p.lora_mode = 0;
+  p.lora_sub = 16;
+  p.n_sub = 1;
+  CUtensorMap mb = mw;
+  if (a.u != nullptr) {
+    bool aligned_mods = true;
+    for (int m = 1; m < a.n_mod; ++m) aligned_mods = aligned_mods && (a.mod_off[m] % BM == 0);
+    const bool pitch_ok = a.r_max == 16 || a.r_max == 32 || a.r_max == 64 || a.r_max == 128;
+    if (pitch_ok && aligned_mods) {
+      p.lora_mode = 2;
+      p.lora_sub = a.r_max < 64 ? a.r_max : 64;
+      p.n_sub = a.r_max / p.lora_sub;
+      rc = make_map(&mb, a.B_all, (long long)a.n_adapters * a.out, a.r_max, a.r_max, BM, p.lora_sub);
+      if (rc) return rc;
+    } else {
+      if (a.r_max > 64) return fail(MLORA_EINVAL, "linear: rank pitch %d needs tile-aligned modules", a.r_max);
+      p.lora_mode = 1;
+    }
+  }
   p.k_blocks = pl.k_blocks;
   p.row_tiles = pl.row_tiles;
   p.n_tiles = pl.row_tiles * pl.tok_tiles;
@@ -540,7 +697,7 @@ int launch(const LinearArgs& a, const Plan& pl, void* work, cudaStream_t st) {
     if (e != cudaSuccess) return fail(MLORA_ECUDA, "linear: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     attr_set = true;
   }
-  linear_tc_kernel<BN><<<pl.grid, kThreads, C::kSmemBytes, st>>>(mw, mx, p);
+  linear_tc_kernel<BN><<<pl.grid, kThreads, C::kSmemBytes, st>>>(mw, mx, mb, p);
   count_launch();
   MLORA_CHECK_LAUNCH("linear_tc_kernel");
   return MLORA_OK;
@@ -552,7 +709,8 @@ bool linear_tc_supported(const LinearArgs& a) {
   // TMA needs 16-byte aligned bases and row pitches; everything else (ragged K, out, T) is handled by
   // zero-filled out-of-bounds boxes and masked stores.
   const long long tiles = (long long)((a.out + BM - 1) / BM) * ((a.T + 127) / 128);
-  return aligned16(a.x) && aligned16(a.W) && (a.ldx * 2) % 16 == 0 && (a.in * 2) % 16 == 0 && a.r_max <= 64 &&
+  return aligned16(a.x) && aligned16(a.W) && (a.ldx * 2) % 16 == 0 && (a.in * 2) % 16 == 0 && (a.u == nullptr || a.r_max % 8 == 0) &&
+         (a.u == nullptr || a.r_max <= 64 || a.r_max == 128) &&
          tiles * ((a.in + BK - 1) / BK) < 2000000000ll;
 }
 

@@ -78,7 +78,7 @@ class PackedLlama:
             ka = next(k for k in ad if k.endswith("lora_A.weight"))
             ranks.append(ad[ka].shape[0])
         self.ranks_host = ranks
-        self.r_max = max(8, -(-max(ranks) // 8) * 8) if ranks else 0
+        self.r_max = (16 if max(ranks) <= 16 else 32 if max(ranks) <= 32 else -(-max(ranks) // 64) * 64) if ranks else 0
         if adapters:
             self.ranks = torch.tensor(ranks, dtype=torch.int32, device=self.device)
             self.scales = torch.tensor(list(scales), dtype=torch.float32, device=self.device)
@@ -122,7 +122,10 @@ class PackedLlama:
                     A_all[s, m * r_max:m * r_max + r] = A.to(device=dev, dtype=torch.bfloat16)
                     B_parts[m][s, :, :r] = B.to(device=dev, dtype=torch.bfloat16)
             if interleave:
-                B_all = torch.stack([interleave_gate_up(B_parts[0][s], B_parts[1][s]) for s in range(N)])
+                # gate rows carry [B_gate | 0], up rows [0 | B_up]: one dot product against [u_gate | u_up]
+                z = torch.zeros_like(B_parts[0])
+                g2, u2 = torch.cat([B_parts[0], z], 2), torch.cat([z, B_parts[1]], 2)
+                B_all = torch.stack([interleave_gate_up(g2[s], u2[s]) for s in range(N)])
             else:
                 B_all = torch.cat(B_parts, 1)
             offs = tuple(int(x) for x in np.cumsum([0] + list(outs)))

@@ -81,7 +81,10 @@ class LoraStack:
     """Packed adapters of one (fused) projection.
 
     A_all [N, n_mod*r_max, in] bf16, B_all [N, out, r_max] bf16 (module m of
-    adapter s uses rows m*r_max.. of A and its own rows of B), ranks [N] int32,
+    adapter s uses rows m*r_max.. of A and its own rows of B; for an interleaved
+    gate/up stack B_all is [N, out, 2*r_max] with the other module's half zero),
+    r_max a multiple of 8 (16, 32 or 64 for the tensor-core expand), padding
+    beyond an adapter's rank zero, ranks [N] int32,
     scales [N] float32 (alpha/r), mod_offsets: host list of n_mod+1 output-row
     offsets.
     """
@@ -100,7 +103,7 @@ def lora_shrink(x, stack: LoraStack, slots, out=None):
     r_tot = stack.r_max * stack.n_mod
     u = out if out is not None else torch.empty(T, r_tot, dtype=torch.float32, device=x.device)
     check(_lib.lib().mlora_lora_shrink(_ptr(x), x.stride(0), _ptr(stack.A_all), _ptr(stack.ranks), _ptr(slots),
-                                       T, K, stack.r_max, stack.n_mod, _ptr(u), _stream()), "mlora_lora_shrink")
+                                       stack.A_all.shape[0], T, K, stack.r_max, stack.n_mod, _ptr(u), _stream()), "mlora_lora_shrink")
     return u
 
 
@@ -125,7 +128,8 @@ def linear(x, W, stack: LoraStack = None, slots=None, u=None, flags: int = 0, ou
         _ptr(x), x.stride(0), _ptr(W), _ptr(out), out.stride(0), T, K, N,
         _ptr(u) if stack is not None else None, _ptr(stack.B_all) if stack is not None else None,
         _ptr(stack.ranks) if stack is not None else None, _ptr(stack.scales) if stack is not None else None,
-        _ptr(slots) if stack is not None else None, stack.r_max if stack is not None else 0,
+        _ptr(slots) if stack is not None else None, stack.A_all.shape[0] if stack is not None else 0,
+        stack.r_max if stack is not None else 0,
         stack.n_mod if stack is not None else 1, mod, flags, _ptr(ws), wb, _stream()), "mlora_linear")
     return out
 

@@ -28,7 +28,7 @@ def test_host_side_argument_checks_need_no_gpu():
     lib = load("_lib")
     h = lib.lib()
     # size / alignment validation happens before any CUDA call
-    rc = h.mlora_linear(None, 0, None, None, 0, 4, 12, 8, None, None, None, None, None, 0, 1, None, 0, None, 0, None)
+    rc = h.mlora_linear(None, 0, None, None, 0, 4, 12, 8, None, None, None, None, None, 0, 0, 1, None, 0, None, 0, None)
     assert rc == -1 and b"multiples of 8" in h.mlora_last_error()
     rc = h.mlora_paged_attention(None, 0, None, None, None, 0, None, None, 1, 4, 4, 80, 16, 1e4, 1, None, 0, 1,
                                  None, 0, None)

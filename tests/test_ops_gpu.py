@@ -7,6 +7,7 @@ import numpy as np
 import pytest
 import torch
 
+from conftest import load
 from oracle import bucketing, ops as oops
 
 pytestmark = pytest.mark.gpu
@@ -85,8 +86,16 @@ def test_bucket_sort_segments(ops, cuda, n):
 
 # ----------------------------------------------------------------------------- LoRA + projection
 def _stack(ops, A, B, ranks, scales, dev, n_mod=1, mod_offsets=None):
-    return ops.LoraStack(A.to(dev), B.to(dev), _i32(ranks, dev), torch.tensor(scales, dtype=torch.float32, device=dev),
-                         B.shape[2], n_mod, mod_offsets)
+    """Packs A [N, n_mod*r, K] / B [N, out, r] into stacks whose rank pitch is 16, 32 or 64 (zero padded)."""
+    r = B.shape[2]
+    rp = 16 if r <= 16 else 32 if r <= 32 else 64
+    Ap = torch.zeros(A.shape[0], n_mod * rp, A.shape[2], dtype=A.dtype)
+    for m in range(n_mod):
+        Ap[:, m * rp:m * rp + r] = A[:, m * r:(m + 1) * r]
+    Bp = torch.zeros(B.shape[0], B.shape[1], rp, dtype=B.dtype)
+    Bp[..., :r] = B
+    return ops.LoraStack(Ap.to(dev), Bp.to(dev), _i32(ranks, dev), torch.tensor(scales, dtype=torch.float32, device=dev),
+                         rp, n_mod, mod_offsets)
 
 
 @pytest.mark.parametrize("T", [1, 8, 32, 128])
@@ -151,6 +160,72 @@ def test_mixed_ranks_no_adapter_rows_and_modules(ops, cuda):
             u = A[s, m * r_max:m * r_max + r].float() @ x[t].float()
             want[t, offs[m]:offs[m + 1]] += scales[s] * (B[s, offs[m]:offs[m + 1], :r].float() @ u)
     torch.testing.assert_close(y, want, atol=ATOL, rtol=RTOL)
+
+
+@pytest.mark.parametrize("T,r", [(5, 16), (32, 16), (40, 32), (130, 64)])
+def test_fused_qkv_modules_on_tensor_cores(ops, cuda, T, r):
+    """Three modules of 256/128/128 rows (tile-aligned): the expand runs as extra MMA stages."""
+    g = torch.Generator().manual_seed(T + r)
+    K, outs, n_ad = 512, (256, 128, 128), 6
+    offs = (0, 256, 384, 512)
+    x = torch.randn(T, K, generator=g).bfloat16()
+    W = (torch.randn(512, K, generator=g) * 0.05).bfloat16()
+    A = (torch.randn(n_ad, 3 * r, K, generator=g) * 0.05).bfloat16()
+    B = (torch.randn(n_ad, 512, r, generator=g) * 0.05).bfloat16()
+    ranks = [r, r // 2, r, 8, r, r][:n_ad]
+    for s in range(n_ad):  # zero the padding beyond each adapter's rank
+        for m in range(3):
+            A[s, m * r + ranks[s]:(m + 1) * r] = 0
+        B[s, :, ranks[s]:] = 0
+    scales = [2.0, 1.0, 0.5, 1.5, 3.0, 0.25]
+    slots = torch.randint(-1, n_ad, (T,), generator=g).int()
+    st = _stack(ops, A, B, ranks, scales, cuda, 3, offs)
+    want = x.float() @ W.float().t()
+    for t in range(T):
+        s = int(slots[t])
+        if s < 0:
+            continue
+        for m in range(3):
+            u = A[s, m * r:(m + 1) * r].float() @ x[t].float()
+            want[t, offs[m]:offs[m + 1]] += scales[s] * (B[s, offs[m]:offs[m + 1]].float() @ u)
+    y = ops.linear(x.to(cuda), W.to(cuda), st, slots.to(cuda)).float().cpu()
+    y2 = ops.linear(x.to(cuda), W.to(cuda), st, slots.to(cuda), flags=ops.FORCE_SIMT).float().cpu()
+    torch.cuda.synchronize()
+    assert int(ops.workspace(4, cuda, "linear")[:4].view(torch.int32)) == 0, "a bounded wait expired"
+    torch.testing.assert_close(y, want, atol=ATOL, rtol=RTOL)
+    torch.testing.assert_close(y2, want, atol=ATOL, rtol=RTOL)
+
+
+@pytest.mark.parametrize("T,r", [(4, 16), (32, 16), (70, 64)])
+def test_gate_up_silu_with_lora(ops, cuda, T, r):
+    """Interleaved gate/up with LoRA on both: B rows carry [gate half | up half] with the other half zero."""
+    model = load("model")
+    g = torch.Generator().manual_seed(T)
+    K, I, n_ad = 256, 384, 3
+    x = torch.randn(T, K, generator=g).bfloat16()
+    Wg = (torch.randn(I, K, generator=g) * 0.05).bfloat16()
+    Wu = (torch.randn(I, K, generator=g) * 0.05).bfloat16()
+    Ag = (torch.randn(n_ad, r, K, generator=g) * 0.05).bfloat16()
+    Au = (torch.randn(n_ad, r, K, generator=g) * 0.05).bfloat16()
+    Bg = (torch.randn(n_ad, I, r, generator=g) * 0.05).bfloat16()
+    Bu = (torch.randn(n_ad, I, r, generator=g) * 0.05).bfloat16()
+    slots = torch.randint(-1, n_ad, (T,), generator=g).int()
+    z = torch.zeros_like(Bg)
+    B_all = torch.stack([model.interleave_gate_up(torch.cat([Bg, z], 2)[s], torch.cat([z, Bu], 2)[s])
+                         for s in range(n_ad)])
+    st = ops.LoraStack(torch.cat([Ag, Au], 1).to(cuda), B_all.to(cuda), _i32([r] * n_ad, cuda),
+                       torch.full((n_ad,), 2.0, device=cuda), r, 2, None)
+    Wi = model.interleave_gate_up(Wg, Wu)
+    gate, up = x.float() @ Wg.float().t(), x.float() @ Wu.float().t()
+    for t in range(T):
+        s = int(slots[t])
+        if s >= 0:
+            gate[t] += 2.0 * (Bg[s].float() @ (Ag[s].float() @ x[t].float()))
+            up[t] += 2.0 * (Bu[s].float() @ (Au[s].float() @ x[t].float()))
+    want = oops.silu_mul(gate, up)
+    for flags in (ops.SILU_MUL, ops.SILU_MUL | ops.FORCE_SIMT):
+        y = ops.linear(x.to(cuda), Wi.to(cuda), st, slots.to(cuda), flags=flags).float().cpu()
+        torch.testing.assert_close(y, want, atol=ATOL, rtol=RTOL)
 
 
 @pytest.mark.parametrize("T,K,I", [(3, 256, 688), (32, 512, 1024)])
