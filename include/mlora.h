@@ -32,6 +32,7 @@ extern "C" {
                                rows 8j.., rows 16j+8..16j+15 = up rows 8j..); y[t, c] = silu(g)*u, y has
                                out/2 columns */
 #define MLORA_FORCE_SIMT 4  /* use the CUDA-core warp-per-row kernel whatever the shape */
+#define MLORA_W_PACKED 8    /* d_W is the tiled layout written by mlora_pack_weight */
 
 int mlora_version(void);
 const char* mlora_last_error(void);
@@ -99,6 +100,15 @@ int mlora_lora_shrink(const void* d_x, int64_t ldx, const void* d_A_all, const i
  *   Its first int32 is a status word: non-zero after a kernel gave up a bounded wait (bit 0: TMA
  *   producer, bit 1: MMA issuer, bit 2: epilogue); the output of that call is then undefined. */
 size_t mlora_linear_workspace(int32_t T, int32_t in, int32_t out);
+/* Weight pre-packing (load time).  Rewrites W [out,in] bf16 as tiles [ceil(out/128)][ceil(in/64)] of
+ * 128 rows x 64 columns, each tile 16 KB contiguous and already in the 128-byte-swizzled K-major
+ * layout the tensor cores read from shared memory (zero padded), so that the projection kernel
+ * fetches a whole pipeline stage with one contiguous bulk copy instead of 128 row requests.
+ * The reference transposes / stacks weights once at load as well
+ * (tvm/llama_auto_batcher/compile_tvm.py:287-320).  Pass the result to mlora_linear with
+ * MLORA_W_PACKED (tensor-core kernel only). */
+size_t mlora_packed_weight_bytes(int32_t out, int32_t in);
+int mlora_pack_weight(const void* d_W, int32_t out, int32_t in, void* d_Wp, void* stream);
 int mlora_linear(const void* d_x, int64_t ldx, const void* d_W, void* d_y, int64_t ldy, int32_t T,
                  int32_t in, int32_t out, const float* d_u, const void* d_B_all,
                  const int32_t* d_ranks, const float* d_scales, const int32_t* d_slots,

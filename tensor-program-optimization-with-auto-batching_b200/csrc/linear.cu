@@ -65,7 +65,23 @@ extern "C" int mlora_linear(const void* d_x, int64_t ldx, const void* d_W, void*
   }
   if (T == 0) return MLORA_OK;
   cudaStream_t st = (cudaStream_t)stream;
+  if (flags & MLORA_W_PACKED) {
+    MLORA_REQUIRE(!(flags & MLORA_FORCE_SIMT) && d_work && linear_tc_supported(a),
+                  "linear: a packed weight needs the tensor-core kernel (scratch buffer, 16-byte aligned operands)");
+    return launch_linear_tc(a, d_work, work_bytes, st);
+  }
   if (!(flags & MLORA_FORCE_SIMT) && d_work && linear_tc_supported(a))
     return launch_linear_tc(a, d_work, work_bytes, st);
   return launch_linear_simt(a, st);
+}
+
+extern "C" size_t mlora_packed_weight_bytes(int32_t out, int32_t in) {
+  if (out <= 0 || in <= 0) return 0;
+  return packed_weight_bytes(out, in);
+}
+
+extern "C" int mlora_pack_weight(const void* d_W, int32_t out, int32_t in, void* d_Wp, void* stream) {
+  MLORA_REQUIRE(out > 0 && in > 0 && in % 8 == 0, "pack_weight: in must be a positive multiple of 8 (out=%d in=%d)", out, in);
+  MLORA_REQUIRE(d_W && d_Wp && aligned16(d_W) && aligned16(d_Wp), "pack_weight: pointers must be non-null and 16-byte aligned");
+  return launch_pack_weight(d_W, out, in, d_Wp, (cudaStream_t)stream);
 }

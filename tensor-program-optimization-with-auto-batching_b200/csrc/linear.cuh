@@ -69,5 +69,7 @@ int launch_linear_simt(const LinearArgs& a, cudaStream_t st);
 bool linear_tc_supported(const LinearArgs& a);
 size_t linear_tc_workspace(int T, int in, int out);
 int launch_linear_tc(const LinearArgs& a, void* work, size_t work_bytes, cudaStream_t st);
+size_t packed_weight_bytes(int out, int in);
+int launch_pack_weight(const void* W, int out, int in, void* Wp, cudaStream_t st);
 
 }  // namespace mlora

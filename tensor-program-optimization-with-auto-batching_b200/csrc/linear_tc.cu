@@ -4,8 +4,10 @@
 // accumulator lives in BN TMEM columns and one thread issues all MMAs.
 //
 // Persistent, warp-specialised, stream-K:
-//   * one CTA per SM (grid <= SM count), 192 threads: warp 0 = TMA producer (one thread), warp 1 =
-//     MMA issuer (one thread), warps 2..5 = epilogue (one TMEM lane = one output row per thread);
+//   * one CTA per SM (grid <= SM count), 224 threads: warp 0 = weight producer, warp 1 = MMA issuer
+//     (one thread each), warps 2..5 = epilogue (one TMEM lane = one output row per thread), warp 6 =
+//     token-tile producer.  Weights stream from HBM through a deep ring (12 x 16 KB) plus an L2
+//     prefetch running further ahead; token tiles come from L2 through their own shallow ring;
 //   * the iteration space (tile, k-block) -- tiles = row tiles x token tiles, k-blocks of 64 -- is
 //     cut into equal contiguous ranges, one per CTA, so every SM streams the same number of bytes
 //     whatever the shape; a range covers a tail of one tile, whole tiles, and a head of another;
@@ -27,12 +29,13 @@ namespace {
 
 constexpr int BM = 128;            // weight rows per tile (MMA M)
 constexpr int BK = 64;             // K elements per stage = one 128-byte swizzle span
-constexpr int kThreads = 192;
+constexpr int kThreads = 224;          // 7 warps: W producer, MMA, 4 epilogue, x producer
+#define kPrefetch p.prefetch          // weight tiles requested from HBM into L2 ahead of the ring
 constexpr int kEpiThreads = 128;
 constexpr int kHeaderBytes = 256;  // status word + padding at the start of the scratch buffer
 constexpr int kMaxGrid = 256;      // tickets / partial slots are sized for at most this many CTAs
 constexpr uint32_t kSpinLimit = 1u << 22;
-constexpr int kStageUMax = 16 * 1024;  // shrink outputs are staged in shared memory up to this size
+constexpr int kStageUMax = 8 * 1024;  // shrink outputs are staged in shared memory up to this size
 
 struct TcParams {
   LinearArgs a;
@@ -43,6 +46,7 @@ struct TcParams {
   int lora_mode;   // 0 none, 1 expand on CUDA cores in the epilogue, 2 expand on the tensor cores
   int lora_sub;    // K elements of one LoRA stage (16, 32 or 64 = row bytes 32, 64, 128)
   int n_sub;       // LoRA stages per adapter segment (r_max / lora_sub)
+  int prefetch;    // weight tiles requested into L2 ahead of the ring (0 = off)
   int32_t* status;  // scratch[0]
   int32_t* tickets; // [kMaxGrid], indexed by the first contributing CTA of a split tile
   float* partials;  // [grid][2][BN][BM]
@@ -82,6 +86,14 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
       ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
       : "memory");
+}
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void l2_prefetch(const void* src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
@@ -184,14 +196,82 @@ __host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+// Four adjacent outputs of one token: one 8-byte (bf16) or 16-byte (fp32) store when aligned and
+// all four exist, scalar stores otherwise.
+__device__ __forceinline__ void store4(const LinearArgs& a, int t, int col, const float (&o)[4], bool out_f32,
+                                       int n_valid) {
+  const size_t idx = (size_t)t * a.ldy + col;
+  if (n_valid >= 4 && (idx & 3) == 0) {
+    if (out_f32) {
+      *reinterpret_cast<float4*>(reinterpret_cast<float*>(a.y) + idx) = make_float4(o[0], o[1], o[2], o[3]);
+    } else {
+      uint2 v;
+      *reinterpret_cast<__nv_bfloat162*>(&v.x) = __floats2bfloat162_rn(o[0], o[1]);
+      *reinterpret_cast<__nv_bfloat162*>(&v.y) = __floats2bfloat162_rn(o[2], o[3]);
+      *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(a.y) + idx) = v;
+    }
+  } else {
+    for (int e = 0; e < 4 && e < n_valid; ++e) {
+      if (out_f32)
+        reinterpret_cast<float*>(a.y)[idx + e] = o[e];
+      else
+        reinterpret_cast<bf16*>(a.y)[idx + e] = __float2bfloat16_rn(o[e]);
+    }
+  }
+}
+
+// LoRA expand on CUDA cores for one 32-token chunk of one output row (used only when the tensor-core
+// expand does not apply: module boundaries inside a tile).  v[i] += scale * <u[token i], B[slot, row, :]>.
+template <int BN>
+__device__ __forceinline__ void simt_lora_expand(const LinearArgs& a, float (&v)[32], int c0, int t0, int row,
+                                                 int r_tot, bool stage_u, const int* s_slots, const float* s_u) {
+  constexpr int kChunk = BN < 32 ? BN : 32;
+  if (row >= a.out) return;
+  const int m = module_of(a, row);
+  int cur = -1, r = 0;
+  float sc = 0.f;
+  uint4 bq[8];
+#pragma unroll
+  for (int i = 0; i < kChunk; ++i) {
+    const int s = s_slots[c0 + i];
+    if (s < 0 || s >= a.n_adapters) continue;
+    if (s != cur) {  // rows of one adapter are usually adjacent (ordered batches): reuse B[s, row, :]
+      cur = s;
+      r = a.full_rank ? a.r_max : a.ranks[s];
+      sc = a.scales[s];
+      const bf16* b = a.B_all + ((size_t)s * a.out + row) * a.r_max;
+#pragma unroll
+      for (int g = 0; g < 8; ++g)
+        if (g * 8 < r) bq[g] = ld_cached(b + g * 8);
+    }
+    const float* ur = stage_u ? s_u + (c0 + i) * r_tot + m * a.r_max
+                              : a.u + (size_t)(t0 + c0 + i) * r_tot + m * a.r_max;
+    float acc = 0.f;
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+      if (g * 8 < r) {
+        float bf[8];
+        unpack8(bq[g], bf);
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          if (g * 8 + e < r) acc = fmaf(ur[g * 8 + e], bf[e], acc);
+      }
+    }
+    v[i] = fmaf(sc, acc, v[i]);
+  }
+}
+
 template <int BN>
 struct Cfg {
-  static constexpr int kStageBytes = BM * BK * 2 + BN * BK * 2;
-  static constexpr int kRing = 176 * 1024;
-  static constexpr int kStages = (kRing / kStageBytes) > 10 ? 10 : (kRing / kStageBytes);
-  // barriers | epilogue slots | producer: token slots, distinct list | MMA warp: token slots, distinct list | u
-  static constexpr int kAuxBytes = 512 + 5 * BN * 4 + kStageUMax;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + kAuxBytes;
+  static constexpr int kWBytes = BM * BK * 2;    // weight stage: 16 KB
+  static constexpr int kXBytes = BN * BK * 2;    // token-tile stage
+  static constexpr int kXStages = BN >= 64 ? 4 : 8;  // token tiles come from L2: a shallower ring is enough
+  // barriers | 7 integer lists of BN (token slots / distinct adapters per role) | staged shrink outputs
+  static constexpr int kAuxBytes = 1024 + 7 * BN * 4 + kStageUMax;
+  static constexpr int kBudget = 227 * 1024 - 1024 /*alignment slack*/ - 64 /*static*/;
+  static constexpr int kWStages0 = (kBudget - kAuxBytes - kXStages * kXBytes) / kWBytes;
+  static constexpr int kWStages = kWStages0 > 12 ? 12 : kWStages0;  // weights come from HBM: as deep as fits
+  static constexpr int kSmemBytes = kWStages * kWBytes + kXStages * kXBytes + kAuxBytes + 1024;
   static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;  // two accumulators
   static constexpr int kChunk = BN < 32 ? BN : 32;              // columns per TMEM load
 };
@@ -219,45 +299,56 @@ __device__ __forceinline__ Segment next_segment(const TcParams& p, int& it, int 
   return s;
 }
 
-template <int BN>
+template <int BN, bool SIMT_LORA>
 __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                 const __grid_constant__ CUtensorMap map_x,
                                                                 const __grid_constant__ CUtensorMap map_b,
                                                                 TcParams p) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint8_t* aux = tiles + C::kStages * C::kStageBytes;
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(aux);
-  uint64_t* empty_bar = full_bar + C::kStages;
-  uint64_t* acc_full = empty_bar + C::kStages;   // [2]
-  uint64_t* acc_empty = acc_full + 2;            // [2]
+  uint8_t* w_ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* x_ring = w_ring + C::kWStages * C::kWBytes;
+  uint8_t* aux = x_ring + C::kXStages * C::kXBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(aux);  // [kWStages] weight stage filled
+  uint64_t* empty_bar = full_bar + C::kWStages;           // [kWStages] weight stage consumed
+  uint64_t* xfull_bar = empty_bar + C::kWStages;          // [kXStages]
+  uint64_t* xempty_bar = xfull_bar + C::kXStages;         // [kXStages]
+  uint64_t* acc_full = xempty_bar + C::kXStages;          // [2]
+  uint64_t* acc_empty = acc_full + 2;                     // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
-  int* s_slots = reinterpret_cast<int*>(aux + 512);  // [BN] epilogue warps (CUDA-core expand)
-  int* p_tok = s_slots + BN;                          // [BN] producer warp: slots of the token tile
-  int* p_list = p_tok + BN;                           // [BN] producer warp: distinct slots
-  int* m_tok = p_list + BN;                           // [BN] MMA warp
-  int* m_list = m_tok + BN;                           // [BN] MMA warp
-  float* s_u = reinterpret_cast<float*>(m_list + BN); // [BN * r_tot] when it fits
+  int* s_slots = reinterpret_cast<int*>(aux + 1024);  // [BN] epilogue warps (CUDA-core expand)
+  int* p_tok = s_slots + BN;                           // weight producer: slots of the token tile
+  int* p_list = p_tok + BN;                            //                  distinct slots
+  int* m_tok = p_list + BN;                            // MMA warp
+  int* m_list = m_tok + BN;
+  int* x_tok = m_list + BN;                            // token-tile producer
+  int* x_list = x_tok + BN;
+  float* s_u = reinterpret_cast<float*>(x_list + BN);  // [BN * r_tot] when it fits
   __shared__ int s_abort;
   __shared__ int s_last;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const Range rg = cta_range(p, blockIdx.x);
   if (rg.it0 >= rg.it1) return;  // whole CTA idle (uniform)
+  const LinearArgs& a = p.a;
+  const int r_tot = a.r_max * a.n_mod;
 
   if (tid == 0) {
     s_abort = 0;
-    for (int s = 0; s < C::kStages; ++s) {
+    for (int s = 0; s < C::kWStages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
+    }
+    for (int s = 0; s < C::kXStages; ++s) {
+      mbar_init(&xfull_bar[s], 1);
+      mbar_init(&xempty_bar[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
       mbar_init(&acc_empty[b], 4);  // one arrival per epilogue warp
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    tma_prefetch_desc(&map_w);
+    if (!(a.flags & MLORA_W_PACKED)) tma_prefetch_desc(&map_w);
     tma_prefetch_desc(&map_x);
     if (p.lora_mode == 2) tma_prefetch_desc(&map_b);
   }
@@ -266,11 +357,83 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  const uint32_t rb = p.lora_sub * 2;  // row bytes of a LoRA stage
 
   if (warp == 0) {
-    // ---- TMA producer: lane 0 issues the copies; all lanes build the LoRA operand tiles -----------------
-    const LinearArgs& a = p.a;
-    const int r_tot = a.r_max * a.n_mod;
+    // ---- weight producer: lane 0 issues the copies; all lanes list the adapters of a token tile ------
+    const bool packed = (a.flags & MLORA_W_PACKED) != 0;
+    const uint8_t* wp = reinterpret_cast<const uint8_t*>(a.W);
+    int it = rg.it0, n = 0, cur_tok_tile = -1, n_seg = 0;
+    bool ok = true;
+    if (lane == 0 && packed) {
+      // Weights are read once, in a known order: ask L2 for the next kPrefetch tiles now, then one more
+      // per stage issued, so HBM requests in flight are not limited by the shared-memory ring.
+      for (int i = rg.it0; i < min(rg.it1, rg.it0 + kPrefetch); ++i) {
+        const int tile = i / p.k_blocks, kb = i - tile * p.k_blocks;
+        l2_prefetch(wp + ((size_t)(tile % p.row_tiles) * p.k_blocks + kb) * C::kWBytes, C::kWBytes);
+      }
+    }
+    while (it < rg.it1 && ok) {
+      const int it_seg = it;
+      const Segment sg = next_segment(p, it, rg.it1);
+      const int row_tile = sg.tile % p.row_tiles, tok_tile = sg.tile / p.row_tiles;
+      if (lane == 0) {
+        int nn = n;
+        for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++nn) {
+          const int s = nn % C::kWStages, round = nn / C::kWStages;
+          if (!mbar_wait(&empty_bar[s], (round & 1) ^ 1, &s_abort)) {
+            s_abort = 1;
+            atomicOr(p.status, 1);
+            ok = false;
+            break;
+          }
+          uint8_t* st = w_ring + s * C::kWBytes;
+          mbar_expect_tx(&full_bar[s], C::kWBytes);
+          if (packed) {  // one contiguous 16 KB tile, already in the swizzled K-major layout
+            bulk_load(st, wp + ((size_t)row_tile * p.k_blocks + kb) * C::kWBytes, C::kWBytes, &full_bar[s]);
+            const int ahead = it_seg + (kb - sg.kb0) + kPrefetch;
+            if (ahead < rg.it1) {
+              const int tile = ahead / p.k_blocks, kb2 = ahead - tile * p.k_blocks;
+              l2_prefetch(wp + ((size_t)(tile % p.row_tiles) * p.k_blocks + kb2) * C::kWBytes, C::kWBytes);
+            }
+          } else {
+            tma_load_2d(st, &map_w, kb * BK, row_tile * BM, &full_bar[s]);
+          }
+        }
+      }
+      n += sg.kb1 - sg.kb0;
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (ok && p.lora_mode == 2 && sg.kb1 == p.k_blocks) {
+        // The tile's last k-block is ours: one more stage per (adapter present in the token tile,
+        // 64-wide slice of the rank) whose A operand is B_all[slot, rows of the tile, slice].
+        if (tok_tile != cur_tok_tile) {
+          n_seg = distinct_slots<BN>(a, tok_tile * BN, p_tok, p_list);
+          cur_tok_tile = tok_tile;
+        }
+        if (lane == 0) {
+          int nn = n;
+          for (int sgi = 0; sgi < n_seg && ok; ++sgi) {
+            const int slot = p_list[sgi];
+            for (int sb = 0; sb < p.n_sub; ++sb, ++nn) {
+              const int s = nn % C::kWStages, round = nn / C::kWStages;
+              if (!mbar_wait(&empty_bar[s], (round & 1) ^ 1, &s_abort)) {
+                s_abort = 1;
+                atomicOr(p.status, 1);
+                ok = false;
+                break;
+              }
+              mbar_expect_tx(&full_bar[s], BM * rb);
+              tma_load_2d(w_ring + s * C::kWBytes, &map_b, sb * p.lora_sub, slot * a.out + row_tile * BM,
+                          &full_bar[s]);
+            }
+          }
+        }
+        n += n_seg * p.n_sub;
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      }
+    }
+  } else if (warp == 6) {
+    // ---- token-tile producer: lane 0 issues the x copies; all lanes build the LoRA B operands --------
     const bool stage_u = p.lora_mode == 2 && (size_t)BN * r_tot * sizeof(float) <= (size_t)kStageUMax;
     int it = rg.it0, n = 0, cur_tok_tile = -1, n_seg = 0;
     bool ok = true;
@@ -280,29 +443,25 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
       if (lane == 0) {
         int nn = n;
         for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++nn) {
-          const int s = nn % C::kStages, round = nn / C::kStages;
-          if (!mbar_wait(&empty_bar[s], (round & 1) ^ 1, &s_abort)) {
+          const int s = nn % C::kXStages, round = nn / C::kXStages;
+          if (!mbar_wait(&xempty_bar[s], (round & 1) ^ 1, &s_abort)) {
             s_abort = 1;
-            atomicOr(p.status, 1);
+            atomicOr(p.status, 16);
             ok = false;
             break;
           }
-          uint8_t* st = tiles + s * C::kStageBytes;
-          mbar_expect_tx(&full_bar[s], C::kStageBytes);
-          tma_load_2d(st, &map_w, kb * BK, row_tile * BM, &full_bar[s]);
-          tma_load_2d(st + BM * BK * 2, &map_x, kb * BK, tok_tile * BN, &full_bar[s]);
+          mbar_expect_tx(&xfull_bar[s], C::kXBytes);
+          tma_load_2d(x_ring + s * C::kXBytes, &map_x, kb * BK, tok_tile * BN, &xfull_bar[s]);
         }
       }
       n += sg.kb1 - sg.kb0;
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (ok && p.lora_mode == 2 && sg.kb1 == p.k_blocks) {
-        // The tile's last k-block is ours: append one stage per (adapter present in the token tile,
-        // 64-wide slice of the rank): A operand = B_all[slot, rows of the tile, slice] by TMA, B operand
-        // = scale * u of the tokens that use the adapter (zero rows for the others), written here in
-        // the swizzled K-major layout the MMA expects.
+        // B operand of a LoRA stage = scale * u of the tokens that use the adapter (zero rows for the
+        // others), written in the swizzled K-major layout the MMA expects.
         const int t0 = tok_tile * BN;
         if (tok_tile != cur_tok_tile) {
-          n_seg = distinct_slots<BN>(a, t0, p_tok, p_list);
+          n_seg = distinct_slots<BN>(a, t0, x_tok, x_list);
           if (stage_u) {
             const int n_valid = min(BN, a.T - t0) * r_tot;
             for (int i = lane; i < n_valid; i += 32) s_u[i] = a.u[(size_t)t0 * r_tot + i];
@@ -311,30 +470,28 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
           cur_tok_tile = tok_tile;
         }
         const int u_off = module_of(a, row_tile * BM) * a.r_max;
-        const int rb = p.lora_sub * 2;      // row bytes of a LoRA stage
         const int chunks = p.lora_sub / 8;  // 16-byte chunks per row
         for (int sgi = 0; sgi < n_seg && ok; ++sgi) {
-          const int slot = p_list[sgi];
+          const int slot = x_list[sgi];
           const float sc = a.scales[slot];
           for (int sb = 0; sb < p.n_sub; ++sb, ++n) {
-            const int s = n % C::kStages, round = n / C::kStages;
+            const int s = n % C::kXStages, round = n / C::kXStages;
             int w = 1;
-            if (lane == 0) w = mbar_wait(&empty_bar[s], (round & 1) ^ 1, &s_abort) ? 1 : 0;
+            if (lane == 0) w = mbar_wait(&xempty_bar[s], (round & 1) ^ 1, &s_abort) ? 1 : 0;
             w = __shfl_sync(0xffffffffu, w, 0);
             if (!w) {
               if (lane == 0) {
                 s_abort = 1;
-                atomicOr(p.status, 1);
+                atomicOr(p.status, 16);
               }
               ok = false;
               break;
             }
-            uint8_t* st = tiles + s * C::kStageBytes;
-            uint8_t* xt = st + BM * BK * 2;
+            uint8_t* xt = x_ring + s * C::kXBytes;
             for (int idx = lane; idx < BN * chunks; idx += 32) {
               const int nrow = idx / chunks, c = idx - nrow * chunks;
               uint4 val = make_uint4(0u, 0u, 0u, 0u);
-              if (p_tok[nrow] == slot) {
+              if (x_tok[nrow] == slot) {
                 const float* ur = (stage_u ? s_u + nrow * r_tot : a.u + (size_t)(t0 + nrow) * r_tot) + u_off +
                                   sb * p.lora_sub + c * 8;
                 float f[8];
@@ -347,17 +504,13 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
-            if (lane == 0) {
-              mbar_expect_tx(&full_bar[s], BM * rb);
-              tma_load_2d(st, &map_b, sb * p.lora_sub, slot * a.out + row_tile * BM, &full_bar[s]);
-            }
+            if (lane == 0) mbar_arrive(&xfull_bar[s]);
           }
         }
       }
     }
   } else if (warp == 1) {
     // ---- MMA issuer: lane 0 issues; all lanes count the LoRA stages of a token tile ---------------------
-    const LinearArgs& a = p.a;
     constexpr uint32_t idesc = make_idesc(BM, BN);
     int it = rg.it0, n = 0, j = 0, cur_tok_tile = -1, n_seg = 0;
     bool ok = true;
@@ -382,40 +535,29 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
           ok = false;
         }
         tc_fence_after();
-        for (int kb = sg.kb0; kb < sg.kb1 && ok; ++kb, ++nn) {
-          const int s = nn % C::kStages, round = nn / C::kStages;
-          if (!mbar_wait(&full_bar[s], round & 1, &s_abort)) {
+        const int n_w = sg.kb1 - sg.kb0;
+        for (int l = 0; l < n_w + n_lora && ok; ++l, ++nn) {
+          const int s = nn % C::kWStages, xs = nn % C::kXStages;
+          if (!mbar_wait(&full_bar[s], (nn / C::kWStages) & 1, &s_abort) ||
+              !mbar_wait(&xfull_bar[xs], (nn / C::kXStages) & 1, &s_abort)) {
             s_abort = 1;
             atomicOr(p.status, 2);
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint32_t wa = smem_u32(tiles + s * C::kStageBytes);
-          const uint64_t adesc = make_smem_desc(wa);
-          const uint64_t bdesc = make_smem_desc(wa + BM * BK * 2);
+          const uint32_t wa = smem_u32(w_ring + s * C::kWBytes), xa = smem_u32(x_ring + xs * C::kXBytes);
+          if (l < n_w) {
+            const uint64_t adesc = make_smem_desc(wa), bdesc = make_smem_desc(xa);
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k) {
-            // advancing 16 elements (32 bytes) along K inside the swizzle span = +2 in the address field
-            umma_bf16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > sg.kb0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < BK / 16; ++k)  // +16 elements (32 bytes) along K = +2 in the address field
+              umma_bf16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (l > 0 || k > 0) ? 1u : 0u);
+          } else {
+            const uint64_t adesc = make_smem_desc(wa, rb), bdesc = make_smem_desc(xa, rb);
+            for (int k = 0; k < p.lora_sub / 16; ++k) umma_bf16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, 1u);
           }
-          umma_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
-        }
-        const uint32_t rb = p.lora_sub * 2;
-        for (int l = 0; l < n_lora && ok; ++l, ++nn) {
-          const int s = nn % C::kStages, round = nn / C::kStages;
-          if (!mbar_wait(&full_bar[s], round & 1, &s_abort)) {
-            s_abort = 1;
-            atomicOr(p.status, 2);
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          const uint32_t wa = smem_u32(tiles + s * C::kStageBytes);
-          const uint64_t adesc = make_smem_desc(wa, rb);
-          const uint64_t bdesc = make_smem_desc(wa + BM * BK * 2, rb);
-          for (int k = 0; k < p.lora_sub / 16; ++k) umma_bf16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, 1u);
-          umma_commit(&empty_bar[s]);
+          umma_commit(&empty_bar[s]);    // both stages are free once these MMAs have read them
+          umma_commit(&xempty_bar[xs]);
         }
         if (ok) umma_commit(&acc_full[buf]);
       }
@@ -424,19 +566,16 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
       ++j;
     }
   } else {
-    // ---- epilogue warps: TMEM lane quarter = warp % 4 -------------------------------------------------
-    const LinearArgs& a = p.a;
+    // ---- epilogue warps 2..5: TMEM lane quarter = warp % 4 ------------------------------------------------
     const int q = warp & 3;
     const int etid = q * 32 + lane;           // 0..127 = row inside the tile
     const bool silu = (a.flags & MLORA_SILU_MUL) != 0;
-    const int r_tot = a.r_max * a.n_mod;
-    const bool simt_lora = p.lora_mode == 1;
+    constexpr bool simt_lora = SIMT_LORA;
     const bool stage_u = simt_lora && (size_t)BN * r_tot * sizeof(float) <= (size_t)kStageUMax;
     int staged_tok_tile = -1;
     int it = rg.it0, j = 0;
-    bool ok = true;
 
-    while (it < rg.it1 && ok) {
+    while (it < rg.it1) {
       const Segment sg = next_segment(p, it, rg.it1);
       const int row_tile = sg.tile % p.row_tiles, tok_tile = sg.tile / p.row_tiles;
       const int row = row_tile * BM + etid;
@@ -444,7 +583,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
       const int buf = j & 1;
       const bool full_seg = sg.kb0 == 0 && sg.kb1 == p.k_blocks;
 
-      // per-token LoRA operands of this token tile -> shared memory (once per token tile)
+      // per-token LoRA operands of this token tile -> shared memory (CUDA-core expand only)
       if (simt_lora && staged_tok_tile != tok_tile) {
         epi_bar_sync();  // previous users of the staging area are done
         for (int i = etid; i < BN; i += kEpiThreads) s_slots[i] = (t0 + i < a.T) ? a.slots[t0 + i] : -1;
@@ -456,42 +595,9 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
         staged_tok_tile = tok_tile;
       }
 
-      // Adds the LoRA expand, applies SiLU*up, stores.  v[i] = projection of (token t0+c0+i, row).
+      // Adds the CUDA-core LoRA expand if any, applies SiLU*up, stores.  v[i] = (token t0+c0+i, row).
       auto finish = [&](float (&v)[32], int c0) {
-        if (simt_lora && row < a.out) {
-          const int m = module_of(a, row);
-          int cur = -1, r = 0;
-          float sc = 0.f;
-          uint4 bq[8];
-#pragma unroll
-          for (int i = 0; i < C::kChunk; ++i) {
-            const int s = s_slots[c0 + i];
-            if (s < 0 || s >= a.n_adapters) continue;
-            if (s != cur) {  // rows of one adapter are usually adjacent (ordered batches): reuse B[s, row, :]
-              cur = s;
-              r = a.full_rank ? a.r_max : a.ranks[s];
-              sc = a.scales[s];
-              const bf16* b = a.B_all + ((size_t)s * a.out + row) * a.r_max;
-#pragma unroll
-              for (int g = 0; g < 8; ++g)
-                if (g * 8 < r) bq[g] = ld_cached(b + g * 8);
-            }
-            const float* ur = stage_u ? s_u + (c0 + i) * r_tot + m * a.r_max
-                                      : a.u + (size_t)(t0 + c0 + i) * r_tot + m * a.r_max;
-            float acc = 0.f;
-#pragma unroll
-            for (int g = 0; g < 8; ++g) {
-              if (g * 8 < r) {
-                float bf[8];
-                unpack8(bq[g], bf);
-#pragma unroll
-                for (int e = 0; e < 8; ++e)
-                  if (g * 8 + e < r) acc = fmaf(ur[g * 8 + e], bf[e], acc);
-              }
-            }
-            v[i] = fmaf(sc, acc, v[i]);
-          }
-        }
+        if (SIMT_LORA) simt_lora_expand<BN>(a, v, c0, t0, row, r_tot, stage_u, s_slots, s_u);
 #pragma unroll
         for (int i = 0; i < C::kChunk; ++i) {
           const int t = t0 + c0 + i;
@@ -656,10 +762,14 @@ template <int BN>
 int launch(const LinearArgs& a, const Plan& pl, void* work, cudaStream_t st) {
   using C = Cfg<BN>;
   CUtensorMap mw, mx;
-  int rc = make_map(&mw, a.W, a.out, a.in, a.in, BM);
+  int rc = make_map(&mx, a.x, a.T, a.in, a.ldx, BN);
   if (rc) return rc;
-  rc = make_map(&mx, a.x, a.T, a.in, a.ldx, BN);
-  if (rc) return rc;
+  if (a.flags & MLORA_W_PACKED) {
+    mw = mx;  // unused by the kernel
+  } else {
+    rc = make_map(&mw, a.W, a.out, a.in, a.in, BM);
+    if (rc) return rc;
+  }
   TcParams p;
   p.a = a;
   // LoRA expand: on the tensor cores when the rank pitch is 16/32/64/128 and every module boundary
@@ -687,23 +797,60 @@ int launch(const LinearArgs& a, const Plan& pl, void* work, cudaStream_t st) {
   p.row_tiles = pl.row_tiles;
   p.n_tiles = pl.row_tiles * pl.tok_tiles;
   p.per_cta = pl.per_cta;
+  p.prefetch = 0;  // measured: an L2 prefetch stream ahead of the ring slows the kernel down on B200
   p.status = (int32_t*)work;
   p.tickets = (int32_t*)((uint8_t*)work + kHeaderBytes);
   p.partials = (float*)((uint8_t*)work + kHeaderBytes + kMaxGrid * 4);
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(linear_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(linear_tc_kernel<BN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          C::kSmemBytes);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(linear_tc_kernel<BN, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               C::kSmemBytes);
     if (e != cudaSuccess) return fail(MLORA_ECUDA, "linear: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     attr_set = true;
   }
-  linear_tc_kernel<BN><<<pl.grid, kThreads, C::kSmemBytes, st>>>(mw, mx, mb, p);
+  if (p.lora_mode == 1)
+    linear_tc_kernel<BN, true><<<pl.grid, kThreads, C::kSmemBytes, st>>>(mw, mx, mb, p);
+  else
+    linear_tc_kernel<BN, false><<<pl.grid, kThreads, C::kSmemBytes, st>>>(mw, mx, mb, p);
   count_launch();
   MLORA_CHECK_LAUNCH("linear_tc_kernel");
   return MLORA_OK;
 }
 
+// Repacks W [out, in] into tiles [row_tile][k_block][128 rows][64 k] whose bytes are the
+// shared-memory image the MMA reads: row r of a tile at r*128 bytes, its 16-byte chunk c at
+// ((c ^ (r & 7)) * 16) (128-byte swizzle).  Rows / columns past the matrix are zero.
+__global__ void __launch_bounds__(256) pack_weight_kernel(const bf16* __restrict__ W, int out, int in, int k_blocks,
+                                                          uint4* __restrict__ Wp) {
+  const size_t tile = blockIdx.x;  // row_tile * k_blocks + kb
+  const int row_tile = (int)(tile / k_blocks), kb = (int)(tile % k_blocks);
+  for (int idx = threadIdx.x; idx < BM * 8; idx += blockDim.x) {
+    const int r = idx >> 3, c = idx & 7;
+    const int row = row_tile * BM + r, k = kb * BK + c * 8;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (row < out && k < in) v = *reinterpret_cast<const uint4*>(W + (size_t)row * in + k);  // in % 8 == 0
+    Wp[tile * (BM * 8) + r * 8 + (c ^ (r & 7))] = v;
+  }
+}
+
 }  // namespace
+
+size_t packed_weight_bytes(int out, int in) {
+  return (size_t)((out + BM - 1) / BM) * ((in + BK - 1) / BK) * (BM * BK * 2);
+}
+
+int launch_pack_weight(const void* W, int out, int in, void* Wp, cudaStream_t st) {
+  const int k_blocks = (in + BK - 1) / BK;
+  const long long tiles = (long long)((out + BM - 1) / BM) * k_blocks;
+  if (tiles > 2147483647ll) return fail(MLORA_ESIZE, "pack_weight: matrix too large");
+  pack_weight_kernel<<<(unsigned)tiles, 256, 0, st>>>((const bf16*)W, out, in, k_blocks, (uint4*)Wp);
+  count_launch();
+  MLORA_CHECK_LAUNCH("pack_weight_kernel");
+  return MLORA_OK;
+}
 
 bool linear_tc_supported(const LinearArgs& a) {
   // TMA needs 16-byte aligned bases and row pitches; everything else (ragged K, out, T) is handled by

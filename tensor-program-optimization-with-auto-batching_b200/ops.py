@@ -13,7 +13,7 @@ import torch
 from . import _lib
 from ._lib import check
 
-OUT_F32, SILU_MUL, FORCE_SIMT = 1, 2, 4
+OUT_F32, SILU_MUL, FORCE_SIMT, W_PACKED = 1, 2, 4, 8
 
 
 def _ptr(t):
@@ -107,11 +107,39 @@ def lora_shrink(x, stack: LoraStack, slots, out=None):
     return u
 
 
+class PackedWeight:
+    """W [out,in] in the tiled layout of ``mlora_pack_weight`` (see include/mlora.h)."""
+
+    def __init__(self, W):
+        _need_cuda(W)
+        if W.dtype != torch.bfloat16 or not W.is_contiguous():
+            raise ValueError("PackedWeight needs a contiguous bf16 matrix")
+        self.shape = tuple(W.shape)
+        self.dtype = W.dtype
+        n = _lib.lib().mlora_packed_weight_bytes(W.shape[0], W.shape[1])
+        self.data = torch.empty(n, dtype=torch.uint8, device=W.device)
+        check(_lib.lib().mlora_pack_weight(_ptr(W), W.shape[0], W.shape[1], _ptr(self.data), _stream()),
+              "mlora_pack_weight")
+
+    def data_ptr(self):
+        return self.data.data_ptr()
+
+    def numel(self):
+        return self.shape[0] * self.shape[1]
+
+    @property
+    def is_cuda(self):
+        return True
+
+
 def linear(x, W, stack: LoraStack = None, slots=None, u=None, flags: int = 0, out=None, use_workspace=True):
-    """y = x W^T (+ LoRA expand of ``u``) ; see ``mlora_linear`` in include/mlora.h."""
+    """y = x W^T (+ LoRA expand of ``u``) ; see ``mlora_linear`` in include/mlora.h.
+    ``W`` is a bf16 [out,in] tensor or a :class:`PackedWeight`."""
     _need_cuda(x, W)
     if x.dtype != torch.bfloat16 or W.dtype != torch.bfloat16:
         raise ValueError("mlora.linear needs bf16 x and W")
+    if isinstance(W, PackedWeight):
+        flags |= W_PACKED
     T, K = x.shape
     N = W.shape[0]
     cols = N // 2 if flags & SILU_MUL else N

@@ -402,3 +402,15 @@ def test_tensor_core_projection_shapes(ops, cuda, T, K, N):
     torch.testing.assert_close(y_tc.float().cpu(), want, atol=ATOL, rtol=RTOL)
     assert torch.equal(y_tc, y_tc2)  # split-K partials are summed in a fixed order
     torch.testing.assert_close(y_tc.float(), y_simt.float(), atol=ATOL, rtol=RTOL)
+
+
+@pytest.mark.parametrize("T,K,N", [(32, 4096, 4096), (33, 688, 256), (7, 1024, 200), (130, 512, 384)])
+def test_packed_weight_equals_row_major(ops, cuda, T, K, N):
+    """The pre-tiled weight layout is a pure re-arrangement: results are bit-identical."""
+    g = torch.Generator().manual_seed(K + N)
+    x = torch.randn(T, K, generator=g).bfloat16().to(cuda)
+    W = (torch.randn(N, K, generator=g) * 0.05).bfloat16().to(cuda)
+    y0 = ops.linear(x, W)
+    y1 = ops.linear(x, ops.PackedWeight(W))
+    assert torch.equal(y0, y1)
+    torch.testing.assert_close(y1.float().cpu(), x.float().cpu() @ W.float().cpu().t(), atol=ATOL, rtol=RTOL)
