@@ -33,6 +33,7 @@ extern "C" {
                                out/2 columns */
 #define MLORA_FORCE_SIMT 4  /* use the CUDA-core warp-per-row kernel whatever the shape */
 #define MLORA_W_PACKED 8    /* d_W is the tiled layout written by mlora_pack_weight */
+#define MLORA_B_PACKED 16   /* d_B_all is the tiled layout written by mlora_pack_lora_b */
 
 int mlora_version(void);
 const char* mlora_last_error(void);
@@ -107,6 +108,13 @@ size_t mlora_linear_workspace(int32_t T, int32_t in, int32_t out);
  * The reference transposes / stacks weights once at load as well
  * (tvm/llama_auto_batcher/compile_tvm.py:287-320).  Pass the result to mlora_linear with
  * MLORA_W_PACKED (tensor-core kernel only). */
+/* The same for an adapter stack: B_all [N, out, r_max] (r_max 16, 32, 64 or 128; for an interleaved
+ * gate/up stack pass the doubled pitch) -> tiles [slot][row tile][64-wide rank slice] of 128 rows,
+ * pre-swizzled, so each LoRA stage of the tensor-core expand is one bulk copy.  Pass the result to
+ * mlora_linear with MLORA_B_PACKED (needs tile-aligned module boundaries). */
+size_t mlora_packed_lora_b_bytes(int32_t n_adapters, int32_t out, int32_t r_max);
+int mlora_pack_lora_b(const void* d_B_all, int32_t n_adapters, int32_t out, int32_t r_max, void* d_Bp,
+                      void* stream);
 size_t mlora_packed_weight_bytes(int32_t out, int32_t in);
 int mlora_pack_weight(const void* d_W, int32_t out, int32_t in, void* d_Wp, void* stream);
 int mlora_linear(const void* d_x, int64_t ldx, const void* d_W, void* d_y, int64_t ldy, int32_t T,

@@ -22,6 +22,8 @@ PROTOTYPES = {
     "mlora_bucket_sort": (C.c_int, [_vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "mlora_lora_shrink": (C.c_int, [_vp, _i64, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp]),
     "mlora_linear_workspace": (_sz, [_i32, _i32, _i32]),
+    "mlora_packed_lora_b_bytes": (_sz, [_i32, _i32, _i32]),
+    "mlora_pack_lora_b": (C.c_int, [_vp, _i32, _i32, _i32, _vp, _vp]),
     "mlora_packed_weight_bytes": (_sz, [_i32, _i32]),
     "mlora_pack_weight": (C.c_int, [_vp, _i32, _i32, _vp, _vp]),
     "mlora_linear": (C.c_int, [_vp, _i64, _vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32,

@@ -65,7 +65,9 @@ extern "C" int mlora_linear(const void* d_x, int64_t ldx, const void* d_W, void*
   }
   if (T == 0) return MLORA_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  if (flags & MLORA_W_PACKED) {
+  if (flags & MLORA_B_PACKED)
+    MLORA_REQUIRE(d_u && !(flags & MLORA_FORCE_SIMT) && d_work, "linear: a packed B_all needs the tensor-core kernel");
+  if (flags & (MLORA_W_PACKED | MLORA_B_PACKED)) {
     MLORA_REQUIRE(!(flags & MLORA_FORCE_SIMT) && d_work && linear_tc_supported(a),
                   "linear: a packed weight needs the tensor-core kernel (scratch buffer, 16-byte aligned operands)");
     return launch_linear_tc(a, d_work, work_bytes, st);
@@ -84,4 +86,17 @@ extern "C" int mlora_pack_weight(const void* d_W, int32_t out, int32_t in, void*
   MLORA_REQUIRE(out > 0 && in > 0 && in % 8 == 0, "pack_weight: in must be a positive multiple of 8 (out=%d in=%d)", out, in);
   MLORA_REQUIRE(d_W && d_Wp && aligned16(d_W) && aligned16(d_Wp), "pack_weight: pointers must be non-null and 16-byte aligned");
   return launch_pack_weight(d_W, out, in, d_Wp, (cudaStream_t)stream);
+}
+
+extern "C" size_t mlora_packed_lora_b_bytes(int32_t n_adapters, int32_t out, int32_t r_max) {
+  if (n_adapters <= 0 || out <= 0 || r_max <= 0) return 0;
+  return packed_lora_b_bytes(n_adapters, out, r_max);
+}
+
+extern "C" int mlora_pack_lora_b(const void* d_B_all, int32_t n_adapters, int32_t out, int32_t r_max, void* d_Bp,
+                                 void* stream) {
+  MLORA_REQUIRE(n_adapters > 0 && out > 0, "pack_lora_b: bad sizes");
+  MLORA_REQUIRE(d_B_all && d_Bp && aligned16(d_B_all) && aligned16(d_Bp),
+                "pack_lora_b: pointers must be non-null and 16-byte aligned");
+  return launch_pack_lora_b(d_B_all, n_adapters, out, r_max, d_Bp, (cudaStream_t)stream);
 }

@@ -70,6 +70,8 @@ bool linear_tc_supported(const LinearArgs& a);
 size_t linear_tc_workspace(int T, int in, int out);
 int launch_linear_tc(const LinearArgs& a, void* work, size_t work_bytes, cudaStream_t st);
 size_t packed_weight_bytes(int out, int in);
+size_t packed_lora_b_bytes(int n_adapters, int out, int r_max);
+int launch_pack_lora_b(const void* B, int n_adapters, int out, int r_max, void* Bp, cudaStream_t st);
 int launch_pack_weight(const void* W, int out, int in, void* Wp, cudaStream_t st);
 
 }  // namespace mlora

@@ -267,7 +267,8 @@ struct Cfg {
   static constexpr int kXBytes = BN * BK * 2;    // token-tile stage
   static constexpr int kXStages = BN >= 64 ? 4 : 8;  // token tiles come from L2: a shallower ring is enough
   // barriers | 7 integer lists of BN (token slots / distinct adapters per role) | staged shrink outputs
-  static constexpr int kAuxBytes = 1024 + 7 * BN * 4 + kStageUMax;
+  static constexpr int kCacheBytes = 16 * 1024;  // LoRA B operands (scaled, masked shrink outputs) of a token tile
+  static constexpr int kAuxBytes = 1024 + 8 * BN * 4 + kStageUMax + kCacheBytes;
   static constexpr int kBudget = 227 * 1024 - 1024 /*alignment slack*/ - 64 /*static*/;
   static constexpr int kWStages0 = (kBudget - kAuxBytes - kXStages * kXBytes) / kWBytes;
   static constexpr int kWStages = kWStages0 > 12 ? 12 : kWStages0;  // weights come from HBM: as deep as fits
@@ -275,6 +276,12 @@ struct Cfg {
   static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;  // two accumulators
   static constexpr int kChunk = BN < 32 ? BN : 32;              // columns per TMEM load
 };
+
+// Do the LoRA B operands of a token tile with n_seg distinct adapters fit the shared-memory cache?
+template <int BN>
+__device__ __forceinline__ bool lora_cached(const TcParams& p, int n_seg) {
+  return n_seg * p.n_sub * BN * p.lora_sub * 2 <= Cfg<BN>::kCacheBytes;
+}
 
 // One CTA's share of the iteration space and the walk over its segments.
 struct Range {
@@ -308,14 +315,17 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
   extern __shared__ uint8_t smem_raw[];
   uint8_t* w_ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* x_ring = w_ring + C::kWStages * C::kWBytes;
-  uint8_t* aux = x_ring + C::kXStages * C::kXBytes;
+  uint8_t* s_cache = x_ring + C::kXStages * C::kXBytes;  // 1024-byte aligned like the rings
+  uint8_t* aux = s_cache + C::kCacheBytes;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(aux);  // [kWStages] weight stage filled
   uint64_t* empty_bar = full_bar + C::kWStages;           // [kWStages] weight stage consumed
   uint64_t* xfull_bar = empty_bar + C::kWStages;          // [kXStages]
   uint64_t* xempty_bar = xfull_bar + C::kXStages;         // [kXStages]
   uint64_t* acc_full = xempty_bar + C::kXStages;          // [2]
   uint64_t* acc_empty = acc_full + 2;                     // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint64_t* cache_full = acc_empty + 2;                   // LoRA operand cache written / all readers retired
+  uint64_t* cache_empty = cache_full + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(cache_empty + 1);
   int* s_slots = reinterpret_cast<int*>(aux + 1024);  // [BN] epilogue warps (CUDA-core expand)
   int* p_tok = s_slots + BN;                           // weight producer: slots of the token tile
   int* p_list = p_tok + BN;                            //                  distinct slots
@@ -323,9 +333,11 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
   int* m_list = m_tok + BN;
   int* x_tok = m_list + BN;                            // token-tile producer
   int* x_list = x_tok + BN;
-  float* s_u = reinterpret_cast<float*>(x_list + BN);  // [BN * r_tot] when it fits
+  float* x_scale = reinterpret_cast<float*>(x_list + BN);  // scale of each distinct slot
+  float* s_u = x_scale + BN;                           // [BN * r_tot] when it fits
   __shared__ int s_abort;
   __shared__ int s_last;
+  __shared__ int s_nseg0;  // distinct adapters of the CTA's first token tile (listed before the roles start)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const Range rg = cta_range(p, blockIdx.x);
@@ -347,12 +359,34 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
       mbar_init(&acc_full[b], 1);
       mbar_init(&acc_empty[b], 4);  // one arrival per epilogue warp
     }
+    mbar_init(cache_full, 1);
+    mbar_init(cache_empty, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     if (!(a.flags & MLORA_W_PACKED)) tma_prefetch_desc(&map_w);
     tma_prefetch_desc(&map_x);
-    if (p.lora_mode == 2) tma_prefetch_desc(&map_b);
+    if (p.lora_mode == 2 && !(a.flags & MLORA_B_PACKED)) tma_prefetch_desc(&map_b);
   }
   if (warp == 1) tmem_alloc(tmem_slot, C::kTmemCols);
+  // The per-token LoRA operands of the CTA's first token tile (decode: the only one) are fetched now,
+  // by warps that are idle at start-up, so that no pipeline role stops mid-stream for a global load.
+  const int tok_tile0 = (rg.it0 / p.k_blocks) / p.row_tiles;
+  const bool stage_u2 = p.lora_mode == 2 && (size_t)BN * r_tot * sizeof(float) <= (size_t)kStageUMax;
+  if (p.lora_mode == 2) {
+    if (warp == 2) {
+      const int ns = distinct_slots<BN>(a, tok_tile0 * BN, p_tok, p_list);
+      for (int i = lane; i < BN; i += 32) {
+        m_tok[i] = x_tok[i] = p_tok[i];
+        if (i < ns) {
+          m_list[i] = x_list[i] = p_list[i];
+          x_scale[i] = a.scales[p_list[i]];
+        }
+      }
+      if (lane == 0) s_nseg0 = ns;
+    } else if (warp >= 3 && warp <= 5 && stage_u2) {
+      const int n_valid = min(BN, a.T - tok_tile0 * BN) * r_tot;
+      for (int i = (warp - 3) * 32 + lane; i < n_valid; i += 96) s_u[i] = a.u[(size_t)tok_tile0 * BN * r_tot + i];
+    }
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -363,18 +397,9 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
     // ---- weight producer: lane 0 issues the copies; all lanes list the adapters of a token tile ------
     const bool packed = (a.flags & MLORA_W_PACKED) != 0;
     const uint8_t* wp = reinterpret_cast<const uint8_t*>(a.W);
-    int it = rg.it0, n = 0, cur_tok_tile = -1, n_seg = 0;
+    int it = rg.it0, n = 0, cur_tok_tile = tok_tile0, n_seg = s_nseg0;
     bool ok = true;
-    if (lane == 0 && packed) {
-      // Weights are read once, in a known order: ask L2 for the next kPrefetch tiles now, then one more
-      // per stage issued, so HBM requests in flight are not limited by the shared-memory ring.
-      for (int i = rg.it0; i < min(rg.it1, rg.it0 + kPrefetch); ++i) {
-        const int tile = i / p.k_blocks, kb = i - tile * p.k_blocks;
-        l2_prefetch(wp + ((size_t)(tile % p.row_tiles) * p.k_blocks + kb) * C::kWBytes, C::kWBytes);
-      }
-    }
     while (it < rg.it1 && ok) {
-      const int it_seg = it;
       const Segment sg = next_segment(p, it, rg.it1);
       const int row_tile = sg.tile % p.row_tiles, tok_tile = sg.tile / p.row_tiles;
       if (lane == 0) {
@@ -389,53 +414,57 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
           }
           uint8_t* st = w_ring + s * C::kWBytes;
           mbar_expect_tx(&full_bar[s], C::kWBytes);
-          if (packed) {  // one contiguous 16 KB tile, already in the swizzled K-major layout
+          if (packed)  // one contiguous 16 KB tile, already in the swizzled K-major layout
             bulk_load(st, wp + ((size_t)row_tile * p.k_blocks + kb) * C::kWBytes, C::kWBytes, &full_bar[s]);
-            const int ahead = it_seg + (kb - sg.kb0) + kPrefetch;
-            if (ahead < rg.it1) {
-              const int tile = ahead / p.k_blocks, kb2 = ahead - tile * p.k_blocks;
-              l2_prefetch(wp + ((size_t)(tile % p.row_tiles) * p.k_blocks + kb2) * C::kWBytes, C::kWBytes);
-            }
-          } else {
+          else
             tma_load_2d(st, &map_w, kb * BK, row_tile * BM, &full_bar[s]);
-          }
         }
       }
       n += sg.kb1 - sg.kb0;
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (ok && p.lora_mode == 2 && sg.kb1 == p.k_blocks) {
-        // The tile's last k-block is ours: one more stage per (adapter present in the token tile,
-        // 64-wide slice of the rank) whose A operand is B_all[slot, rows of the tile, slice].
+        // The tile's last k-block is ours: append the LoRA stages.  One stage per (adapter present in
+        // the token tile, 64-wide slice of the rank); its A operand is B_all[slot, rows of the tile, slice].
+        // When the B operands are cached in shared memory, up to `group` such slices share one ring slot.
         if (tok_tile != cur_tok_tile) {
           n_seg = distinct_slots<BN>(a, tok_tile * BN, p_tok, p_list);
           cur_tok_tile = tok_tile;
         }
+        const int n_l = n_seg * p.n_sub;
+        const int group = lora_cached<BN>(p, n_seg) ? C::kWBytes / (BM * (int)rb) : 1;
+        const int n_groups = (n_l + group - 1) / group;
         if (lane == 0) {
           int nn = n;
-          for (int sgi = 0; sgi < n_seg && ok; ++sgi) {
-            const int slot = p_list[sgi];
-            for (int sb = 0; sb < p.n_sub; ++sb, ++nn) {
-              const int s = nn % C::kWStages, round = nn / C::kWStages;
-              if (!mbar_wait(&empty_bar[s], (round & 1) ^ 1, &s_abort)) {
-                s_abort = 1;
-                atomicOr(p.status, 1);
-                ok = false;
-                break;
-              }
-              mbar_expect_tx(&full_bar[s], BM * rb);
-              tma_load_2d(w_ring + s * C::kWBytes, &map_b, sb * p.lora_sub, slot * a.out + row_tile * BM,
-                          &full_bar[s]);
+          for (int g = 0; g < n_groups && ok; ++g, ++nn) {
+            const int s = nn % C::kWStages, round = nn / C::kWStages;
+            if (!mbar_wait(&empty_bar[s], (round & 1) ^ 1, &s_abort)) {
+              s_abort = 1;
+              atomicOr(p.status, 1);
+              ok = false;
+              break;
+            }
+            const int l0 = g * group, l1 = min(n_l, l0 + group);
+            mbar_expect_tx(&full_bar[s], (l1 - l0) * BM * rb);
+            for (int l = l0; l < l1; ++l) {
+              const int slot = p_list[l / p.n_sub], sb = l % p.n_sub;
+              uint8_t* dst = w_ring + s * C::kWBytes + (l - l0) * BM * rb;
+              if (a.flags & MLORA_B_PACKED)  // one contiguous pre-swizzled tile
+                bulk_load(dst, reinterpret_cast<const uint8_t*>(a.B_all) +
+                                   (((size_t)slot * p.row_tiles + row_tile) * p.n_sub + sb) * (BM * rb),
+                          BM * rb, &full_bar[s]);
+              else
+                tma_load_2d(dst, &map_b, sb * p.lora_sub, slot * a.out + row_tile * BM, &full_bar[s]);
             }
           }
         }
-        n += n_seg * p.n_sub;
+        n += n_groups;
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       }
     }
   } else if (warp == 6) {
     // ---- token-tile producer: lane 0 issues the x copies; all lanes build the LoRA B operands --------
-    const bool stage_u = p.lora_mode == 2 && (size_t)BN * r_tot * sizeof(float) <= (size_t)kStageUMax;
-    int it = rg.it0, n = 0, cur_tok_tile = -1, n_seg = 0;
+    const bool stage_u = stage_u2;
+    int it = rg.it0, n = 0, cur_tok_tile = tok_tile0, n_seg = s_nseg0, cur_key = -1, n_build = 0;
     bool ok = true;
     while (it < rg.it1 && ok) {
       const Segment sg = next_segment(p, it, rg.it1);
@@ -458,10 +487,12 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (ok && p.lora_mode == 2 && sg.kb1 == p.k_blocks) {
         // B operand of a LoRA stage = scale * u of the tokens that use the adapter (zero rows for the
-        // others), written in the swizzled K-major layout the MMA expects.
+        // others), written in the swizzled K-major layout the MMA expects: once per (token tile, module)
+        // into the shared-memory cache when all of them fit, else stage by stage into the x ring.
         const int t0 = tok_tile * BN;
         if (tok_tile != cur_tok_tile) {
           n_seg = distinct_slots<BN>(a, t0, x_tok, x_list);
+          for (int i = lane; i < n_seg; i += 32) x_scale[i] = a.scales[x_list[i]];
           if (stage_u) {
             const int n_valid = min(BN, a.T - t0) * r_tot;
             for (int i = lane; i < n_valid; i += 32) s_u[i] = a.u[(size_t)t0 * r_tot + i];
@@ -469,12 +500,50 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
           }
           cur_tok_tile = tok_tile;
         }
-        const int u_off = module_of(a, row_tile * BM) * a.r_max;
+        const int mod = module_of(a, row_tile * BM);
+        const int u_off = mod * a.r_max;
         const int chunks = p.lora_sub / 8;  // 16-byte chunks per row
-        for (int sgi = 0; sgi < n_seg && ok; ++sgi) {
+        const bool cached = lora_cached<BN>(p, n_seg);
+        if (cached && tok_tile * 8 + mod == cur_key) continue;  // operands already in the cache
+        if (cached) {
+          int w = 1;
+          if (lane == 0) w = mbar_wait(cache_empty, (n_build & 1) ^ 1, &s_abort) ? 1 : 0;
+          w = __shfl_sync(0xffffffffu, w, 0);
+          if (!w) {
+            if (lane == 0) {
+              s_abort = 1;
+              atomicOr(p.status, 32);
+            }
+            break;
+          }
+        }
+        if (cached) {
+          // zero the tiles, then drop each token's scaled shrink output into the tile of its adapter
+          const int n_vec = n_seg * p.n_sub * BN * (int)rb / 16;
+          for (int i = lane; i < n_vec; i += 32) reinterpret_cast<uint4*>(s_cache)[i] = make_uint4(0u, 0u, 0u, 0u);
+          __syncwarp();
+          const int per_row = chunks * p.n_sub;
+          for (int idx = lane; idx < BN * per_row; idx += 32) {
+            const int nrow = idx / per_row, rem = idx - nrow * per_row;
+            const int sb = rem / chunks, c = rem - sb * chunks;
+            const int slot = x_tok[nrow];
+            if (slot < 0) continue;
+            int sgi = 0;
+            while (x_list[sgi] != slot) ++sgi;  // slot is in the list by construction
+            const float sc = x_scale[sgi];
+            const float* ur = (stage_u ? s_u + nrow * r_tot : a.u + (size_t)(t0 + nrow) * r_tot) + u_off +
+                              sb * p.lora_sub + c * 8;
+            float f[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[e] = ur[e] * sc;
+            const int sw = rb == 128 ? (nrow & 7) : rb == 64 ? ((nrow >> 1) & 3) : ((nrow >> 2) & 1);
+            *reinterpret_cast<uint4*>(s_cache + (sgi * p.n_sub + sb) * BN * rb + nrow * rb + ((c ^ sw) << 4)) = pack8(f);
+          }
+        }
+        for (int sgi = 0; sgi < n_seg && ok && !cached; ++sgi) {
           const int slot = x_list[sgi];
-          const float sc = a.scales[slot];
-          for (int sb = 0; sb < p.n_sub; ++sb, ++n) {
+          const float sc = x_scale[sgi];
+          for (int sb = 0; sb < p.n_sub; ++sb) {
             const int s = n % C::kXStages, round = n / C::kXStages;
             int w = 1;
             if (lane == 0) w = mbar_wait(&xempty_bar[s], (round & 1) ^ 1, &s_abort) ? 1 : 0;
@@ -505,63 +574,116 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&xfull_bar[s]);
+            ++n;
           }
+        }
+        if (cached && ok) {
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive(cache_full);
+          cur_key = tok_tile * 8 + mod;
+          ++n_build;
         }
       }
     }
   } else if (warp == 1) {
     // ---- MMA issuer: lane 0 issues; all lanes count the LoRA stages of a token tile ---------------------
     constexpr uint32_t idesc = make_idesc(BM, BN);
-    int it = rg.it0, n = 0, j = 0, cur_tok_tile = -1, n_seg = 0;
+    int it = rg.it0, nw = 0, nx = 0, j = 0, cur_tok_tile = tok_tile0, n_seg = s_nseg0, cur_key = -1, n_build = 0;
     bool ok = true;
     while (it < rg.it1 && ok) {
       const Segment sg = next_segment(p, it, rg.it1);
-      const int tok_tile = sg.tile / p.row_tiles;
+      const int row_tile = sg.tile % p.row_tiles, tok_tile = sg.tile / p.row_tiles;
       const int buf = j & 1;
       const uint32_t d_tmem = tmem_base + buf * BN;
-      int n_lora = 0;
+      int n_l = 0, group = 1;
+      bool cached = false, new_build = false;
       if (p.lora_mode == 2 && sg.kb1 == p.k_blocks) {
         if (tok_tile != cur_tok_tile) {
           n_seg = distinct_slots<BN>(a, tok_tile * BN, m_tok, m_list);
           cur_tok_tile = tok_tile;
         }
-        n_lora = n_seg * p.n_sub;
+        n_l = n_seg * p.n_sub;
+        cached = lora_cached<BN>(p, n_seg);
+        if (cached) {
+          group = C::kWBytes / (BM * (int)rb);
+          const int key = tok_tile * 8 + module_of(a, row_tile * BM);
+          new_build = key != cur_key;
+          cur_key = key;
+        }
       }
+      const int n_groups = (n_l + group - 1) / group;
+      const int n_w = sg.kb1 - sg.kb0;
       if (lane == 0) {
-        int nn = n;
+        int w_i = nw, x_i = nx;
         if (!mbar_wait(&acc_empty[buf], ((j >> 1) & 1) ^ 1, &s_abort)) {
           s_abort = 1;
           atomicOr(p.status, 8);
           ok = false;
         }
         tc_fence_after();
-        const int n_w = sg.kb1 - sg.kb0;
-        for (int l = 0; l < n_w + n_lora && ok; ++l, ++nn) {
-          const int s = nn % C::kWStages, xs = nn % C::kXStages;
-          if (!mbar_wait(&full_bar[s], (nn / C::kWStages) & 1, &s_abort) ||
-              !mbar_wait(&xfull_bar[xs], (nn / C::kXStages) & 1, &s_abort)) {
+        for (int l = 0; l < n_w && ok; ++l, ++w_i, ++x_i) {
+          const int s = w_i % C::kWStages, xs = x_i % C::kXStages;
+          if (!mbar_wait(&full_bar[s], (w_i / C::kWStages) & 1, &s_abort) ||
+              !mbar_wait(&xfull_bar[xs], (x_i / C::kXStages) & 1, &s_abort)) {
             s_abort = 1;
             atomicOr(p.status, 2);
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint32_t wa = smem_u32(w_ring + s * C::kWBytes), xa = smem_u32(x_ring + xs * C::kXBytes);
-          if (l < n_w) {
-            const uint64_t adesc = make_smem_desc(wa), bdesc = make_smem_desc(xa);
+          const uint64_t adesc = make_smem_desc(smem_u32(w_ring + s * C::kWBytes));
+          const uint64_t bdesc = make_smem_desc(smem_u32(x_ring + xs * C::kXBytes));
 #pragma unroll
-            for (int k = 0; k < BK / 16; ++k)  // +16 elements (32 bytes) along K = +2 in the address field
-              umma_bf16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (l > 0 || k > 0) ? 1u : 0u);
-          } else {
-            const uint64_t adesc = make_smem_desc(wa, rb), bdesc = make_smem_desc(xa, rb);
+          for (int k = 0; k < BK / 16; ++k)  // +16 elements (32 bytes) along K = +2 in the address field
+            umma_bf16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (l > 0 || k > 0) ? 1u : 0u);
+          umma_commit(&empty_bar[s]);  // both stages are free once these MMAs have read them
+          umma_commit(&xempty_bar[xs]);
+        }
+        if (cached && new_build && ok) {
+          // every MMA that read the previous cache contents has been issued: let the builder overwrite
+          // them once those MMAs retire, then wait for the new contents
+          if (n_build > 0) umma_commit(cache_empty);
+          if (!mbar_wait(cache_full, n_build & 1, &s_abort)) {
+            s_abort = 1;
+            atomicOr(p.status, 64);
+            ok = false;
+          }
+          tc_fence_after();
+        }
+        for (int g = 0; g < n_groups && ok; ++g, ++w_i) {
+          const int s = w_i % C::kWStages;
+          int xs = 0;
+          bool got = mbar_wait(&full_bar[s], (w_i / C::kWStages) & 1, &s_abort);
+          if (got && !cached) {
+            xs = x_i % C::kXStages;
+            got = mbar_wait(&xfull_bar[xs], (x_i / C::kXStages) & 1, &s_abort);
+          }
+          if (!got) {
+            s_abort = 1;
+            atomicOr(p.status, 2);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const int l0 = g * group, l1 = min(n_l, l0 + group);
+          for (int l = l0; l < l1; ++l) {
+            const uint64_t adesc = make_smem_desc(smem_u32(w_ring + s * C::kWBytes + (l - l0) * BM * rb), rb);
+            const uint64_t bdesc = make_smem_desc(
+                cached ? smem_u32(s_cache + l * BN * rb) : smem_u32(x_ring + xs * C::kXBytes), rb);
             for (int k = 0; k < p.lora_sub / 16; ++k) umma_bf16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, 1u);
           }
-          umma_commit(&empty_bar[s]);    // both stages are free once these MMAs have read them
-          umma_commit(&xempty_bar[xs]);
+          umma_commit(&empty_bar[s]);
+          if (!cached) {
+            umma_commit(&xempty_bar[xs]);
+            ++x_i;
+          }
         }
         if (ok) umma_commit(&acc_full[buf]);
       }
-      n += (sg.kb1 - sg.kb0) + n_lora;
+      nw += n_w + n_groups;
+      nx += n_w + (cached ? 0 : n_groups);
+      if (cached && new_build) ++n_build;
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       ++j;
     }
@@ -786,9 +908,13 @@ int launch(const LinearArgs& a, const Plan& pl, void* work, cudaStream_t st) {
       p.lora_mode = 2;
       p.lora_sub = a.r_max < 64 ? a.r_max : 64;
       p.n_sub = a.r_max / p.lora_sub;
-      rc = make_map(&mb, a.B_all, (long long)a.n_adapters * a.out, a.r_max, a.r_max, BM, p.lora_sub);
-      if (rc) return rc;
+      if (!(a.flags & MLORA_B_PACKED)) {
+        rc = make_map(&mb, a.B_all, (long long)a.n_adapters * a.out, a.r_max, a.r_max, BM, p.lora_sub);
+        if (rc) return rc;
+      }
     } else {
+      if (a.flags & MLORA_B_PACKED)
+        return fail(MLORA_EINVAL, "linear: a packed B_all needs rank pitch 16/32/64/128 and tile-aligned modules");
       if (a.r_max > 64) return fail(MLORA_EINVAL, "linear: rank pitch %d needs tile-aligned modules", a.r_max);
       p.lora_mode = 1;
     }
@@ -836,7 +962,45 @@ __global__ void __launch_bounds__(256) pack_weight_kernel(const bf16* __restrict
   }
 }
 
+// Repacks B_all [N, out, r_max] into tiles [slot][row_tile][sub-block][128 rows][lora_sub] whose bytes
+// are the shared-memory image of a LoRA stage's A operand: row r at r*rb bytes (rb = 2*lora_sub), its
+// 16-byte chunk c at ((c ^ swizzle(r)) * 16), swizzle span = rb.  Rows past `out` are zero.
+__global__ void __launch_bounds__(256) pack_lora_b_kernel(const bf16* __restrict__ B, int out, int r_max,
+                                                          int row_tiles, int lora_sub, int n_sub,
+                                                          uint4* __restrict__ Bp) {
+  const size_t tile = blockIdx.x;  // (slot * row_tiles + row_tile) * n_sub + sb
+  const int sb = (int)(tile % n_sub);
+  const size_t sr = tile / n_sub;
+  const int row_tile = (int)(sr % row_tiles), slot = (int)(sr / row_tiles);
+  const int chunks = lora_sub / 8, rb = lora_sub * 2;
+  for (int idx = threadIdx.x; idx < BM * chunks; idx += blockDim.x) {
+    const int r = idx / chunks, c = idx - r * chunks;
+    const int row = row_tile * BM + r;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (row < out) v = *reinterpret_cast<const uint4*>(B + ((size_t)slot * out + row) * r_max + sb * lora_sub + c * 8);
+    const int sw = rb == 128 ? (r & 7) : rb == 64 ? ((r >> 1) & 3) : ((r >> 2) & 1);
+    Bp[tile * (BM * chunks) + r * chunks + (c ^ sw)] = v;
+  }
+}
+
 }  // namespace
+
+size_t packed_lora_b_bytes(int n_adapters, int out, int r_max) {
+  return (size_t)n_adapters * ((out + BM - 1) / BM) * BM * r_max * 2;
+}
+
+int launch_pack_lora_b(const void* B, int n_adapters, int out, int r_max, void* Bp, cudaStream_t st) {
+  if (!(r_max == 16 || r_max == 32 || r_max == 64 || r_max == 128))
+    return fail(MLORA_EINVAL, "pack_lora_b: rank pitch must be 16, 32, 64 or 128 (got %d)", r_max);
+  const int lora_sub = r_max < 64 ? r_max : 64, n_sub = r_max / lora_sub;
+  const int row_tiles = (out + BM - 1) / BM;
+  const long long tiles = (long long)n_adapters * row_tiles * n_sub;
+  if (tiles > 2147483647ll) return fail(MLORA_ESIZE, "pack_lora_b: stack too large");
+  pack_lora_b_kernel<<<(unsigned)tiles, 256, 0, st>>>((const bf16*)B, out, r_max, row_tiles, lora_sub, n_sub, (uint4*)Bp);
+  count_launch();
+  MLORA_CHECK_LAUNCH("pack_lora_b_kernel");
+  return MLORA_OK;
+}
 
 size_t packed_weight_bytes(int out, int in) {
   return (size_t)((out + BM - 1) / BM) * ((in + BK - 1) / BK) * (BM * BK * 2);

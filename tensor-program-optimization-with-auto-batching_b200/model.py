@@ -58,8 +58,11 @@ class PackedLlama:
     ``init_peft_weights/lora_weights.py:18-23``), ``scales[i]`` = alpha/r of adapter i.
     Adapter ``i`` occupies slot ``i`` of every stack."""
 
-    def __init__(self, cfg, weights, adapters=(), scales=(), device="cuda", n_layers=None):
+    def __init__(self, cfg, weights, adapters=(), scales=(), device="cuda", n_layers=None, pack=True):
+        """pack=True stores every projection matrix and adapter B stack in the pre-tiled layouts of
+        mlora_pack_weight / mlora_pack_lora_b (one bulk copy per pipeline stage)."""
         self.cfg = dict(cfg)
+        self.pack = pack
         self.device = torch.device(device)
         c = self.cfg
         self.H, self.I, self.V = c["hidden_size"], c["intermediate_size"], c["vocab_size"]
@@ -71,7 +74,7 @@ class PackedLlama:
         bf = lambda t: t.to(device=self.device, dtype=torch.bfloat16).contiguous()
         self.embed = bf(weights["model.embed_tokens.weight"])
         self.norm = bf(weights["model.norm.weight"])
-        self.lm_head = bf(weights["lm_head.weight"])
+        self.lm_head = ops.PackedWeight(bf(weights["lm_head.weight"])) if pack else bf(weights["lm_head.weight"])
         self.n_adapters = len(adapters)
         ranks = []
         for ad in adapters:
@@ -86,12 +89,13 @@ class PackedLlama:
         for l in range(self.L):
             p = f"model.layers.{l}."
             w = lambda n: weights[p + n + ".weight"]
+            pk = lambda t: ops.PackedWeight(bf(t)) if pack else bf(t)
             lw = LayerWeights(
                 ln1=bf(w("input_layernorm")), ln2=bf(w("post_attention_layernorm")),
-                w_qkv=bf(torch.cat([w("self_attn.q_proj"), w("self_attn.k_proj"), w("self_attn.v_proj")], 0)),
-                w_o=bf(w("self_attn.o_proj")),
-                w_gu=bf(interleave_gate_up(w("mlp.gate_proj"), w("mlp.up_proj"))),
-                w_down=bf(w("mlp.down_proj")))
+                w_qkv=pk(torch.cat([w("self_attn.q_proj"), w("self_attn.k_proj"), w("self_attn.v_proj")], 0)),
+                w_o=pk(w("self_attn.o_proj")),
+                w_gu=pk(interleave_gate_up(w("mlp.gate_proj"), w("mlp.up_proj"))),
+                w_down=pk(w("mlp.down_proj")))
             if adapters:
                 self._pack_lora(l, lw, adapters)
             self.layers.append(lw)
@@ -129,7 +133,11 @@ class PackedLlama:
             else:
                 B_all = torch.cat(B_parts, 1)
             offs = tuple(int(x) for x in np.cumsum([0] + list(outs)))
-            return LoraStack(A_all, B_all.contiguous(), self.ranks, self.scales, r_max, n_mod, offs)
+            st = LoraStack(A_all, B_all.contiguous(), self.ranks, self.scales, r_max, n_mod, offs)
+            st.bytes_per_adapter = 2 * (A_all[0].numel() + sum(o for o in outs) * r_max)
+            if self.pack and all(o % 128 == 0 for o in offs[1:-1]):
+                st.pack_b()
+            return st
 
         for key, st in (("qkv", build("self_attn", ("q_proj", "k_proj", "v_proj"), (qd, kvd, kvd), self.H)),
                         ("o", build("self_attn", ("o_proj",), (self.H,), qd)),
@@ -149,8 +157,8 @@ class PackedLlama:
         n = 0
         for lw in self.layers:
             for st in lw.lora.values():
-                n += st.A_all[0].numel() + st.B_all[0].numel()
-        return 2 * n
+                n += st.bytes_per_adapter
+        return n
 
 
 class Engine:
@@ -179,6 +187,7 @@ class Engine:
         self.row_slot = torch.zeros(T, dtype=torch.int32, device=dev)
         self.row_pos = torch.zeros(T, dtype=torch.int32, device=dev)
         self.last_rows = torch.zeros(T, dtype=torch.int32, device=dev)
+        self.iota = torch.arange(T, dtype=torch.int32, device=dev)
         self.xn_last = torch.zeros(T, m.H, **bf)
         # scratch sized for the largest projection of this model at max_rows
         lib = ops._lib.lib()
@@ -198,16 +207,19 @@ class Engine:
             return ops.linear(x, W, stack, slots, u=u, flags=flags, out=out)
         return ops.linear(x, W, flags=flags, out=out)
 
-    def forward(self, T: int, fused_append: bool, use_lora: bool = True, lm_rows=None, n_lm=None):
+    def forward(self, T: int, fused_append: bool, use_lora: bool = True, lm_rows=None, n_lm=None, hidden=None):
         """One pass over the T rows staged in self.tokens / self.slots / self.row_slot /
         self.row_pos.  Logits (fp32) land in self.logits[:n_lm], greedy tokens in self.next_tok.
         ``lm_rows`` (device int32 [n_lm]) selects the rows that get logits (prefill: last token of
-        each sequence); None = every row."""
+        each sequence); None = every row.  ``hidden`` (bf16 [T,H]) replaces the embedding lookup."""
         m, kv = self.m, self.kv
         tok, slots = self.tokens[:T], (self.slots[:T] if (use_lora and m.n_adapters) else None)
         row_slot, row_pos = self.row_slot[:T], self.row_pos[:T]
         res, xn, qkv, attn, y, act = self.res[:T], self.xn[:T], self.qkv[:T], self.attn[:T], self.y[:T], self.act[:T]
-        ops.embed(tok, m.embed, res=res)
+        if hidden is None:
+            ops.embed(tok, m.embed, res=res)
+        else:  # hidden states handed in by the caller (the VM's separate "embed" function): bf16 [T,H] -> fp32 residual
+            ops.embed(self.iota[:T], hidden, res=res)
         delta = None
         for l, lw in enumerate(m.layers):
             ops.residual_rmsnorm(delta, res, lw.ln1, m.eps, out=xn)

@@ -13,7 +13,7 @@ import torch
 from . import _lib
 from ._lib import check
 
-OUT_F32, SILU_MUL, FORCE_SIMT, W_PACKED = 1, 2, 4, 8
+OUT_F32, SILU_MUL, FORCE_SIMT, W_PACKED, B_PACKED = 1, 2, 4, 8, 16
 
 
 def _ptr(t):
@@ -95,6 +95,19 @@ class LoraStack:
     r_max: int
     n_mod: int = 1
     mod_offsets: tuple = None
+    b_packed: bool = False   # B_all holds the tiled layout of mlora_pack_lora_b (uint8 buffer)
+    n_out: int = 0           # output features (needed once B_all is packed)
+
+    def pack_b(self, interleaved: bool = False):
+        """Replace B_all by its pre-tiled form (tensor-core expand only; modules must be tile aligned)."""
+        if self.b_packed:
+            return self
+        N, out, pitch = self.B_all.shape
+        n = _lib.lib().mlora_packed_lora_b_bytes(N, out, pitch)
+        buf = torch.empty(n, dtype=torch.uint8, device=self.B_all.device)
+        check(_lib.lib().mlora_pack_lora_b(_ptr(self.B_all), N, out, pitch, _ptr(buf), _stream()), "mlora_pack_lora_b")
+        self.B_all, self.b_packed, self.n_out = buf, True, out
+        return self
 
 
 def lora_shrink(x, stack: LoraStack, slots, out=None):
@@ -140,6 +153,8 @@ def linear(x, W, stack: LoraStack = None, slots=None, u=None, flags: int = 0, ou
         raise ValueError("mlora.linear needs bf16 x and W")
     if isinstance(W, PackedWeight):
         flags |= W_PACKED
+    if stack is not None and stack.b_packed:
+        flags |= B_PACKED
     T, K = x.shape
     N = W.shape[0]
     cols = N // 2 if flags & SILU_MUL else N

@@ -414,3 +414,20 @@ def test_packed_weight_equals_row_major(ops, cuda, T, K, N):
     y1 = ops.linear(x, ops.PackedWeight(W))
     assert torch.equal(y0, y1)
     torch.testing.assert_close(y1.float().cpu(), x.float().cpu() @ W.float().cpu().t(), atol=ATOL, rtol=RTOL)
+
+
+@pytest.mark.parametrize("T,r", [(32, 16), (9, 32), (70, 64)])
+def test_packed_lora_stack_equals_row_major(ops, cuda, T, r):
+    """Pre-tiled B stacks are a pure re-arrangement of B_all: bit-identical results."""
+    g = torch.Generator().manual_seed(r)
+    K, N, n_ad = 256, 384, 5
+    x = torch.randn(T, K, generator=g).bfloat16().to(cuda)
+    W = (torch.randn(N, K, generator=g) * 0.05).bfloat16().to(cuda)
+    A = (torch.randn(n_ad, 3 * r, K, generator=g) * 0.05).bfloat16()
+    B = (torch.randn(n_ad, N, r, generator=g) * 0.05).bfloat16()
+    slots = torch.randint(-1, n_ad, (T,), generator=g).int().to(cuda)
+    st = _stack(ops, A, B, [r] * n_ad, [1.5] * n_ad, cuda, 3, (0, 128, 256, 384))
+    y0 = ops.linear(x, W, st, slots)
+    st2 = _stack(ops, A, B, [r] * n_ad, [1.5] * n_ad, cuda, 3, (0, 128, 256, 384)).pack_b()
+    y1 = ops.linear(x, ops.PackedWeight(W), st2, slots)
+    assert torch.equal(y0, y1)
