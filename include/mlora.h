@@ -175,6 +175,30 @@ int mlora_paged_attention(const void* d_qkv, int64_t ld, void* d_k_pages, void* 
                           int32_t fused_append, void* d_out, int64_t ld_out, int32_t n_splits,
                           void* d_work, size_t work_bytes, void* stream);
 
+/* mlora_paged_attention_static: the same operation for callers that must not allocate.
+ * (No counterpart in the reference project; added for embedders of this library.)
+ * Some hosts of this code hand out all device memory themselves at start-up -- a serving runtime
+ * with a fixed arena, or a plugin loaded into a process whose allocator belongs to someone else --
+ * and their request path may not call cudaMalloc (it can stall the whole device, and the memory may
+ * simply all be spoken for).  For them the split-KV partial results go into a 16 MiB array that is
+ * part of the library image (mlora_paged_attention_static_max_bytes()); each GPU that loads the
+ * library holds that array until the process ends.  The call allocates and frees nothing.
+ *  - The first call on each device looks up the array's device address (one cudaGetSymbolAddress, with
+ *    that device current) and remembers it; make that first call before any stream capture starts.
+ *  - n_splits > 1 whose partials (T * Hq * n_splits * (D+2) * 4 bytes) exceed the array is rejected with
+ *    MLORA_ESIZE; n_splits <= 0 picks a split count that fits.
+ *  - All calls on a device share the one array, and it keeps whatever the previous call left in it.
+ *    Nothing in it needs clearing between calls (every partial is written before it is read), but two
+ *    calls that overlap on the GPU (different streams) would overwrite each other: serialise them.
+ * Arguments as mlora_paged_attention, without d_work / work_bytes. */
+size_t mlora_paged_attention_static_max_bytes(void);
+int mlora_paged_attention_static(const void* d_qkv, int64_t ld, void* d_k_pages, void* d_v_pages,
+                                 const int32_t* d_block_table, int32_t max_pages,
+                                 const int32_t* d_row_slot, const int32_t* d_row_pos, int32_t T,
+                                 int32_t Hq, int32_t Hkv, int32_t D, int32_t page_size,
+                                 float rope_theta, int32_t fused_append, void* d_out, int64_t ld_out,
+                                 int32_t n_splits, void* stream);
+
 /* ---- decode-step bookkeeping on the device (keeps a whole step inside one CUDA graph) ----------
  * For each live row b: slot = d_row_slot[b]; d_row_pos[b] = d_seq_lens[slot]; d_seq_lens[slot] += 1.
  * What kv_state_begin_forward(kv, seq_ids, [1]*B) does on the host in the reference

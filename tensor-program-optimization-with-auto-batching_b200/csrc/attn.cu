@@ -8,6 +8,7 @@
 // group with xor-shuffles; every lane group keeps its own online-softmax state (m, l, acc[8]);
 // groups, warps and splits are merged at the end.
 #include <cmath>
+#include <mutex>
 
 #include "common.cuh"
 
@@ -381,4 +382,65 @@ extern "C" int mlora_paged_attention(const void* d_qkv, int64_t ld, void* d_k_pa
   }
   MLORA_CHECK_LAUNCH("paged_attn_kernel");
   return MLORA_OK;
+}
+
+// ---- allocation-free variant -------------------------------------------------------------------------
+// Scratch for the split-KV partial results lives in the library image itself, so a caller that is not
+// allowed to allocate device memory can still use the split-KV path.  Every GPU that loads the library
+// carries this array until the process exits.
+namespace {
+constexpr size_t kStaticScratchBytes = (size_t)16 << 20;  // 16 MiB
+static __device__ __align__(256) unsigned char g_attn_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mu;
+void* g_static_ptr[kMaxDevices] = {};
+bool g_static_ready[kMaxDevices] = {};
+
+// Device address of the array on the current device.  In host code the array's name is only a handle,
+// not an address a kernel could use; the runtime has to translate it, once per device, with that
+// device current.
+int static_scratch_for_current_device(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(MLORA_ECUDA, "paged_attention_static: cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices)
+    return fail(MLORA_EINVAL, "paged_attention_static: device ordinal %d not supported (limit %d)", dev, kMaxDevices);
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  if (!g_static_ready[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_attn_static_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return fail(MLORA_ECUDA, "paged_attention_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    g_static_ptr[dev] = p;
+    g_static_ready[dev] = true;
+  }
+  *out = g_static_ptr[dev];
+  return MLORA_OK;
+}
+}  // namespace
+
+extern "C" size_t mlora_paged_attention_static_max_bytes(void) { return kStaticScratchBytes; }
+
+extern "C" int mlora_paged_attention_static(const void* d_qkv, int64_t ld, void* d_k_pages, void* d_v_pages,
+                                            const int32_t* d_block_table, int32_t max_pages,
+                                            const int32_t* d_row_slot, const int32_t* d_row_pos, int32_t T,
+                                            int32_t Hq, int32_t Hkv, int32_t D, int32_t page_size, float rope_theta,
+                                            int32_t fused_append, void* d_out, int64_t ld_out, int32_t n_splits,
+                                            void* stream) {
+  if (n_splits > 1) {
+    const size_t need = mlora_paged_attention_workspace(T, Hq, D, n_splits);
+    if (need > kStaticScratchBytes)
+      return fail(MLORA_ESIZE,
+                  "paged_attention_static: %d rows x %d heads x %d splits need %zu bytes of scratch, the built-in "
+                  "array holds %zu; use fewer splits or rows, or mlora_paged_attention with your own buffer",
+                  T, Hq, n_splits, need, kStaticScratchBytes);
+  }
+  void* scratch = nullptr;
+  int rc = static_scratch_for_current_device(&scratch);
+  if (rc) return rc;
+  // n_splits <= 0: the library picks the split count and lowers it until the partials fit the array
+  return mlora_paged_attention(d_qkv, ld, d_k_pages, d_v_pages, d_block_table, max_pages, d_row_slot, d_row_pos, T, Hq,
+                               Hkv, D, page_size, rope_theta, fused_append, d_out, ld_out, n_splits, scratch,
+                               kStaticScratchBytes, stream);
 }
