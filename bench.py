@@ -202,7 +202,18 @@ def run_ours(args, rank, world, local_rank):
 
     # ---- prefill through the product path (untimed set-up) ---------------------------------------------
     t0 = time.perf_counter()
-    _, first_tok = eng.prefill(sids, prompts, slots)
+    if args.skip_prefill:
+        g = torch.Generator(device=dev).manual_seed(synth.SEED_TOKENS)
+        for s in sids:
+            kv.reserve(s, PROMPT_LEN)
+        kv.pages.copy_(torch.randn(kv.pages.shape, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+                       if kv.pages.numel() < (1 << 28) else
+                       torch.randn(kv.pages.shape, generator=g, device=dev, dtype=torch.bfloat16))
+        kv._len_host[:B] = PROMPT_LEN
+        kv.seq_lens[:B] = PROMPT_LEN
+        first_tok = torch.from_numpy(np.asarray([p[-1] for p in prompts], dtype=np.int32)).to(dev)
+    else:
+        _, first_tok = eng.prefill(sids, prompts, slots)
     torch.cuda.synchronize()
     prefill_s = time.perf_counter() - t0
 
@@ -382,6 +393,44 @@ def kernel_rooflines(eng, pm, kv, B, slots, ops, torch, ctx, n_uniq, peak, reps=
     return out
 
 
+def run_kernel_case(which):
+    """A few launches of one hot kernel on a case sized for an ncu capture: operands larger than L2
+    (126 MB) but well under 1 GB, decode shapes of the benchmark."""
+    import torch
+
+    ops, synth = load("ops"), load("synth")
+    load("build").build()
+    dev = torch.device("cuda", 0)
+    T = N_REQ
+    if which == "linear":
+        # the q/k/v projection of one layer with its LoRA stack: 4 weight copies = 403 MB
+        c = synth.operator_case(T, 4096, 12288, N_ADAPTERS, RANK, device=dev)
+        Ws = [ops.PackedWeight((torch.randn(12288, 4096, device=dev) * 0.02).to(torch.bfloat16)) for _ in range(4)]
+        A = torch.cat([c["A"]] * 3, 1).contiguous()
+        st = ops.LoraStack(A, c["B"], torch.full((N_ADAPTERS,), RANK, dtype=torch.int32, device=dev),
+                           torch.full((N_ADAPTERS,), ALPHA / RANK, device=dev), RANK, 3, (0, 4096, 8192, 12288)).pack_b()
+        slots = c["ids"].to(torch.int32)
+        u = ops.lora_shrink(c["x"], st, slots)
+        out = torch.empty(T, 12288, dtype=torch.bfloat16, device=dev)
+        for i in range(6):
+            ops.linear(c["x"], Ws[i % 4], st, slots, u=u, out=out)
+    else:
+        # one layer's attention at context 576: 32 rows x 32 heads, 302 MB of KV
+        Hq = Hkv = 32
+        D, ctx = 128, 576
+        n_pg = ctx // PAGE + 1
+        kp = torch.randn(T * n_pg, Hkv, PAGE, D, device=dev, dtype=torch.bfloat16)
+        vp = torch.randn(T * n_pg, Hkv, PAGE, D, device=dev, dtype=torch.bfloat16)
+        bt = torch.arange(T * n_pg, device=dev, dtype=torch.int32).view(T, n_pg)
+        qkv = torch.randn(T, 3 * Hq * D, device=dev, dtype=torch.bfloat16)
+        slot = torch.arange(T, device=dev, dtype=torch.int32)
+        pos = torch.full((T,), ctx, device=dev, dtype=torch.int32)
+        for _ in range(4):
+            ops.paged_attention(qkv, kp, vp, bt, slot, pos, Hq, Hkv, D, PAGE, 10000.0, True)
+    torch.cuda.synchronize()
+    print(json.dumps({"kernel_case": which, "launches": ops.launch_count()}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -390,11 +439,18 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="debug: truncate the model (the number is then not a bench value)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--skip-prefill", action="store_true",
+                    help="profiling aid: fill the KV cache with seeded random values instead of running prefill "
+                         "(the number is then not a bench value)")
+    ap.add_argument("--kernel-case", default="", choices=["", "linear", "attention"],
+                    help="profiling aid: launch one kernel a few times on a small case (> L2, < 1 GB) and exit")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.impl == "reference":
+    if args.kernel_case:
+        run_kernel_case(args.kernel_case)
+    elif args.impl == "reference":
         run_reference(args, rank, world)
     else:
         run_ours(args, rank, world, local_rank)
