@@ -72,6 +72,8 @@ __global__ void __launch_bounds__(128) paged_attn_kernel(AttnArgs a) {
   __shared__ float wacc[4][D];
   __shared__ float s_new;
 
+  pdl_launch_dependents();
+  pdl_wait();
   const int h = blockIdx.x, t = blockIdx.y, split = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int rep = a.Hq / a.Hkv, kvh = h / rep;
@@ -242,6 +244,8 @@ __global__ void __launch_bounds__(128) paged_attn_kernel(AttnArgs a) {
 // grid (Hq, T), D threads: combine the n_splits partial results of one (row, head).
 __global__ void attn_merge_kernel(const float* __restrict__ work, int Hq, int D, int n_splits,
                                   bf16* __restrict__ out, int64_t ld_out) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int h = blockIdx.x, t = blockIdx.y, d = threadIdx.x;
   const float* w = work + ((size_t)t * Hq + h) * n_splits * (D + 2);
   float M = -INFINITY;
@@ -265,6 +269,8 @@ __global__ void __launch_bounds__(256) kv_append_rope_kernel(bf16* __restrict__ 
                                                              const int32_t* __restrict__ row_slot,
                                                              const int32_t* __restrict__ row_pos, int Hq, int Hkv,
                                                              int D, int PS, float theta) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int slot = row_slot[t], pos = row_pos[t];
   const int page = block_table[(size_t)slot * max_pages + pos / PS];
@@ -331,7 +337,7 @@ extern "C" int mlora_kv_append_rope(void* d_qkv, int64_t ld, void* d_k_pages, vo
                 "kv_append_rope: null pointer");
   MLORA_REQUIRE(ld % 8 == 0 && aligned16(d_qkv) && aligned16(d_v_pages), "kv_append_rope: alignment");
   if (T == 0) return MLORA_OK;
-  kv_append_rope_kernel<<<T, 256, 0, (cudaStream_t)stream>>>((bf16*)d_qkv, ld, (bf16*)d_k_pages, (bf16*)d_v_pages,
+  launch_pdl(kv_append_rope_kernel, T, 256, 0, (cudaStream_t)stream, (bf16*)d_qkv, ld, (bf16*)d_k_pages, (bf16*)d_v_pages,
                                                              d_block_table, max_pages, d_row_slot, d_row_pos, Hq, Hkv,
                                                              D, page_size, rope_theta);
   count_launch();
@@ -368,16 +374,16 @@ extern "C" int mlora_paged_attention(const void* d_qkv, int64_t ld, void* d_k_pa
   dim3 grid(Hq, T, n_splits);
   cudaStream_t st = (cudaStream_t)stream;
   if (D == 128 && page_size == 16)
-    paged_attn_kernel<128, 8><<<grid, 128, 0, st>>>(a);
+    launch_pdl(paged_attn_kernel<128, 8>, grid, 128, 0, st, a);
   else if (D == 128 && page_size == 32)
-    paged_attn_kernel<128, 16><<<grid, 128, 0, st>>>(a);
+    launch_pdl(paged_attn_kernel<128, 16>, grid, 128, 0, st, a);
   else if (D == 64 && page_size == 16)
-    paged_attn_kernel<64, 4><<<grid, 128, 0, st>>>(a);
+    launch_pdl(paged_attn_kernel<64, 4>, grid, 128, 0, st, a);
   else
-    paged_attn_kernel<64, 8><<<grid, 128, 0, st>>>(a);
+    launch_pdl(paged_attn_kernel<64, 8>, grid, 128, 0, st, a);
   count_launch();
   if (n_splits > 1) {
-    attn_merge_kernel<<<dim3(Hq, T), D, 0, st>>>((const float*)d_work, Hq, D, n_splits, (bf16*)d_out, ld_out);
+    launch_pdl(attn_merge_kernel, dim3(Hq, T), D, 0, st, (const float*)d_work, Hq, D, n_splits, (bf16*)d_out, ld_out);
     count_launch();
   }
   MLORA_CHECK_LAUNCH("paged_attn_kernel");

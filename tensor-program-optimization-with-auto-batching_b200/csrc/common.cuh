@@ -75,4 +75,28 @@ __device__ __forceinline__ uint4 ld_cached(const void* p) {
 
 namespace mlora {
 void count_launch(int n = 1);
+bool pdl_enabled();
+
+// Programmatic dependent launch.  Every kernel of the decode step is launched with the
+// "programmatic stream serialization" attribute and begins with pdl_launch_dependents(), so the next
+// kernel in the stream may become resident while this one still runs; a kernel calls pdl_wait() before
+// it reads anything an earlier kernel wrote and before it writes global memory at all (work that only
+// touches constant inputs -- streaming weights into shared memory -- may run ahead of it).
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 }

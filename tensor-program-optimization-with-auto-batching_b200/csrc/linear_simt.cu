@@ -14,6 +14,8 @@ __global__ void __launch_bounds__(256) lora_shrink_kernel(const bf16* __restrict
                                                           const int32_t* __restrict__ ranks,
                                                           const int32_t* __restrict__ slots, int n_adapters,
                                                           int in, int r_max, int r_tot, float* __restrict__ u) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.y;
   const int j = blockIdx.x * 8 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
@@ -37,6 +39,8 @@ __global__ void __launch_bounds__(256) lora_shrink_kernel(const bf16* __restrict
 
 template <int TT, bool SILU>
 __global__ void __launch_bounds__(256) linear_simt_kernel(LinearArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int unit = blockIdx.x * 8 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   const int n_units = SILU ? a.out / 2 : a.out;
@@ -90,9 +94,9 @@ void launch_simt(const LinearArgs& a, cudaStream_t st) {
   const int n_units = (a.flags & MLORA_SILU_MUL) ? a.out / 2 : a.out;
   const int grid = (n_units + 7) / 8;
   if (a.flags & MLORA_SILU_MUL)
-    linear_simt_kernel<TT, true><<<grid, 256, 0, st>>>(a);
+    launch_pdl(linear_simt_kernel<TT, true>, grid, 256, 0, st, a);
   else
-    linear_simt_kernel<TT, false><<<grid, 256, 0, st>>>(a);
+    launch_pdl(linear_simt_kernel<TT, false>, grid, 256, 0, st, a);
 }
 
 }  // namespace
@@ -126,8 +130,8 @@ extern "C" int mlora_lora_shrink(const void* d_x, int64_t ldx, const void* d_A_a
   MLORA_REQUIRE(T <= 65535, "lora_shrink: T=%d exceeds 65535 rows per call", T);
   const int r_tot = r_max * n_mod;
   dim3 grid((r_tot + 7) / 8, T);
-  lora_shrink_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const bf16*)d_x, ldx, (const bf16*)d_A_all, d_ranks,
-                                                             d_slots, n_adapters, in, r_max, r_tot, d_u);
+  launch_pdl(lora_shrink_kernel, grid, 256, 0, (cudaStream_t)stream, (const bf16*)d_x, ldx, (const bf16*)d_A_all, d_ranks,
+             d_slots, n_adapters, in, r_max, r_tot, d_u);
   count_launch();
   MLORA_CHECK_LAUNCH("lora_shrink_kernel");
   return MLORA_OK;

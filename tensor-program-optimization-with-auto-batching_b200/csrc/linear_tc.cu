@@ -325,7 +325,8 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
   uint64_t* acc_empty = acc_full + 2;                     // [2]
   uint64_t* cache_full = acc_empty + 2;                   // LoRA operand cache written / all readers retired
   uint64_t* cache_empty = cache_full + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(cache_empty + 1);
+  uint64_t* preload_bar = cache_empty + 1;                // LoRA operands of the first token tile are in smem
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(preload_bar + 1);
   int* s_slots = reinterpret_cast<int*>(aux + 1024);  // [BN] epilogue warps (CUDA-core expand)
   int* p_tok = s_slots + BN;                           // weight producer: slots of the token tile
   int* p_list = p_tok + BN;                            //                  distinct slots
@@ -361,17 +362,27 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
     }
     mbar_init(cache_full, 1);
     mbar_init(cache_empty, 1);
+    mbar_init(preload_bar, 4);  // the four epilogue warps
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     if (!(a.flags & MLORA_W_PACKED)) tma_prefetch_desc(&map_w);
     tma_prefetch_desc(&map_x);
     if (p.lora_mode == 2 && !(a.flags & MLORA_B_PACKED)) tma_prefetch_desc(&map_b);
   }
   if (warp == 1) tmem_alloc(tmem_slot, C::kTmemCols);
-  // The per-token LoRA operands of the CTA's first token tile (decode: the only one) are fetched now,
-  // by warps that are idle at start-up, so that no pipeline role stops mid-stream for a global load.
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  // From here on the next kernel in the stream may become resident; this kernel's weight producer
+  // starts streaming at once (weights are constant inputs), every other role first waits until the
+  // kernels before it have completed.
+  pdl_launch_dependents();
   const int tok_tile0 = (rg.it0 / p.k_blocks) / p.row_tiles;
   const bool stage_u2 = p.lora_mode == 2 && (size_t)BN * r_tot * sizeof(float) <= (size_t)kStageUMax;
-  if (p.lora_mode == 2) {
+  if (warp != 0) pdl_wait();
+  if (p.lora_mode == 2 && warp >= 2 && warp <= 5) {
+    // The per-token LoRA operands of the CTA's first token tile (decode: the only one) are fetched now,
+    // by the epilogue warps, which are idle at start-up, so that no pipeline role stops mid-stream for a
+    // global load.  The roles pick the result up through `preload_bar` when they first need it.
     if (warp == 2) {
       const int ns = distinct_slots<BN>(a, tok_tile0 * BN, p_tok, p_list);
       for (int i = lane; i < BN; i += 32) {
@@ -382,14 +393,13 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
         }
       }
       if (lane == 0) s_nseg0 = ns;
-    } else if (warp >= 3 && warp <= 5 && stage_u2) {
+    } else if (stage_u2) {
       const int n_valid = min(BN, a.T - tok_tile0 * BN) * r_tot;
       for (int i = (warp - 3) * 32 + lane; i < n_valid; i += 96) s_u[i] = a.u[(size_t)tok_tile0 * BN * r_tot + i];
     }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(preload_bar);
   }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t rb = p.lora_sub * 2;  // row bytes of a LoRA stage
 
@@ -397,7 +407,8 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
     // ---- weight producer: lane 0 issues the copies; all lanes list the adapters of a token tile ------
     const bool packed = (a.flags & MLORA_W_PACKED) != 0;
     const uint8_t* wp = reinterpret_cast<const uint8_t*>(a.W);
-    int it = rg.it0, n = 0, cur_tok_tile = tok_tile0, n_seg = s_nseg0;
+    int it = rg.it0, n = 0, cur_tok_tile = tok_tile0, n_seg = 0;
+    bool got_preload = false;
     bool ok = true;
     while (it < rg.it1 && ok) {
       const Segment sg = next_segment(p, it, rg.it1);
@@ -423,6 +434,11 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
       n += sg.kb1 - sg.kb0;
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (ok && p.lora_mode == 2 && sg.kb1 == p.k_blocks) {
+        if (!got_preload) {  // operands of the first token tile, staged by the epilogue warps at start-up
+          mbar_wait(preload_bar, 0, &s_abort);
+          n_seg = s_nseg0;
+          got_preload = true;
+        }
         // The tile's last k-block is ours: append the LoRA stages.  One stage per (adapter present in
         // the token tile, 64-wide slice of the rank); its A operand is B_all[slot, rows of the tile, slice].
         // When the B operands are cached in shared memory, up to `group` such slices share one ring slot.
@@ -464,7 +480,8 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
   } else if (warp == 6) {
     // ---- token-tile producer: lane 0 issues the x copies; all lanes build the LoRA B operands --------
     const bool stage_u = stage_u2;
-    int it = rg.it0, n = 0, cur_tok_tile = tok_tile0, n_seg = s_nseg0, cur_key = -1, n_build = 0;
+    int it = rg.it0, n = 0, cur_tok_tile = tok_tile0, n_seg = 0, cur_key = -1, n_build = 0;
+    bool got_preload = false;
     bool ok = true;
     while (it < rg.it1 && ok) {
       const Segment sg = next_segment(p, it, rg.it1);
@@ -486,6 +503,11 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
       n += sg.kb1 - sg.kb0;
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (ok && p.lora_mode == 2 && sg.kb1 == p.k_blocks) {
+        if (!got_preload) {  // operands of the first token tile, staged by the epilogue warps at start-up
+          mbar_wait(preload_bar, 0, &s_abort);
+          n_seg = s_nseg0;
+          got_preload = true;
+        }
         // B operand of a LoRA stage = scale * u of the tokens that use the adapter (zero rows for the
         // others), written in the swizzled K-major layout the MMA expects: once per (token tile, module)
         // into the shared-memory cache when all of them fit, else stage by stage into the x ring.
@@ -589,7 +611,8 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
   } else if (warp == 1) {
     // ---- MMA issuer: lane 0 issues; all lanes count the LoRA stages of a token tile ---------------------
     constexpr uint32_t idesc = make_idesc(BM, BN);
-    int it = rg.it0, nw = 0, nx = 0, j = 0, cur_tok_tile = tok_tile0, n_seg = s_nseg0, cur_key = -1, n_build = 0;
+    int it = rg.it0, nw = 0, nx = 0, j = 0, cur_tok_tile = tok_tile0, n_seg = 0, cur_key = -1, n_build = 0;
+    bool got_preload = false;
     bool ok = true;
     while (it < rg.it1 && ok) {
       const Segment sg = next_segment(p, it, rg.it1);
@@ -599,6 +622,11 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
       int n_l = 0, group = 1;
       bool cached = false, new_build = false;
       if (p.lora_mode == 2 && sg.kb1 == p.k_blocks) {
+        if (!got_preload) {  // operands of the first token tile, staged by the epilogue warps at start-up
+          mbar_wait(preload_bar, 0, &s_abort);
+          n_seg = s_nseg0;
+          got_preload = true;
+        }
         if (tok_tile != cur_tok_tile) {
           n_seg = distinct_slots<BN>(a, tok_tile * BN, m_tok, m_list);
           cur_tok_tile = tok_tile;
@@ -938,9 +966,9 @@ int launch(const LinearArgs& a, const Plan& pl, void* work, cudaStream_t st) {
     attr_set = true;
   }
   if (p.lora_mode == 1)
-    linear_tc_kernel<BN, true><<<pl.grid, kThreads, C::kSmemBytes, st>>>(mw, mx, mb, p);
+    launch_pdl(linear_tc_kernel<BN, true>, pl.grid, kThreads, C::kSmemBytes, st, mw, mx, mb, p);
   else
-    linear_tc_kernel<BN, false><<<pl.grid, kThreads, C::kSmemBytes, st>>>(mw, mx, mb, p);
+    launch_pdl(linear_tc_kernel<BN, false>, pl.grid, kThreads, C::kSmemBytes, st, mw, mx, mb, p);
   count_launch();
   MLORA_CHECK_LAUNCH("linear_tc_kernel");
   return MLORA_OK;

@@ -35,6 +35,8 @@ __global__ void __launch_bounds__(kNormThreads) residual_rmsnorm_kernel(const bf
                                                                         const bf16* __restrict__ w, float eps,
                                                                         bf16* __restrict__ out, int H) {
   __shared__ float sm[33];
+  pdl_launch_dependents();
+  pdl_wait();
   const size_t row = blockIdx.x;
   float* r = res + row * H;
   const bf16* d = delta ? delta + row * H : nullptr;
@@ -91,6 +93,8 @@ __global__ void __launch_bounds__(kNormThreads) residual_rmsnorm_kernel(const bf
 __global__ void __launch_bounds__(256) embed_kernel(const int32_t* __restrict__ ids, const bf16* __restrict__ E,
                                                     int H, int vocab, float* __restrict__ res,
                                                     bf16* __restrict__ out_bf16) {
+  pdl_launch_dependents();
+  pdl_wait();
   const size_t row = blockIdx.x;
   int id = ids[row];
   id = min(max(id, 0), vocab - 1);  // out-of-range ids are clamped, never dereferenced
@@ -112,6 +116,8 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
                                                       int32_t* __restrict__ tok) {
   __shared__ float sv[32];
   __shared__ int si[32];
+  pdl_launch_dependents();
+  pdl_wait();
   const float* l = logits + (size_t)blockIdx.x * ld;
   float best = -FLT_MAX;
   int bi = 0x7fffffff;
@@ -155,6 +161,8 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
 
 __global__ void kv_begin_decode_kernel(const int32_t* __restrict__ row_slot, int32_t* __restrict__ seq_lens,
                                        int32_t* __restrict__ row_pos, int B) {
+  pdl_launch_dependents();
+  pdl_wait();
   int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b < B) {
     int s = row_slot[b];
@@ -176,8 +184,8 @@ extern "C" int mlora_residual_rmsnorm(const void* d_delta, float* d_res, const v
   MLORA_REQUIRE(aligned16(d_res) && aligned16(d_w) && aligned16(d_out) && aligned16(d_delta),
                 "residual_rmsnorm: pointers must be 16-byte aligned");
   if (T == 0) return MLORA_OK;
-  residual_rmsnorm_kernel<<<T, kNormThreads, 0, (cudaStream_t)stream>>>((const bf16*)d_delta, d_res,
-                                                                        (const bf16*)d_w, eps, (bf16*)d_out, H);
+  launch_pdl(residual_rmsnorm_kernel, T, kNormThreads, 0, (cudaStream_t)stream, (const bf16*)d_delta, d_res,
+             (const bf16*)d_w, eps, (bf16*)d_out, H);
   count_launch();
   MLORA_CHECK_LAUNCH("residual_rmsnorm_kernel");
   return MLORA_OK;
@@ -189,7 +197,7 @@ extern "C" int mlora_embed(const int32_t* d_ids, const void* d_E, int32_t T, int
   MLORA_REQUIRE(d_ids && d_E && (d_res || d_out_bf16), "embed: null pointer");
   MLORA_REQUIRE(aligned16(d_E) && aligned16(d_res) && aligned16(d_out_bf16), "embed: pointers must be 16-byte aligned");
   if (T == 0) return MLORA_OK;
-  embed_kernel<<<T, 256, 0, (cudaStream_t)stream>>>(d_ids, (const bf16*)d_E, H, vocab, d_res, (bf16*)d_out_bf16);
+  launch_pdl(embed_kernel, T, 256, 0, (cudaStream_t)stream, d_ids, (const bf16*)d_E, H, vocab, d_res, (bf16*)d_out_bf16);
   count_launch();
   MLORA_CHECK_LAUNCH("embed_kernel");
   return MLORA_OK;
@@ -199,7 +207,7 @@ extern "C" int mlora_argmax(const float* d_logits, int64_t ld, int32_t T, int32_
   MLORA_REQUIRE(T >= 0 && V > 0 && ld >= V, "argmax: bad sizes T=%d V=%d", T, V);
   MLORA_REQUIRE(d_logits && d_tok, "argmax: null pointer");
   if (T == 0) return MLORA_OK;
-  argmax_kernel<<<T, 1024, 0, (cudaStream_t)stream>>>(d_logits, ld, V, d_tok);
+  launch_pdl(argmax_kernel, T, 1024, 0, (cudaStream_t)stream, d_logits, ld, V, d_tok);
   count_launch();
   MLORA_CHECK_LAUNCH("argmax_kernel");
   return MLORA_OK;
@@ -209,7 +217,7 @@ extern "C" int mlora_kv_begin_decode(const int32_t* d_row_slot, int32_t* d_seq_l
                                      void* stream) {
   MLORA_REQUIRE(B >= 0 && d_row_slot && d_seq_lens && d_row_pos, "kv_begin_decode: bad arguments");
   if (B == 0) return MLORA_OK;
-  kv_begin_decode_kernel<<<(B + 127) / 128, 128, 0, (cudaStream_t)stream>>>(d_row_slot, d_seq_lens, d_row_pos, B);
+  launch_pdl(kv_begin_decode_kernel, (B + 127) / 128, 128, 0, (cudaStream_t)stream, d_row_slot, d_seq_lens, d_row_pos, B);
   count_launch();
   MLORA_CHECK_LAUNCH("kv_begin_decode_kernel");
   return MLORA_OK;

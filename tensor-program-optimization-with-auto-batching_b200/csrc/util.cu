@@ -2,6 +2,8 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
+#include <cstring>
 
 #include "common.cuh"
 
@@ -16,6 +18,15 @@ int fail(int code, const char* fmt, ...) {
   vsnprintf(g_err, sizeof(g_err), fmt, ap);
   va_end(ap);
   return code;
+}
+
+bool pdl_enabled() {
+  // MLORA_PDL=0 turns programmatic dependent launch off (plain stream order), e.g. for debugging.
+  static const bool on = [] {
+    const char* e = getenv("MLORA_PDL");
+    return !(e && strcmp(e, "0") == 0);
+  }();
+  return on;
 }
 
 void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
