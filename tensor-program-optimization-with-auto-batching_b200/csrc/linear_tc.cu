@@ -47,6 +47,7 @@ struct TcParams {
   int lora_sub;    // K elements of one LoRA stage (16, 32 or 64 = row bytes 32, 64, 128)
   int n_sub;       // LoRA stages per adapter segment (r_max / lora_sub)
   int prefetch;    // weight tiles requested into L2 ahead of the ring (0 = off)
+  int tma_store;   // 1: output tiles leave through shared memory + one TMA store per 32-token chunk
   int32_t* status;  // scratch[0]
   int32_t* tickets; // [kMaxGrid], indexed by the first contributing CTA of a split tile
   float* partials;  // [grid][2][BN][BM]
@@ -95,6 +96,14 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
 __device__ __forceinline__ void l2_prefetch(const void* src, uint32_t bytes) {
   asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
 }
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(smem_u32(src)), "r"(x), "r"(y)
+               : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -268,10 +277,11 @@ struct Cfg {
   static constexpr int kXStages = BN >= 64 ? 4 : 8;  // token tiles come from L2: a shallower ring is enough
   // barriers | 7 integer lists of BN (token slots / distinct adapters per role) | staged shrink outputs
   static constexpr int kCacheBytes = 16 * 1024;  // LoRA B operands (scaled, masked shrink outputs) of a token tile
-  static constexpr int kAuxBytes = 1024 + 8 * BN * 4 + kStageUMax + kCacheBytes;
+  static constexpr int kOutBytes = 32 * BM * 4;  // staging of one 32-token output chunk (fp32 worst case)
+  static constexpr int kAuxBytes = 1024 + 8 * BN * 4 + kStageUMax + kCacheBytes + kOutBytes;
   static constexpr int kBudget = 227 * 1024 - 1024 /*alignment slack*/ - 64 /*static*/;
   static constexpr int kWStages0 = (kBudget - kAuxBytes - kXStages * kXBytes) / kWBytes;
-  static constexpr int kWStages = kWStages0 > 12 ? 12 : kWStages0;  // weights come from HBM: as deep as fits
+  static constexpr int kWStages = kWStages0 > 10 ? 10 : kWStages0;  // measured: 5 stages already saturate
   static constexpr int kSmemBytes = kWStages * kWBytes + kXStages * kXBytes + kAuxBytes + 1024;
   static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;  // two accumulators
   static constexpr int kChunk = BN < 32 ? BN : 32;              // columns per TMEM load
@@ -310,13 +320,15 @@ template <int BN, bool SIMT_LORA>
 __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                 const __grid_constant__ CUtensorMap map_x,
                                                                 const __grid_constant__ CUtensorMap map_b,
+                                                                const __grid_constant__ CUtensorMap map_y,
                                                                 TcParams p) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* w_ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* x_ring = w_ring + C::kWStages * C::kWBytes;
   uint8_t* s_cache = x_ring + C::kXStages * C::kXBytes;  // 1024-byte aligned like the rings
-  uint8_t* aux = s_cache + C::kCacheBytes;
+  uint8_t* s_out = s_cache + C::kCacheBytes;             // output staging for the TMA store
+  uint8_t* aux = s_out + C::kOutBytes;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(aux);  // [kWStages] weight stage filled
   uint64_t* empty_bar = full_bar + C::kWStages;           // [kWStages] weight stage consumed
   uint64_t* xfull_bar = empty_bar + C::kWStages;          // [kXStages]
@@ -367,6 +379,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
     if (!(a.flags & MLORA_W_PACKED)) tma_prefetch_desc(&map_w);
     tma_prefetch_desc(&map_x);
     if (p.lora_mode == 2 && !(a.flags & MLORA_B_PACKED)) tma_prefetch_desc(&map_b);
+    if (p.tma_store) tma_prefetch_desc(&map_y);
   }
   if (warp == 1) tmem_alloc(tmem_slot, C::kTmemCols);
   tc_fence_before();
@@ -720,6 +733,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
     const int q = warp & 3;
     const int etid = q * 32 + lane;           // 0..127 = row inside the tile
     const bool silu = (a.flags & MLORA_SILU_MUL) != 0;
+    const bool out_f32 = (a.flags & MLORA_OUT_F32) != 0;
     constexpr bool simt_lora = SIMT_LORA;
     const bool stage_u = simt_lora && (size_t)BN * r_tot * sizeof(float) <= (size_t)kStageUMax;
     int staged_tok_tile = -1;
@@ -748,6 +762,32 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
       // Adds the CUDA-core LoRA expand if any, applies SiLU*up, stores.  v[i] = (token t0+c0+i, row).
       auto finish = [&](float (&v)[32], int c0) {
         if (SIMT_LORA) simt_lora_expand<BN>(a, v, c0, t0, row, r_tot, stage_u, s_slots, s_u);
+        if (p.tma_store) {
+          // registers -> shared memory [tokens][outputs of the tile] -> one TMA store (which also clips
+          // tokens >= T and outputs >= out); far fewer instructions than 32 strided stores per thread
+          if (etid == 0) bulk_wait_read0();  // the previous chunk's store has finished reading s_out
+          epi_bar_sync();
+          if (silu) {
+            bf16* so = reinterpret_cast<bf16*>(s_out);
+#pragma unroll
+            for (int i = 0; i < C::kChunk; ++i) {
+              const float other = __shfl_xor_sync(0xffffffffu, v[i], 8);
+              if ((etid & 8) == 0) so[i * (BM / 2) + (etid >> 4) * 8 + (etid & 7)] = __float2bfloat16_rn(silu_mul(v[i], other));
+            }
+          } else if (out_f32) {
+            float* so = reinterpret_cast<float*>(s_out);
+#pragma unroll
+            for (int i = 0; i < C::kChunk; ++i) so[i * BM + etid] = v[i];
+          } else {
+            bf16* so = reinterpret_cast<bf16*>(s_out);
+#pragma unroll
+            for (int i = 0; i < C::kChunk; ++i) so[i * BM + etid] = __float2bfloat16_rn(v[i]);
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          epi_bar_sync();
+          if (etid == 0) tma_store_2d(&map_y, s_out, silu ? row_tile * (BM / 2) : row_tile * BM, t0 + c0);
+          return;
+        }
 #pragma unroll
         for (int i = 0; i < C::kChunk; ++i) {
           const int t = t0 + c0 + i;
@@ -831,6 +871,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
   }
 
   // ---- teardown -----------------------------------------------------------------------------------------
+  if (p.tma_store && warp == 4 && lane == 0) bulk_wait_all0();  // epilogue thread 0 (warp 4, lane 0) issued the stores
   __syncwarp();
   tc_fence_before();
   __syncthreads();
@@ -859,6 +900,22 @@ EncodeTiledFn encode_fn() {
 }
 
 // 2-D bf16 tensor [rows, cols] with row pitch ld elements; box = [box_rows, 64 cols], 128-byte swizzle.
+// Output tensor [T, cols] (row pitch ld elements, bf16 or fp32), box = [box_rows tokens, box_cols outputs], no swizzle.
+int make_out_map(CUtensorMap* m, void* ptr, int rows, int cols, int64_t ld, int box_rows, int box_cols, bool f32) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(MLORA_ECUDA, "linear: cuTensorMapEncodeTiled is not available from this driver");
+  const int es = f32 ? 4 : 2;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * es};
+  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(m, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ptr, dims, strides, box,
+                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(MLORA_ECUDA, "linear: cuTensorMapEncodeTiled (output) failed with %d", (int)r);
+  return MLORA_OK;
+}
+
 int make_map(CUtensorMap* m, const void* ptr, long long rows, int cols, int64_t ld, int box_rows, int box_cols = BK) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return fail(MLORA_ECUDA, "linear: cuTensorMapEncodeTiled is not available from this driver");
@@ -951,6 +1008,17 @@ int launch(const LinearArgs& a, const Plan& pl, void* work, cudaStream_t st) {
   p.row_tiles = pl.row_tiles;
   p.n_tiles = pl.row_tiles * pl.tok_tiles;
   p.per_cta = pl.per_cta;
+  // output through TMA when the tensor satisfies its alignment rules (16-byte base and row pitch)
+  CUtensorMap my = mx;
+  {
+    const bool f32 = (a.flags & MLORA_OUT_F32) != 0, silu = (a.flags & MLORA_SILU_MUL) != 0;
+    const int es = f32 ? 4 : 2, cols = silu ? a.out / 2 : a.out;
+    p.tma_store = aligned16(a.y) && (a.ldy * es) % 16 == 0 && (cols * es) % 16 == 0;
+    if (p.tma_store) {
+      rc = make_out_map(&my, a.y, a.T, cols, a.ldy, BN < 32 ? BN : 32, silu ? BM / 2 : BM, f32);
+      if (rc) return rc;
+    }
+  }
   p.prefetch = 0;  // measured: an L2 prefetch stream ahead of the ring slows the kernel down on B200
   p.status = (int32_t*)work;
   p.tickets = (int32_t*)((uint8_t*)work + kHeaderBytes);
@@ -966,9 +1034,9 @@ int launch(const LinearArgs& a, const Plan& pl, void* work, cudaStream_t st) {
     attr_set = true;
   }
   if (p.lora_mode == 1)
-    launch_pdl(linear_tc_kernel<BN, true>, pl.grid, kThreads, C::kSmemBytes, st, mw, mx, mb, p);
+    launch_pdl(linear_tc_kernel<BN, true>, pl.grid, kThreads, C::kSmemBytes, st, mw, mx, mb, my, p);
   else
-    launch_pdl(linear_tc_kernel<BN, false>, pl.grid, kThreads, C::kSmemBytes, st, mw, mx, mb, p);
+    launch_pdl(linear_tc_kernel<BN, false>, pl.grid, kThreads, C::kSmemBytes, st, mw, mx, mb, my, p);
   count_launch();
   MLORA_CHECK_LAUNCH("linear_tc_kernel");
   return MLORA_OK;
