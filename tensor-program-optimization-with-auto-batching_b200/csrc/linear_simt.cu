@@ -25,12 +25,28 @@ __global__ void __launch_bounds__(256) lora_shrink_kernel(const bf16* __restrict
   if (slot >= 0 && slot < n_adapters && (j % r_max) < ranks[slot]) {
     const bf16* a = A_all + ((size_t)slot * r_tot + j) * in;
     const bf16* xr = x + (size_t)t * ldx;
-    for (int k = lane * 8; k < in; k += 256) {
-      float af[8], xf[8];
-      unpack8(ld_cached(a + k), af);
-      unpack8(ld_cached(xr + k), xf);
+    // 8 chunks of A and of x are requested before the first is used: the dot product is a chain of
+    // L2 round trips otherwise (one warp per (row, rank index), nothing else to hide the latency)
+    for (int k0 = lane * 8; k0 < in; k0 += 256 * 8) {
+      uint4 av[8], xv[8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc = fmaf(af[i], xf[i], acc);
+      for (int c = 0; c < 8; ++c) {
+        const int k = k0 + c * 256;
+        if (k < in) {
+          av[c] = ld_cached(a + k);
+          xv[c] = ld_cached(xr + k);
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        if (k0 + c * 256 < in) {
+          float af[8], xf[8];
+          unpack8(av[c], af);
+          unpack8(xv[c], xf);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc = fmaf(af[i], xf[i], acc);
+        }
+      }
     }
     acc = warp_sum(acc);
   }
