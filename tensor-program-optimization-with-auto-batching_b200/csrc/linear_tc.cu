@@ -407,8 +407,18 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
       }
       if (lane == 0) s_nseg0 = ns;
     } else if (stage_u2) {
-      const int n_valid = min(BN, a.T - tok_tile0 * BN) * r_tot;
-      for (int i = (warp - 3) * 32 + lane; i < n_valid; i += 96) s_u[i] = a.u[(size_t)tok_tile0 * BN * r_tot + i];
+      // all loads of a thread are issued before the first store (r_tot is a multiple of 8: float4 granules)
+      const int n_vec = min(BN, a.T - tok_tile0 * BN) * r_tot / 4;
+      const float4* src = reinterpret_cast<const float4*>(a.u + (size_t)tok_tile0 * BN * r_tot);
+      float4 tmp[8];
+      for (int base = (warp - 3) * 32 + lane; base < n_vec; base += 96 * 8) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          if (base + c * 96 < n_vec) tmp[c] = __ldg(src + base + c * 96);
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          if (base + c * 96 < n_vec) reinterpret_cast<float4*>(s_u)[base + c * 96] = tmp[c];
+      }
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(preload_bar);
@@ -871,7 +881,9 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
   }
 
   // ---- teardown -----------------------------------------------------------------------------------------
-  if (p.tma_store && warp == 4 && lane == 0) bulk_wait_all0();  // epilogue thread 0 (warp 4, lane 0) issued the stores
+  // epilogue thread 0 (warp 4, lane 0) issued the stores: shared memory must stay valid until they have
+  // read it; their global writes complete with the grid
+  if (p.tma_store && warp == 4 && lane == 0) bulk_wait_read0();
   __syncwarp();
   tc_fence_before();
   __syncthreads();
