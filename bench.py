@@ -270,6 +270,20 @@ def run_ours(args, rank, world, local_rank):
     barrier()
     ms_e2e = max_over_ranks(ev0.elapsed_time(ev1))
 
+    # ---- base-only decode (same batch, adapters off): the denominator of the LoRA overhead ------------------
+    rewind()
+    graph_base = eng.capture_decode(sids, slots, use_lora=False, reserve_tokens=total_steps)
+    rewind()
+    for _ in range(W):
+        graph_base.replay()
+    barrier()
+    ev0.record()
+    for _ in range(K):
+        graph_base.replay()
+    ev1.record()
+    barrier()
+    ms_base = max_over_ranks(ev0.elapsed_time(ev1)) / K
+
     # ---- kernel-only passes for the roofline: the projection launches, then the attention launches -------
     peak, peak_src = measured_peak()
     n_uniq = len(set(slots))
@@ -307,6 +321,8 @@ def run_ours(args, rank, world, local_rank):
                          "peak_gbs": peak, "peak_source": peak_src,
                          "frac": step_bytes / (ms_step * 1e6) / peak,
                          "frac_of_8tbs": step_bytes / (ms_step * 1e6) / 8000.0},
+            "lora_overhead": {"base_only_ms_per_step": ms_base, "with_lora_ms_per_step": ms_step,
+                              "overhead_frac": ms_step / ms_base - 1.0},
             "clocks": clocks, "prefill_seconds_untimed": prefill_s, "tc_status_word": status,
         }
         if world == 1 and not args.no_cpu:

@@ -1046,9 +1046,9 @@ int launch(const LinearArgs& a, const Plan& pl, void* work, cudaStream_t st) {
     attr_set = true;
   }
   if (p.lora_mode == 1)
-    launch_pdl(linear_tc_kernel<BN, true>, pl.grid, kThreads, C::kSmemBytes, st, mw, mx, mb, my, p);
+    launch_pdl_if(pdl_enabled_gemm(), linear_tc_kernel<BN, true>, pl.grid, kThreads, C::kSmemBytes, st, mw, mx, mb, my, p);
   else
-    launch_pdl(linear_tc_kernel<BN, false>, pl.grid, kThreads, C::kSmemBytes, st, mw, mx, mb, my, p);
+    launch_pdl_if(pdl_enabled_gemm(), linear_tc_kernel<BN, false>, pl.grid, kThreads, C::kSmemBytes, st, mw, mx, mb, my, p);
   count_launch();
   MLORA_CHECK_LAUNCH("linear_tc_kernel");
   return MLORA_OK;

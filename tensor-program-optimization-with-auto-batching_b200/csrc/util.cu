@@ -20,16 +20,21 @@ int fail(int code, const char* fmt, ...) {
   return code;
 }
 
-bool pdl_enabled() {
-  // Off by default: on the benchmark's decode step it measured 1-2 % slower than plain stream order
-  // (early-resident projection CTAs compete with the tail of the kernel before them); MLORA_PDL=1 turns
-  // programmatic dependent launch on.
-  static const bool on = [] {
+// Programmatic dependent launch policy (MLORA_PDL): default "2" = only the projection kernel is launched
+// programmatically dependent, so its weight producer streams while the small kernel before it (RMSNorm,
+// LoRA shrink, attention tail) still runs: measured 5 % faster on the benchmark's decode step.  "1" = every
+// decode kernel (measured 1-2 % slower than plain stream order: early-resident CTAs compete with the tail
+// of the kernel before them), "0" = off.
+static int pdl_mode() {
+  static const int mode = [] {
     const char* e = getenv("MLORA_PDL");
-    return e && strcmp(e, "1") == 0;
+    if (!e) return 2;
+    return strcmp(e, "0") == 0 ? 0 : strcmp(e, "1") == 0 ? 1 : 2;
   }();
-  return on;
+  return mode;
 }
+bool pdl_enabled() { return pdl_mode() == 1; }
+bool pdl_enabled_gemm() { return pdl_mode() >= 1; }
 
 void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
 
