@@ -58,15 +58,34 @@ class PackedLlama:
     ``init_peft_weights/lora_weights.py:18-23``), ``scales[i]`` = alpha/r of adapter i.
     Adapter ``i`` occupies slot ``i`` of every stack."""
 
-    def __init__(self, cfg, weights, adapters=(), scales=(), device="cuda", n_layers=None, pack=True):
+    def __init__(self, cfg, weights, adapters=(), scales=(), device="cuda", n_layers=None, pack=True,
+                 tp_rank=0, tp_size=1):
         """pack=True stores every projection matrix and adapter B stack in the pre-tiled layouts of
-        mlora_pack_weight / mlora_pack_lora_b (one bulk copy per pipeline stage)."""
+        mlora_pack_weight / mlora_pack_lora_b (one bulk copy per pipeline stage).
+
+        tp_size > 1: Megatron-style tensor parallelism.  q/k/v and gate/up are column-parallel (this
+        rank keeps the rows of its heads / its slice of the intermediate features), o and down are
+        row-parallel (this rank keeps the matching input columns; the partial outputs are summed by an
+        all-reduce), lm_head is vocabulary-parallel.  Adapters follow their projection: on a
+        column-parallel projection A is replicated and B sliced by rows; on a row-parallel one A is
+        sliced by columns and B replicated, so each rank's LoRA partial rides in its GEMM partial and
+        the one all-reduce sums both."""
         self.cfg = dict(cfg)
         self.pack = pack
+        self.tp_rank, self.tp_size = int(tp_rank), int(tp_size)
         self.device = torch.device(device)
         c = self.cfg
         self.H, self.I, self.V = c["hidden_size"], c["intermediate_size"], c["vocab_size"]
         self.Hq, self.Hkv, self.D = c["num_attention_heads"], c["num_key_value_heads"], c["head_dim"]
+        G, R = self.tp_size, self.tp_rank
+        if self.Hq % G or self.Hkv % G or self.I % (8 * G) or self.V % G:
+            raise ValueError(f"tp_size {G} must divide heads ({self.Hq}/{self.Hkv}), intermediate/8 and vocab")
+        self.Hq_full, self.Hkv_full, self.I_full, self.V_full = self.Hq, self.Hkv, self.I, self.V
+        self.Hq, self.Hkv, self.I, self.V = self.Hq // G, self.Hkv // G, self.I // G, self.V // G
+        self.vocab_offset = R * self.V
+        self._q_rows = slice(R * self.Hq * self.D, (R + 1) * self.Hq * self.D)
+        self._kv_rows = slice(R * self.Hkv * self.D, (R + 1) * self.Hkv * self.D)
+        self._i_rows = slice(R * self.I, (R + 1) * self.I)
         self.L = c["num_hidden_layers"] if n_layers is None else n_layers
         self.eps, self.theta = float(c["rms_norm_eps"]), float(c["rope_theta"])
         if self.I % 8:
@@ -74,7 +93,8 @@ class PackedLlama:
         bf = lambda t: t.to(device=self.device, dtype=torch.bfloat16).contiguous()
         self.embed = bf(weights["model.embed_tokens.weight"])
         self.norm = bf(weights["model.norm.weight"])
-        self.lm_head = ops.PackedWeight(bf(weights["lm_head.weight"])) if pack else bf(weights["lm_head.weight"])
+        lm = weights["lm_head.weight"][self.vocab_offset:self.vocab_offset + self.V]
+        self.lm_head = ops.PackedWeight(bf(lm)) if pack else bf(lm)
         self.n_adapters = len(adapters)
         ranks = []
         for ad in adapters:
@@ -92,10 +112,11 @@ class PackedLlama:
             pk = lambda t: ops.PackedWeight(bf(t)) if pack else bf(t)
             lw = LayerWeights(
                 ln1=bf(w("input_layernorm")), ln2=bf(w("post_attention_layernorm")),
-                w_qkv=pk(torch.cat([w("self_attn.q_proj"), w("self_attn.k_proj"), w("self_attn.v_proj")], 0)),
-                w_o=pk(w("self_attn.o_proj")),
-                w_gu=pk(interleave_gate_up(w("mlp.gate_proj"), w("mlp.up_proj"))),
-                w_down=pk(w("mlp.down_proj")))
+                w_qkv=pk(torch.cat([w("self_attn.q_proj")[self._q_rows], w("self_attn.k_proj")[self._kv_rows],
+                                    w("self_attn.v_proj")[self._kv_rows]], 0)),
+                w_o=pk(w("self_attn.o_proj")[:, self._q_rows]),
+                w_gu=pk(interleave_gate_up(w("mlp.gate_proj")[self._i_rows], w("mlp.up_proj")[self._i_rows])),
+                w_down=pk(w("mlp.down_proj")[:, self._i_rows]))
             if adapters:
                 self._pack_lora(l, lw, adapters)
             self.layers.append(lw)
@@ -104,11 +125,20 @@ class PackedLlama:
         N, r_max, dev = len(adapters), self.r_max, self.device
         qd, kvd = self.Hq * self.D, self.Hkv * self.D
 
+        rows_of = {"q_proj": self._q_rows, "k_proj": self._kv_rows, "v_proj": self._kv_rows,
+                   "gate_proj": self._i_rows, "up_proj": self._i_rows}
+        cols_of = {"o_proj": self._q_rows, "down_proj": self._i_rows}
+
         def get(ad, blk, proj):
             ka = f"layers.{l}.{blk}.{proj}.lora_A.weight"
             if ka not in ad:
                 return None
-            return ad[ka], ad[ka.replace("lora_A", "lora_B")]
+            A, B = ad[ka], ad[ka.replace("lora_A", "lora_B")]
+            if proj in rows_of:      # column-parallel: B follows the output rows of this rank
+                B = B[rows_of[proj]]
+            else:                    # row-parallel: A follows the input columns of this rank
+                A = A[:, cols_of[proj]]
+            return A, B
 
         def build(blk, projs, outs, in_f, interleave=False):
             if not any(get(ad, blk, p) is not None for ad in adapters for p in projs):
@@ -167,8 +197,13 @@ class Engine:
     All activations live in buffers sized for ``max_rows`` rows, allocated once, so a forward does
     no allocation and can be captured in a CUDA graph."""
 
-    def __init__(self, model: PackedLlama, kv: PagedKVCache, max_rows: int):
+    def __init__(self, model: PackedLlama, kv: PagedKVCache, max_rows: int, collective=None):
+        """``collective`` (tensor parallelism only): object with ``all_reduce_sum(t)`` (in place) and
+        ``all_gather(t) -> [G, *t.shape]``; see ``sharding.DistCollective``."""
         self.m, self.kv, self.max_rows = model, kv, int(max_rows)
+        self.coll = collective
+        if model.tp_size > 1 and collective is None:
+            raise ValueError("a tensor-parallel model needs a collective")
         m, dev, T = model, model.device, int(max_rows)
         bf = dict(dtype=torch.bfloat16, device=dev)
         f32 = dict(dtype=torch.float32, device=dev)
@@ -231,9 +266,13 @@ class Engine:
             ops.paged_attention(qkv, kp, vp, kv.block_table, row_slot, row_pos, m.Hq, m.Hkv, m.D, kv.page_size,
                                 m.theta, fused_append, out=attn)
             self._proj(attn, lw.w_o, lw.lora.get("o"), slots, y)
+            if m.tp_size > 1:
+                self.coll.all_reduce_sum(y)  # row-parallel partials (base + LoRA) -> full o_proj output
             ops.residual_rmsnorm(y, res, lw.ln2, m.eps, out=xn)
             self._proj(xn, lw.w_gu, lw.lora.get("gu"), slots, act, flags=SILU_MUL)
             self._proj(act, lw.w_down, lw.lora.get("down"), slots, y)
+            if m.tp_size > 1:
+                self.coll.all_reduce_sum(y)
             delta = y
         ops.residual_rmsnorm(delta, res, m.norm, m.eps, out=xn)
         if lm_rows is not None:
@@ -242,6 +281,15 @@ class Engine:
             n_lm, xl = T, xn
         ops.linear(xl, m.lm_head, flags=OUT_F32, out=self.logits[:n_lm])
         ops.argmax(self.logits[:n_lm], out=self.next_tok[:n_lm])
+        if m.tp_size > 1:
+            # vocabulary-parallel greedy token: every rank offers (its best logit, its global index); the
+            # winner is the highest logit, lowest rank on ties (= lowest index, as np.argmax)
+            lg, tk = self.logits[:n_lm], self.next_tok[:n_lm]
+            best = lg.gather(1, tk.long().unsqueeze(1)).squeeze(1)
+            pair = torch.stack([best, (tk + m.vocab_offset).float()], 1)
+            allp = self.coll.all_gather(pair)                       # [G, n_lm, 2]
+            win = allp[:, :, 0].argmax(0)                           # first maximum along ranks
+            tk.copy_(allp[win, torch.arange(n_lm, device=lg.device), 1].int())
         return self.logits[:n_lm], self.next_tok[:n_lm]
 
     # ------------------------------------------------------------------------------------------

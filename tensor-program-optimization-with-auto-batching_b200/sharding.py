@@ -9,6 +9,8 @@ this is the multi-GPU form of its request->adapter bucketing.
 """
 from __future__ import annotations
 
+import threading
+
 import numpy as np
 
 
@@ -69,3 +71,62 @@ def gather_results(local_indices, local_tokens, n_requests: int, group=None):
         for i, t in zip(idx, toks):
             out[i] = t
     return out
+
+
+# ---- tensor parallelism: the exchange step -------------------------------------------------------------
+class DistCollective:
+    """NCCL (or gloo) collectives of a ``torch.distributed`` process group, one process per GPU."""
+
+    def __init__(self, group=None):
+        import torch.distributed as dist
+        self.dist, self.group = dist, group
+        self.size = dist.get_world_size(group)
+
+    def all_reduce_sum(self, t):
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM, group=self.group)
+
+    def all_gather(self, t):
+        import torch
+        out = torch.empty((self.size,) + tuple(t.shape), dtype=t.dtype, device=t.device)
+        self.dist.all_gather_into_tensor(out, t.contiguous(), group=self.group)
+        return out
+
+
+class ThreadCollective:
+    """The same interface for G ranks that run as threads of ONE process on ONE GPU (tests on a single
+    device: kernels that wait on one another must not run as separate processes there).  Host-side
+    rendezvous; every rank synchronises the device before and after, so it is slow and only for checks."""
+
+    class Shared:
+        def __init__(self, size):
+            self.size = size
+            self.barrier = threading.Barrier(size)
+            self.slots = [None] * size
+            self.result = None
+
+    def __init__(self, shared, rank):
+        self.sh, self.rank, self.size = shared, rank, shared.size
+
+    def _exchange(self, t, fn):
+        import torch
+        torch.cuda.synchronize()
+        self.sh.slots[self.rank] = t
+        self.sh.barrier.wait()
+        if self.rank == 0:
+            self.sh.result = fn(self.sh.slots)
+            torch.cuda.synchronize()
+        self.sh.barrier.wait()
+        res = self.sh.result
+        self.sh.barrier.wait()
+        return res
+
+    def all_reduce_sum(self, t):
+        import torch
+        # summed in rank order in fp32, rounded once: what a tree/ring all-reduce of bf16 partials approximates
+        res = self._exchange(t, lambda ts: torch.stack([x.float() for x in ts]).sum(0))
+        t.copy_(res.to(t.dtype))
+        torch.cuda.synchronize()
+
+    def all_gather(self, t):
+        import torch
+        return self._exchange(t, lambda ts: torch.stack(list(ts))).clone()
