@@ -834,47 +834,70 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
           finish(v, c0);
         }
       } else {
-        // split tile: this CTA's slot 0 if its range starts inside the tile, else slot 1
-        const bool starts_here = rg.it0 >= sg.tile * p.k_blocks;
-        float* part = p.partials + ((size_t)blockIdx.x * 2 + (starts_here ? 0 : 1)) * (size_t)(BN * BM);
-#pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-          float v[32];
-          if (BN >= 32) tmem_ld32(t_addr + c0, v); else tmem_ld16(t_addr + c0, v);
-#pragma unroll
-          for (int i = 0; i < C::kChunk; ++i) part[(size_t)(c0 + i) * BM + etid] = v[i];
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&acc_empty[buf]);
-        // contributors of this tile: the CTAs whose ranges meet [tile*k_blocks, (tile+1)*k_blocks)
+        // Split tile.  Contributors = the CTAs whose ranges meet [tile*k_blocks, (tile+1)*k_blocks).  The
+        // first of them (the one holding the tile's first k-blocks) reaches this segment at the very end
+        // of its range, after every other contributor has long passed theirs, so it is the one that
+        // finishes the tile: the others publish an fp32 partial in scratch and bump the tile's counter;
+        // the finisher waits (bounded) for the counter, adds the partials to its own accumulator in CTA
+        // order -- deterministic -- and runs the epilogue.  It never writes a partial of its own.
         const long long ts = (long long)sg.tile * p.k_blocks, te = ts + p.k_blocks;
         const int c_first = (int)(ts / p.per_cta), c_last = (int)((te - 1) / p.per_cta);
-        __threadfence();
-        epi_bar_sync();
-        if (etid == 0) {
-          const int ticket = atomicAdd(&p.tickets[c_first], 1);
-          s_last = ticket == c_last - c_first;
-          if (s_last) p.tickets[c_first] = 0;  // ready for the next call
-        }
-        epi_bar_sync();
-        if (s_last) {
-          __threadfence();
+        if ((int)blockIdx.x != c_first) {
+          // slot 0 if this CTA's range starts inside the tile (always, except for c_first), kept general
+          const bool starts_here = rg.it0 >= ts;
+          float* part = p.partials + ((size_t)blockIdx.x * 2 + (starts_here ? 0 : 1)) * (size_t)(BN * BM);
 #pragma unroll 1
           for (int c0 = 0; c0 < BN; c0 += 32) {
             float v[32];
+            if (BN >= 32) tmem_ld32(t_addr + c0, v); else tmem_ld16(t_addr + c0, v);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = 0.f;
-            for (int cc = c_first; cc <= c_last; ++cc) {
-              const bool cc_starts_here = (long long)cc * p.per_cta >= ts;
-              const float* ps = p.partials + ((size_t)cc * 2 + (cc_starts_here ? 0 : 1)) * (size_t)(BN * BM);
-#pragma unroll
-              for (int i = 0; i < C::kChunk; ++i) v[i] += __ldcg(ps + (size_t)(c0 + i) * BM + etid);
-            }
-            finish(v, c0);
+            for (int i = 0; i < C::kChunk; ++i) part[(size_t)(c0 + i) * BM + etid] = v[i];
           }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&acc_empty[buf]);
+          __threadfence();
+          epi_bar_sync();
+          if (etid == 0) atomicAdd(&p.tickets[c_first], 1);
+        } else {
+          if (etid == 0) {
+            const int need = c_last - c_first;
+            bool got = false;
+            for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+              int seen;
+              asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(p.tickets + c_first) : "memory");
+              if (seen >= need) {
+                got = true;
+                break;
+              }
+              __nanosleep(64);
+            }
+            p.tickets[c_first] = 0;  // ready for the next call
+            s_last = got ? 1 : 0;
+            if (!got) atomicOr(p.status, 128);
+          }
+          epi_bar_sync();
+          const bool have = s_last != 0;
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 32) {
+            float v[32];
+            if (BN >= 32) tmem_ld32(t_addr + c0, v); else tmem_ld16(t_addr + c0, v);
+            if (c0 + 32 >= BN) {
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&acc_empty[buf]);
+            }
+            if (have) {
+              for (int cc = c_first + 1; cc <= c_last; ++cc) {
+                const float* ps = p.partials + ((size_t)cc * 2) * (size_t)(BN * BM);
+#pragma unroll
+                for (int i = 0; i < C::kChunk; ++i) v[i] += __ldcg(ps + (size_t)(c0 + i) * BM + etid);
+              }
+              finish(v, c0);
+            }
+          }
+          epi_bar_sync();  // s_last is reused by the next split segment
         }
-        epi_bar_sync();  // s_last is reused by the next split segment
       }
       ++j;
     }
