@@ -409,6 +409,50 @@ def kernel_rooflines(eng, pm, kv, B, slots, ops, torch, ctx, n_uniq, peak, reps=
     return out
 
 
+def run_operator_case(ops, synth, dev, torch):
+    """The operator micro-benchmark: y = x W^T + 2 (x A[id]) B[id], W [4096,4096], 16 rank-16 adapters,
+    T in {1, 8, 32, 128} (shapes of tvm/lora_only/single_rank.py).  CUDA-event time of the shrink +
+    projection pair in a graph over 20 weight copies (671 MB, beyond L2); one JSON line."""
+    peak, src = measured_peak()
+    rows = []
+    for T in (1, 8, 32, 128):
+        c = synth.operator_case(T, device=dev)
+        Ws = [ops.PackedWeight((torch.randn(4096, 4096, device=dev) * 0.02).to(torch.bfloat16)) for _ in range(20)]
+        st = ops.LoraStack(c["A"], c["B"], torch.full((N_ADAPTERS,), RANK, dtype=torch.int32, device=dev),
+                           torch.full((N_ADAPTERS,), c["scale"], device=dev), RANK, 1, (0, 4096)).pack_b()
+        slots = c["ids"].to(torch.int32)
+        out = torch.empty(T, 4096, dtype=torch.bfloat16, device=dev)
+        res = {}
+        for name, with_lora in (("lora", True), ("base", False)):
+            def body():
+                for W in Ws:
+                    if with_lora:
+                        ops.linear(c["x"], W, st, slots, out=out)  # shrink + projection with fused expand
+                    else:
+                        ops.linear(c["x"], W, out=out)
+            body()
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                body()
+            for _ in range(3):
+                g.replay()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(5):
+                g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            res[name] = 1e3 * e0.elapsed_time(e1) / (5 * len(Ws))
+        n_uniq = len(set(slots.tolist()))
+        by = 2 * 4096 * 4096 + n_uniq * 2 * RANK * (4096 + 4096) + 2 * T * 4096 * 2 + 4 * T
+        rows.append({"T": T, "us_with_lora": res["lora"], "us_base_only": res["base"],
+                     "lora_overhead_frac": res["lora"] / res["base"] - 1.0, "algorithmic_bytes": by,
+                     "achieved_gbs": by / (res["lora"] * 1e3), "frac_of_peak": by / (res["lora"] * 1e3) / peak})
+    print(json.dumps({"kernel_case": "operator", "peak_gbs": peak, "peak_source": src, "rows": rows}))
+
+
 def run_kernel_case(which):
     """A few launches of one hot kernel on a case sized for an ncu capture: operands larger than L2
     (126 MB) but well under 1 GB, decode shapes of the benchmark."""
@@ -418,6 +462,8 @@ def run_kernel_case(which):
     load("build").build()
     dev = torch.device("cuda", 0)
     T = N_REQ
+    if which == "operator":
+        return run_operator_case(ops, synth, dev, torch)
     if which == "linear":
         # the q/k/v projection of one layer with its LoRA stack: 4 weight copies = 403 MB
         c = synth.operator_case(T, 4096, 12288, N_ADAPTERS, RANK, device=dev)
@@ -458,7 +504,7 @@ def main():
     ap.add_argument("--skip-prefill", action="store_true",
                     help="profiling aid: fill the KV cache with seeded random values instead of running prefill "
                          "(the number is then not a bench value)")
-    ap.add_argument("--kernel-case", default="", choices=["", "linear", "attention"],
+    ap.add_argument("--kernel-case", default="", choices=["", "linear", "attention", "operator"],
                     help="profiling aid: launch one kernel a few times on a small case (> L2, < 1 GB) and exit")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

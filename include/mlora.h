@@ -122,6 +122,20 @@ int mlora_linear(const void* d_x, int64_t ldx, const void* d_W, void* d_y, int64
                  const int32_t* d_ranks, const float* d_scales, const int32_t* d_slots,
                  int32_t n_adapters, int32_t r_max, int32_t n_mod, const int32_t* h_mod_offsets,
                  int32_t flags, void* d_work, size_t work_bytes, void* stream);
+/* mlora_lora_shrink + mlora_linear as ONE call, i.e. the whole of
+ * base_layer(x) + bmm(bmm(x, A), B*scaling) (huggingface/custom_peft/lora_gatherbmm_linear_layer.py:15-20).
+ * d_A_all as for mlora_lora_shrink (rows beyond an adapter's rank zero); d_u [T, n_mod*r_max] float32 is
+ * scratch the call writes before it reads it.  Where the tensor-core kernel takes the call and its LoRA
+ * expand runs on the tensor cores (rank pitch 16/32/64/128, module boundaries multiples of 128), this is
+ * one launch: the otherwise idle output warps of every CTA compute a slice of u while the weight
+ * stream starts, and a bounded grid-wide counter in d_work publishes it (status bit 8 = that wait gave
+ * up).  Everywhere else it is the two launches.  d_work as for mlora_linear, and the same buffer must
+ * not be used by two calls that may run concurrently. */
+int mlora_lora_linear(const void* d_x, int64_t ldx, const void* d_W, void* d_y, int64_t ldy, int32_t T,
+                      int32_t in, int32_t out, const void* d_A_all, float* d_u, const void* d_B_all,
+                      const int32_t* d_ranks, const float* d_scales, const int32_t* d_slots,
+                      int32_t n_adapters, int32_t r_max, int32_t n_mod, const int32_t* h_mod_offsets,
+                      int32_t flags, void* d_work, size_t work_bytes, void* stream);
 
 /* ---- (b) fused residual add + RMSNorm ----------------------------------------------------------
  *   res[t,:] += delta[t,:] (skipped when d_delta == NULL);  out[t,:] = res * rsqrt(mean(res^2)+eps) * w

@@ -7,12 +7,13 @@ extern "C" size_t mlora_linear_workspace(int32_t T, int32_t in, int32_t out) {
   return linear_tc_workspace(T, in, out);
 }
 
-extern "C" int mlora_linear(const void* d_x, int64_t ldx, const void* d_W, void* d_y, int64_t ldy, int32_t T,
-                            int32_t in, int32_t out, const float* d_u, const void* d_B_all,
-                            const int32_t* d_ranks, const float* d_scales, const int32_t* d_slots,
-                            int32_t n_adapters, int32_t r_max, int32_t n_mod, const int32_t* h_mod_offsets,
-                            int32_t flags,
-                            void* d_work, size_t work_bytes, void* stream) {
+// d_A_all != NULL: the shrink is part of this call (one launch when the tensor-core kernel can take it,
+// else the shrink kernel first).
+static int linear_impl(const void* d_x, int64_t ldx, const void* d_W, void* d_y, int64_t ldy, int32_t T, int32_t in,
+                       int32_t out, const void* d_A_all, const float* d_u, const void* d_B_all,
+                       const int32_t* d_ranks, const float* d_scales, const int32_t* d_slots, int32_t n_adapters,
+                       int32_t r_max, int32_t n_mod, const int32_t* h_mod_offsets, int32_t flags, void* d_work,
+                       size_t work_bytes, void* stream) {
   MLORA_REQUIRE(T >= 0 && in > 0 && out > 0, "linear: bad sizes T=%d in=%d out=%d", T, in, out);
   MLORA_REQUIRE(in % 8 == 0 && ldx % 8 == 0, "linear: in and ldx must be multiples of 8 (in=%d ldx=%lld)", in,
                 (long long)ldx);
@@ -65,16 +66,44 @@ extern "C" int mlora_linear(const void* d_x, int64_t ldx, const void* d_W, void*
   }
   if (T == 0) return MLORA_OK;
   cudaStream_t st = (cudaStream_t)stream;
+  if (d_A_all) {
+    MLORA_REQUIRE(d_u && aligned16(d_A_all) && aligned16(d_u), "lora_linear: A_all and u must be non-null and 16-byte aligned");
+    const bool tc = !(flags & MLORA_FORCE_SIMT) && d_work && linear_tc_supported(a);
+    if (tc && linear_tc_can_fuse_shrink(a)) return launch_linear_tc(a, d_work, work_bytes, d_A_all, st);
+    const int rc = mlora_lora_shrink(d_x, ldx, d_A_all, d_ranks, d_slots, n_adapters, T, in, r_max, n_mod,
+                                     const_cast<float*>(d_u), stream);
+    if (rc != MLORA_OK) return rc;
+  }
   if (flags & MLORA_B_PACKED)
     MLORA_REQUIRE(d_u && !(flags & MLORA_FORCE_SIMT) && d_work, "linear: a packed B_all needs the tensor-core kernel");
   if (flags & (MLORA_W_PACKED | MLORA_B_PACKED)) {
     MLORA_REQUIRE(!(flags & MLORA_FORCE_SIMT) && d_work && linear_tc_supported(a),
                   "linear: a packed weight needs the tensor-core kernel (scratch buffer, 16-byte aligned operands)");
-    return launch_linear_tc(a, d_work, work_bytes, st);
+    return launch_linear_tc(a, d_work, work_bytes, nullptr, st);
   }
   if (!(flags & MLORA_FORCE_SIMT) && d_work && linear_tc_supported(a))
-    return launch_linear_tc(a, d_work, work_bytes, st);
+    return launch_linear_tc(a, d_work, work_bytes, nullptr, st);
   return launch_linear_simt(a, st);
+}
+
+extern "C" int mlora_linear(const void* d_x, int64_t ldx, const void* d_W, void* d_y, int64_t ldy, int32_t T,
+                            int32_t in, int32_t out, const float* d_u, const void* d_B_all,
+                            const int32_t* d_ranks, const float* d_scales, const int32_t* d_slots,
+                            int32_t n_adapters, int32_t r_max, int32_t n_mod, const int32_t* h_mod_offsets,
+                            int32_t flags, void* d_work, size_t work_bytes, void* stream) {
+  return linear_impl(d_x, ldx, d_W, d_y, ldy, T, in, out, nullptr, d_u, d_B_all, d_ranks, d_scales, d_slots,
+                     n_adapters, r_max, n_mod, h_mod_offsets, flags, d_work, work_bytes, stream);
+}
+
+extern "C" int mlora_lora_linear(const void* d_x, int64_t ldx, const void* d_W, void* d_y, int64_t ldy, int32_t T,
+                                 int32_t in, int32_t out, const void* d_A_all, float* d_u, const void* d_B_all,
+                                 const int32_t* d_ranks, const float* d_scales, const int32_t* d_slots,
+                                 int32_t n_adapters, int32_t r_max, int32_t n_mod,
+                                 const int32_t* h_mod_offsets, int32_t flags, void* d_work, size_t work_bytes,
+                                 void* stream) {
+  MLORA_REQUIRE(d_A_all && d_u, "lora_linear: A_all and the u scratch are required");
+  return linear_impl(d_x, ldx, d_W, d_y, ldy, T, in, out, d_A_all, d_u, d_B_all, d_ranks, d_scales, d_slots,
+                     n_adapters, r_max, n_mod, h_mod_offsets, flags, d_work, work_bytes, stream);
 }
 
 extern "C" size_t mlora_packed_weight_bytes(int32_t out, int32_t in) {

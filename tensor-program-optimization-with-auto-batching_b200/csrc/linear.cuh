@@ -68,7 +68,10 @@ int launch_linear_simt(const LinearArgs& a, cudaStream_t st);
 // Tensor-core (tcgen05) weight-streaming kernel; returns MLORA_OK or an error.
 bool linear_tc_supported(const LinearArgs& a);
 size_t linear_tc_workspace(int T, int in, int out);
-int launch_linear_tc(const LinearArgs& a, void* work, size_t work_bytes, cudaStream_t st);
+// lora_A != nullptr: the kernel computes the shrink itself (u is then scratch it writes before use);
+// returns MLORA_OK or an error.
+int launch_linear_tc(const LinearArgs& a, void* work, size_t work_bytes, const void* lora_A, cudaStream_t st);
+bool linear_tc_can_fuse_shrink(const LinearArgs& a);
 size_t packed_weight_bytes(int out, int in);
 size_t packed_lora_b_bytes(int n_adapters, int out, int r_max);
 int launch_pack_lora_b(const void* B, int n_adapters, int out, int r_max, void* Bp, cudaStream_t st);

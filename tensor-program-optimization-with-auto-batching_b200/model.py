@@ -19,6 +19,8 @@ adapters stacked per projection as A_all [N, n_mod*r_max, in] / B_all
 """
 from __future__ import annotations
 
+import os
+
 from dataclasses import dataclass, field
 
 import numpy as np
@@ -231,6 +233,8 @@ class Engine:
         ops.workspace(need, dev, "linear")
         ops.workspace(lib.mlora_paged_attention_workspace(T, m.Hq, m.D, 16), dev, "attn")
         self._graphs = {}
+        # shrink inside the projection kernel (one launch per projection) unless MLORA_FUSED_SHRINK=0
+        self.fuse_shrink = os.environ.get("MLORA_FUSED_SHRINK", "1") != "0"
 
     # ------------------------------------------------------------------------------------------
     def _proj(self, x, W, stack, slots, out, flags=0):
@@ -238,6 +242,8 @@ class Engine:
         if stack is not None and slots is not None:
             r_tot = stack.r_max * stack.n_mod
             u = self.u.view(-1)[: T * r_tot].view(T, r_tot)
+            if self.fuse_shrink:
+                return ops.linear(x, W, stack, slots, u=u, flags=flags, out=out, fuse_shrink=True)
             ops.lora_shrink(x, stack, slots, out=u)
             return ops.linear(x, W, stack, slots, u=u, flags=flags, out=out)
         return ops.linear(x, W, flags=flags, out=out)

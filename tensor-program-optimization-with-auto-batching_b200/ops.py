@@ -145,9 +145,11 @@ class PackedWeight:
         return True
 
 
-def linear(x, W, stack: LoraStack = None, slots=None, u=None, flags: int = 0, out=None, use_workspace=True):
+def linear(x, W, stack: LoraStack = None, slots=None, u=None, flags: int = 0, out=None, use_workspace=True,
+           fuse_shrink=False):
     """y = x W^T (+ LoRA expand of ``u``) ; see ``mlora_linear`` in include/mlora.h.
-    ``W`` is a bf16 [out,in] tensor or a :class:`PackedWeight`."""
+    ``W`` is a bf16 [out,in] tensor or a :class:`PackedWeight`.  ``fuse_shrink``: ``u`` is scratch and
+    the shrink is part of the call (``mlora_lora_linear``: one launch where the kernel can take it)."""
     _need_cuda(x, W)
     if x.dtype != torch.bfloat16 or W.dtype != torch.bfloat16:
         raise ValueError("mlora.linear needs bf16 x and W")
@@ -162,11 +164,20 @@ def linear(x, W, stack: LoraStack = None, slots=None, u=None, flags: int = 0, ou
         out = torch.empty(T, cols, dtype=torch.float32 if flags & OUT_F32 else torch.bfloat16, device=x.device)
     mod = None
     if stack is not None and u is None:
-        u = lora_shrink(x, stack, slots)
+        if fuse_shrink:
+            u = torch.empty(T, stack.r_max * stack.n_mod, dtype=torch.float32, device=x.device)
+        else:
+            u = lora_shrink(x, stack, slots)
     if stack is not None and stack.n_mod > 1 and not flags & SILU_MUL:
         mod = (C.c_int32 * (stack.n_mod + 1))(*stack.mod_offsets)
     wb = _lib.lib().mlora_linear_workspace(T, K, N) if use_workspace else 0
     ws = workspace(wb, x.device, "linear") if wb else None
+    if stack is not None and fuse_shrink:
+        check(_lib.lib().mlora_lora_linear(
+            _ptr(x), x.stride(0), _ptr(W), _ptr(out), out.stride(0), T, K, N, _ptr(stack.A_all), _ptr(u),
+            _ptr(stack.B_all), _ptr(stack.ranks), _ptr(stack.scales), _ptr(slots), stack.A_all.shape[0],
+            stack.r_max, stack.n_mod, mod, flags, _ptr(ws), wb, _stream()), "mlora_lora_linear")
+        return out
     check(_lib.lib().mlora_linear(
         _ptr(x), x.stride(0), _ptr(W), _ptr(out), out.stride(0), T, K, N,
         _ptr(u) if stack is not None else None, _ptr(stack.B_all) if stack is not None else None,

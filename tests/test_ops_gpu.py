@@ -431,3 +431,59 @@ def test_packed_lora_stack_equals_row_major(ops, cuda, T, r):
     st2 = _stack(ops, A, B, [r] * n_ad, [1.5] * n_ad, cuda, 3, (0, 128, 256, 384)).pack_b()
     y1 = ops.linear(x, ops.PackedWeight(W), st2, slots)
     assert torch.equal(y0, y1)
+
+
+@pytest.mark.parametrize("T,r,K,N", [(1, 16, 4096, 4096), (32, 16, 4096, 1536), (9, 32, 1024, 384), (70, 64, 688, 384),
+                                     (200, 16, 512, 4096)])
+def test_shrink_inside_the_projection_kernel(ops, cuda, T, r, K, N):
+    """mlora_lora_linear (shrink computed by the projection kernel's own warps, published grid-wide) against
+    the two-launch form: the shrink sums in a different order, so equal within bf16 rounding; repeated calls on one
+    scratch buffer (the arrival counter resets itself) and no expired wait."""
+    g = torch.Generator().manual_seed(T * 7 + r)
+    n_ad, third = 5, N // 3
+    offs = (0, third, 2 * third, N)
+    x = torch.randn(T, K, generator=g).bfloat16().to(cuda)
+    W = (torch.randn(N, K, generator=g) * 0.05).bfloat16().to(cuda)
+    A = (torch.randn(n_ad, 3 * r, K, generator=g) * 0.05).bfloat16()
+    B = (torch.randn(n_ad, N, r, generator=g) * 0.05).bfloat16()
+    ranks = [r, r // 2, r, 8, r]
+    for s in range(n_ad):
+        for m in range(3):
+            A[s, m * r + ranks[s]:(m + 1) * r] = 0
+        B[s, :, ranks[s]:] = 0
+    slots = torch.randint(-1, n_ad, (T,), generator=g).int().to(cuda)
+    st = _stack(ops, A, B, ranks, [1.5, 2.0, 0.5, 1.0, 3.0], cuda, 3, offs).pack_b()
+    Wp = ops.PackedWeight(W)
+    want = ops.linear(x, Wp, st, slots)
+    u_want = ops.lora_shrink(x, st, slots)
+    for _ in range(3):
+        u = torch.full((T, 3 * st.r_max), float("nan"), device=cuda)
+        got = ops.linear(x, Wp, st, slots, u=u, fuse_shrink=True)
+        torch.cuda.synchronize()
+        assert int(ops.workspace(4, cuda, "linear")[:4].view(torch.int32)) == 0, "a bounded wait expired"
+        rows = (slots >= 0).nonzero().flatten()
+        torch.testing.assert_close(u[rows], u_want[rows], atol=1e-3, rtol=1e-4)
+        torch.testing.assert_close(got.float(), want.float(), atol=ATOL, rtol=RTOL)
+
+
+def test_shrink_inside_the_projection_kernel_gate_up(ops, cuda):
+    """The same through the interleaved gate/up projection with SiLU*up in the output write."""
+    g = torch.Generator().manual_seed(5)
+    T, K, I, r, n_ad = 24, 512, 1024, 16, 4
+    x = torch.randn(T, K, generator=g).bfloat16().to(cuda)
+    Wg = (torch.randn(I, K, generator=g) * 0.05).bfloat16()
+    Wu = (torch.randn(I, K, generator=g) * 0.05).bfloat16()
+    A = (torch.randn(n_ad, 2 * r, K, generator=g) * 0.05).bfloat16()
+    Bg = (torch.randn(n_ad, I, r, generator=g) * 0.05).bfloat16()
+    Bu = (torch.randn(n_ad, I, r, generator=g) * 0.05).bfloat16()
+    model = load("model")
+    z = torch.zeros_like(Bg)
+    B = torch.stack([model.interleave_gate_up(torch.cat([Bg, z], 2)[s], torch.cat([z, Bu], 2)[s]) for s in range(n_ad)])
+    W = model.interleave_gate_up(Wg, Wu).to(cuda)
+    slots = torch.randint(-1, n_ad, (T,), generator=g).int().to(cuda)
+    st = ops.LoraStack(A.to(cuda), B.to(cuda), _i32([r] * n_ad, cuda), torch.full((n_ad,), 2.0, device=cuda), r, 2, None)
+    want = ops.linear(x, W, st, slots, flags=ops.SILU_MUL)
+    got = ops.linear(x, W, st, slots, flags=ops.SILU_MUL, fuse_shrink=True)
+    torch.cuda.synchronize()
+    assert int(ops.workspace(4, cuda, "linear")[:4].view(torch.int32)) == 0, "a bounded wait expired"
+    torch.testing.assert_close(got.float(), want.float(), atol=ATOL, rtol=RTOL)
