@@ -411,8 +411,8 @@ def kernel_rooflines(eng, pm, kv, B, slots, ops, torch, ctx, n_uniq, peak, reps=
 
 def run_operator_case(ops, synth, dev, torch):
     """The operator micro-benchmark: y = x W^T + 2 (x A[id]) B[id], W [4096,4096], 16 rank-16 adapters,
-    T in {1, 8, 32, 128} (shapes of tvm/lora_only/single_rank.py).  CUDA-event time of the shrink +
-    projection pair in a graph over 20 weight copies (671 MB, beyond L2); one JSON line."""
+    T in {1, 8, 32, 128} (shapes of tvm/lora_only/single_rank.py).  CUDA-event time of the one-launch
+    shrink + projection + expand (and of the two-launch form) in a graph over 20 weight copies (671 MB, beyond L2); one JSON line."""
     peak, src = measured_peak()
     rows = []
     for T in (1, 8, 32, 128):
@@ -423,11 +423,14 @@ def run_operator_case(ops, synth, dev, torch):
         slots = c["ids"].to(torch.int32)
         out = torch.empty(T, 4096, dtype=torch.bfloat16, device=dev)
         res = {}
-        for name, with_lora in (("lora", True), ("base", False)):
+        u = torch.empty(T, RANK, dtype=torch.float32, device=dev)
+        for name in ("lora", "lora_two_launches", "base"):
             def body():
                 for W in Ws:
-                    if with_lora:
-                        ops.linear(c["x"], W, st, slots, out=out)  # shrink + projection with fused expand
+                    if name == "lora":  # one launch: shrink, projection and expand
+                        ops.linear(c["x"], W, st, slots, u=u, out=out, fuse_shrink=True)
+                    elif name == "lora_two_launches":  # shrink kernel, then projection with fused expand
+                        ops.linear(c["x"], W, st, slots, out=out)
                     else:
                         ops.linear(c["x"], W, out=out)
             body()
@@ -447,7 +450,8 @@ def run_operator_case(ops, synth, dev, torch):
             res[name] = 1e3 * e0.elapsed_time(e1) / (5 * len(Ws))
         n_uniq = len(set(slots.tolist()))
         by = 2 * 4096 * 4096 + n_uniq * 2 * RANK * (4096 + 4096) + 2 * T * 4096 * 2 + 4 * T
-        rows.append({"T": T, "us_with_lora": res["lora"], "us_base_only": res["base"],
+        rows.append({"T": T, "us_with_lora": res["lora"], "us_with_lora_two_launches": res["lora_two_launches"],
+                     "us_base_only": res["base"],
                      "lora_overhead_frac": res["lora"] / res["base"] - 1.0, "algorithmic_bytes": by,
                      "achieved_gbs": by / (res["lora"] * 1e3), "frac_of_peak": by / (res["lora"] * 1e3) / peak})
     print(json.dumps({"kernel_case": "operator", "peak_gbs": peak, "peak_source": src, "rows": rows}))

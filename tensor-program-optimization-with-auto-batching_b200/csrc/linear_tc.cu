@@ -401,11 +401,13 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
     // an adapter's rank are zero in A_all, so they are simply computed.  All CTAs of this persistent
     // grid are co-resident (grid <= SM count), and the wait below is bounded.
     const int ew = (warp & 3), n_items = a.T * (r_tot / 4);
+    // CTAs that take part: those with work (the others returned above)
+    const int n_active = (int)min((long long)gridDim.x, ((long long)p.n_tiles * p.k_blocks + p.per_cta - 1) / p.per_cta);
     int gen0 = 0;
     if (warp == 4 && lane == 0) {  // epilogue thread 0: generation before anyone of this launch arrives
       asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(gen0) : "l"(p.status + 2) : "memory");
     }
-    for (int item = blockIdx.x * 4 + ew; item < n_items; item += gridDim.x * 4) {
+    for (int item = blockIdx.x * 4 + ew; item < n_items; item += n_active * 4) {
       const int t = item / (r_tot / 4), j0 = (item - t * (r_tot / 4)) * 4;
       const int slot = a.slots[t];
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
@@ -449,7 +451,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
     epi_bar_sync();
     if (warp == 4 && lane == 0) {
       const int ticket = atomicAdd(p.status + 1, 1);
-      if (ticket == (int)gridDim.x - 1) {
+      if (ticket == n_active - 1) {
         p.status[1] = 0;  // ready for the next launch
         __threadfence();
         atomicAdd(p.status + 2, 1);

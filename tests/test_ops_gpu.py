@@ -433,8 +433,8 @@ def test_packed_lora_stack_equals_row_major(ops, cuda, T, r):
     assert torch.equal(y0, y1)
 
 
-@pytest.mark.parametrize("T,r,K,N", [(1, 16, 4096, 4096), (32, 16, 4096, 1536), (9, 32, 1024, 384), (70, 64, 688, 384),
-                                     (200, 16, 512, 4096)])
+@pytest.mark.parametrize("T,r,K,N", [(1, 16, 4096, 3072), (32, 16, 4096, 1536), (9, 32, 1024, 384), (70, 64, 688, 384),
+                                     (200, 16, 512, 3072)])
 def test_shrink_inside_the_projection_kernel(ops, cuda, T, r, K, N):
     """mlora_lora_linear (shrink computed by the projection kernel's own warps, published grid-wide) against
     the two-launch form: the shrink sums in a different order, so equal within bf16 rounding; repeated calls on one
