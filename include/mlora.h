@@ -72,9 +72,16 @@ int mlora_bucket_sort(const int32_t* d_tids, const int32_t* d_wids, int32_t n, i
  * synthesised at tvm/llama_auto_batcher/compile_tvm.py:106-112) and of the two bmm's of
  * GatherBMMLinear.forward (huggingface/custom_peft/lora_gatherbmm_linear_layer.py:16-19).
  *   d_x [T, in] bf16 (row stride ldx elements); d_A_all [N, n_mod*r_max, in] bf16;
- *   d_ranks [N] int32 (rank of each adapter slot, <= r_max; rows >= rank are never read);
+ *   d_ranks [N] int32 (rank of each adapter slot, <= r_max; rows of A_all at or beyond the rank
+ *   must be zero: the decode-size kernel skips them, the prefill-size kernel multiplies them);
  *   d_slots [T] int32 (adapter slot of each row; < 0 or >= n_adapters = none -> u row is zero);
- *   d_u [T, n_mod*r_max] float32.  n_mod modules share the input (q,k,v or gate,up). */
+ *   d_u [T, n_mod*r_max] float32.  n_mod modules share the input (q,k,v or gate,up).
+ * T < 256: one warp per (row, rank index) on CUDA cores.  T >= 256 (prefill) with n_mod*r_max <= 256:
+ * a segmented grouped GEMM on the tensor cores (tcgen05, TMA fed): one CTA per 128 rows, one
+ * accumulator per distinct adapter among them, rows pick their adapter's columns on the way out
+ * (the segmented "take_matmul" of tvm/custom/fuse_take_matmul.py:78-111 without the sort: rows of
+ * one request are contiguous already).  Should one of that kernel's bounded waits expire, the
+ * affected rows of d_u are NaN. */
 int mlora_lora_shrink(const void* d_x, int64_t ldx, const void* d_A_all, const int32_t* d_ranks,
                       const int32_t* d_slots, int32_t n_adapters, int32_t T, int32_t in, int32_t r_max,
                       int32_t n_mod, float* d_u, void* stream);

@@ -72,6 +72,10 @@ size_t linear_tc_workspace(int T, int in, int out);
 // returns MLORA_OK or an error.
 int launch_linear_tc(const LinearArgs& a, void* work, size_t work_bytes, const void* lora_A, cudaStream_t st);
 bool linear_tc_can_fuse_shrink(const LinearArgs& a);
+// LoRA shrink as a segmented grouped GEMM on the tensor cores (prefill sizes).
+bool lora_shrink_tc_supported(const void* x, int64_t ldx, const void* A_all, const float* u, int T, int in, int r_tot);
+int launch_lora_shrink_tc(const void* x, int64_t ldx, const void* A_all, const int32_t* slots, int n_adapters, int T,
+                          int in, int r_tot, float* u, cudaStream_t st);
 size_t packed_weight_bytes(int out, int in);
 size_t packed_lora_b_bytes(int n_adapters, int out, int r_max);
 int launch_pack_lora_b(const void* B, int n_adapters, int out, int r_max, void* Bp, cudaStream_t st);

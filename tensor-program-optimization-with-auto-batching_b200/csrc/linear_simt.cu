@@ -143,8 +143,10 @@ extern "C" int mlora_lora_shrink(const void* d_x, int64_t ldx, const void* d_A_a
   MLORA_REQUIRE(d_x && d_A_all && d_ranks && d_slots && d_u, "lora_shrink: null pointer");
   MLORA_REQUIRE(aligned16(d_x) && aligned16(d_A_all), "lora_shrink: x and A_all must be 16-byte aligned");
   if (T == 0) return MLORA_OK;
-  MLORA_REQUIRE(T <= 65535, "lora_shrink: T=%d exceeds 65535 rows per call", T);
   const int r_tot = r_max * n_mod;
+  if (lora_shrink_tc_supported(d_x, ldx, d_A_all, d_u, T, in, r_tot))
+    return launch_lora_shrink_tc(d_x, ldx, d_A_all, d_slots, n_adapters, T, in, r_tot, d_u, (cudaStream_t)stream);
+  MLORA_REQUIRE(T <= 65535, "lora_shrink: T=%d exceeds 65535 rows per call", T);
   dim3 grid((r_tot + 7) / 8, T);
   launch_pdl(lora_shrink_kernel, grid, 256, 0, (cudaStream_t)stream, (const bf16*)d_x, ldx, (const bf16*)d_A_all, d_ranks,
              d_slots, n_adapters, in, r_max, r_tot, d_u);

@@ -487,3 +487,36 @@ def test_shrink_inside_the_projection_kernel_gate_up(ops, cuda):
     torch.cuda.synchronize()
     assert int(ops.workspace(4, cuda, "linear")[:4].view(torch.int32)) == 0, "a bounded wait expired"
     torch.testing.assert_close(got.float(), want.float(), atol=ATOL, rtol=RTOL)
+
+
+@pytest.mark.parametrize("T,K,r,n_mod,mixing", [(256, 4096, 16, 3, "runs"), (300, 688, 8, 3, "runs"), (1000, 1024, 64, 3, "runs"),
+                                                (384, 512, 16, 1, "random"), (257, 4096, 64, 2, "random"),
+                                                (512, 256, 128, 2, "random")])
+def test_prefill_shrink_on_tensor_cores(ops, cuda, T, K, r, n_mod, mixing):
+    """T >= 256 rows take the grouped-GEMM shrink: contiguous runs of one adapter (prompt rows) and fully mixed
+    rows (many distinct adapters per 128-row tile -> several passes), rows without adapter, ragged T and K."""
+    g = torch.Generator().manual_seed(T + r)
+    n_ad = 24
+    x = torch.randn(T, K, generator=g).bfloat16()
+    A = (torch.randn(n_ad, n_mod * r, K, generator=g) * 0.05).bfloat16()
+    ranks = [(r, r // 2, r)[s % 3] for s in range(n_ad)]
+    for s in range(n_ad):
+        for m in range(n_mod):
+            A[s, m * r + ranks[s]:(m + 1) * r] = 0
+    if mixing == "runs":
+        ids = torch.randint(-1, n_ad, (T // 50 + 1,), generator=g)
+        slots = ids.repeat_interleave(50)[:T].int()
+    else:
+        slots = torch.randint(-1, n_ad, (T,), generator=g).int()
+    slots[-1] = n_ad + 3  # out of range = no adapter
+    B = torch.zeros(n_ad, 128, r, dtype=torch.bfloat16)
+    st = ops.LoraStack(A.to(cuda), B.to(cuda), _i32(ranks, cuda), torch.ones(n_ad, device=cuda), r, n_mod,
+                       tuple(range(0, 128 * n_mod + 1, 128)) if n_mod > 1 else None)
+    u = torch.full((T, n_mod * r), float("nan"), device=cuda)
+    ops.lora_shrink(x.to(cuda), st, slots.to(cuda), out=u)
+    want = torch.zeros(T, n_mod * r)
+    for t in range(T):
+        s = int(slots[t])
+        if 0 <= s < n_ad:
+            want[t] = A[s].float() @ x[t].float()
+    torch.testing.assert_close(u.cpu(), want, atol=2e-3, rtol=1e-4)
