@@ -480,6 +480,40 @@ def run_kernel_case(which):
         out = torch.empty(T, 12288, dtype=torch.bfloat16, device=dev)
         for i in range(6):
             ops.linear(c["x"], Ws[i % 4], st, slots, u=u, out=out)
+    elif which == "prefill":
+        # prefill-size q/k/v projection: 8192 prompt rows (16 requests x 512, one adapter per request), shrink as
+        # a grouped GEMM + projection with the expand as extra MMA stages; CUDA-event TFLOP/s of the pair
+        T = 8192
+        c = synth.operator_case(T, 4096, 12288, N_ADAPTERS, RANK, device=dev)
+        W = ops.PackedWeight((torch.randn(12288, 4096, device=dev) * 0.02).to(torch.bfloat16))
+        A = torch.cat([c["A"]] * 3, 1).contiguous()
+        st = ops.LoraStack(A, c["B"], torch.full((N_ADAPTERS,), RANK, dtype=torch.int32, device=dev),
+                           torch.full((N_ADAPTERS,), ALPHA / RANK, device=dev), RANK, 3, (0, 4096, 8192, 12288)).pack_b()
+        slots = torch.arange(T, device=dev, dtype=torch.int32) // 512 % N_ADAPTERS
+        out = torch.empty(T, 12288, dtype=torch.bfloat16, device=dev)
+        u = torch.empty(T, 3 * RANK, dtype=torch.float32, device=dev)
+        res = {}
+        for name in ("base", "lora"):
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+            for i in range(5):
+                if i == 2:
+                    ev[0].record()
+                if name == "lora":
+                    ops.lora_shrink(c["x"], st, slots, out=u)
+                    ops.linear(c["x"], W, st, slots, u=u, out=out)
+                else:
+                    ops.linear(c["x"], W, out=out)
+            ev[1].record()
+            torch.cuda.synchronize()
+            res[name] = ev[0].elapsed_time(ev[1]) / 3
+        fl = 2.0 * T * 4096 * 12288
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
+        tpk = float(peaks.get("bf16_tflops", 1590.0))  # burst figure: the kernel is timed alone
+        print(json.dumps({"kernel_case": which, "T": T, "ms_base": res["base"], "ms_with_lora": res["lora"],
+                          "tflops_base": fl / res["base"] / 1e9, "tflops_with_lora": (fl + 2.0 * T * 48 * (4096 + 4096)) / res["lora"] / 1e9,
+                          "peak_tflops": tpk, "frac_base": fl / res["base"] / 1e9 / tpk,
+                          "status": int(ops.workspace(4, dev, "linear")[:4].view(torch.int32)), "launches": ops.launch_count()}))
+        return
     else:
         # one layer's attention at context 576: 32 rows x 32 heads, 302 MB of KV
         Hq = Hkv = 32
@@ -508,7 +542,7 @@ def main():
     ap.add_argument("--skip-prefill", action="store_true",
                     help="profiling aid: fill the KV cache with seeded random values instead of running prefill "
                          "(the number is then not a bench value)")
-    ap.add_argument("--kernel-case", default="", choices=["", "linear", "attention", "operator"],
+    ap.add_argument("--kernel-case", default="", choices=["", "linear", "attention", "operator", "prefill"],
                     help="profiling aid: launch one kernel a few times on a small case (> L2, < 1 GB) and exit")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

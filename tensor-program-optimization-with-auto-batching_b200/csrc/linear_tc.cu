@@ -20,6 +20,8 @@
 //
 // Every mbarrier wait is bounded; on expiry the CTA records a code in the status word at the start
 // of the scratch buffer, stops issuing work, and leaves after freeing its TMEM.
+#include <stdlib.h>
+
 #include "linear.cuh"
 #include "tc_ptx.cuh"
 
@@ -39,6 +41,9 @@ struct TcParams {
   int k_blocks;    // ceil(in / BK)
   int row_tiles;   // ceil(out / BM)
   int n_tiles;     // row_tiles * token tiles
+  int tok_tiles;
+  int wave_gt;     // 0: stream-K ranges; > 0: whole tiles, token tiles taken in groups of this many
+  int wave_full, wave_ch, wave_ch_last;  // full groups, tiles per CTA in a full group / in the narrower last one
   int per_cta;     // iterations (tile, k-block) per CTA
   int lora_mode;   // 0 none, 1 expand on CUDA cores in the epilogue, 2 expand on the tensor cores
   int lora_sub;    // K elements of one LoRA stage (16, 32 or 64 = row bytes 32, 64, 128)
@@ -149,7 +154,9 @@ struct Cfg {
   static constexpr int kXBytes = BN * BK * 2;    // token-tile stage
   static constexpr int kXStages = BN >= 64 ? 4 : 8;  // token tiles come from L2: a shallower ring is enough
   // barriers | 7 integer lists of BN (token slots / distinct adapters per role) | staged shrink outputs
-  static constexpr int kCacheBytes = 16 * 1024;  // LoRA B operands (scaled, masked shrink outputs) of a token tile
+  // LoRA B operands (scaled, masked shrink outputs) of a token tile; prefill-size tiles get room for a rank-128
+  // pitch (interleaved gate/up at rank 64) so the operands are built once per token tile, not once per tile
+  static constexpr int kCacheBytes = (BN >= 128 ? 48 : 16) * 1024;
   static constexpr int kOutBytes = 32 * BM * 4;  // staging of one 32-token output chunk (fp32 worst case)
   static constexpr int kAuxBytes = 1024 + 8 * BN * 4 + kStageUMax + kCacheBytes + kOutBytes;
   static constexpr int kBudget = 227 * 1024 - 1024 /*alignment slack*/ - 64 /*static*/;
@@ -173,15 +180,54 @@ struct Range {
 struct Segment {
   int tile, kb0, kb1;
 };
+// Prefill sizes (many token tiles): whole tiles only.  The token tiles are taken in groups of `wave_gt`;
+// inside a group the tiles are ordered token tile major / row tile minor and cut into equal contiguous chunks,
+// one per CTA.  All CTAs walk their chunks in step, so at any time the grid works on wave_gt token tiles
+// (L2 resident) and a handful of row tiles that many CTAs share, instead of every CTA pulling its own
+// operands from HBM; and a CTA's consecutive tiles share the token tile (and mostly the module), so the
+// LoRA operands it caches in shared memory are rebuilt rarely.
+// Slot `lt` of this CTA's walk -> tile id (token tile * row_tiles + row tile), or -1 where its chunk of that
+// group is shorter than the longest.
+__device__ __forceinline__ int wave_tile(const TcParams& p, int lt) {
+  int group, qi, gt, ch;
+  const int full_slots = p.wave_full * p.wave_ch;
+  if (lt < full_slots) {
+    group = lt / p.wave_ch;
+    qi = lt - group * p.wave_ch;
+    gt = p.wave_gt;
+    ch = p.wave_ch;
+  } else {
+    group = p.wave_full;
+    qi = lt - full_slots;
+    gt = p.tok_tiles - group * p.wave_gt;
+    ch = p.wave_ch_last;
+  }
+  const int q = (int)blockIdx.x * ch + qi;
+  if (q >= p.row_tiles * gt) return -1;
+  const int j = q / p.row_tiles;
+  return (group * p.wave_gt + j) * p.row_tiles + (q - j * p.row_tiles);
+}
 __device__ __forceinline__ Range cta_range(const TcParams& p, int cta) {
+  if (p.wave_gt > 0) return Range{0, (p.wave_full * p.wave_ch + p.wave_ch_last) * p.k_blocks};
   const long long total = (long long)p.n_tiles * p.k_blocks;
   long long a = (long long)cta * p.per_cta, b = a + p.per_cta;
   if (a > total) a = total;
   if (b > total) b = total;
   return Range{(int)a, (int)b};
 }
+// Next piece of work of this CTA; tile < 0: none left.
 __device__ __forceinline__ Segment next_segment(const TcParams& p, int& it, int it1) {
   Segment s;
+  if (p.wave_gt > 0) {
+    s.tile = -1;
+    s.kb0 = 0;
+    s.kb1 = p.k_blocks;
+    while (it < it1 && s.tile < 0) {
+      s.tile = wave_tile(p, it / p.k_blocks);
+      it += p.k_blocks;
+    }
+    return s;
+  }
   s.tile = it / p.k_blocks;
   s.kb0 = it - s.tile * p.k_blocks;
   s.kb1 = min(p.k_blocks, s.kb0 + (it1 - it));
@@ -262,7 +308,9 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
   // starts streaming at once (weights are constant inputs), every other role first waits until the
   // kernels before it have completed.
   pdl_launch_dependents();
-  const int tok_tile0 = (rg.it0 / p.k_blocks) / p.row_tiles;
+  int first_it = rg.it0;
+  const int first_tile = next_segment(p, first_it, rg.it1).tile;
+  const int tok_tile0 = (first_tile < 0 ? 0 : first_tile) / p.row_tiles;
   const bool stage_u2 = p.lora_mode == 2 && (size_t)BN * r_tot * sizeof(float) <= (size_t)kStageUMax;
   if (warp != 0) pdl_wait();
   if (p.fused_shrink && warp >= 2 && warp <= 5) {
@@ -385,6 +433,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
     bool ok = true;
     while (it < rg.it1 && ok) {
       const Segment sg = next_segment(p, it, rg.it1);
+      if (sg.tile < 0) break;
       const int row_tile = sg.tile % p.row_tiles, tok_tile = sg.tile / p.row_tiles;
       if (lane == 0) {
         int nn = n;
@@ -458,6 +507,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
     bool ok = true;
     while (it < rg.it1 && ok) {
       const Segment sg = next_segment(p, it, rg.it1);
+      if (sg.tile < 0) break;
       const int row_tile = sg.tile % p.row_tiles, tok_tile = sg.tile / p.row_tiles;
       if (lane == 0) {
         int nn = n;
@@ -518,21 +568,41 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
           for (int i = lane; i < n_vec; i += 32) reinterpret_cast<uint4*>(s_cache)[i] = make_uint4(0u, 0u, 0u, 0u);
           __syncwarp();
           const int per_row = chunks * p.n_sub;
-          for (int idx = lane; idx < BN * per_row; idx += 32) {
-            const int nrow = idx / per_row, rem = idx - nrow * per_row;
-            const int sb = rem / chunks, c = rem - sb * chunks;
-            const int slot = x_tok[nrow];
-            if (slot < 0) continue;
-            int sgi = 0;
-            while (x_list[sgi] != slot) ++sgi;  // slot is in the list by construction
-            const float sc = x_scale[sgi];
-            const float* ur = (stage_u ? s_u + nrow * r_tot : a.u + (size_t)(t0 + nrow) * r_tot) + u_off +
-                              sb * p.lora_sub + c * 8;
-            float f[8];
+          // four items per lane and step, their shrink outputs requested before the first is used (the
+          // loads are L2 round trips when the outputs are not staged in shared memory)
+          for (int base = lane; base < BN * per_row; base += 32 * 4) {
+            float4 lo[4], hi[4];
+            int nr[4], off[4];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) f[e] = ur[e] * sc;
-            const int sw = rb == 128 ? (nrow & 7) : rb == 64 ? ((nrow >> 1) & 3) : ((nrow >> 2) & 1);
-            *reinterpret_cast<uint4*>(s_cache + (sgi * p.n_sub + sb) * BN * rb + nrow * rb + ((c ^ sw) << 4)) = pack8(f);
+            for (int b = 0; b < 4; ++b) {
+              const int idx = base + b * 32;
+              nr[b] = -1;
+              if (idx < BN * per_row) {
+                const int nrow = idx / per_row, rem = idx - nrow * per_row;
+                const int sb = rem / chunks, c = rem - sb * chunks;
+                if (x_tok[nrow] >= 0) {
+                  nr[b] = nrow;
+                  off[b] = sb * 256 + c;
+                  const float* ur = (stage_u ? s_u + nrow * r_tot : a.u + (size_t)(t0 + nrow) * r_tot) + u_off +
+                                    sb * p.lora_sub + c * 8;
+                  lo[b] = *reinterpret_cast<const float4*>(ur);
+                  hi[b] = *reinterpret_cast<const float4*>(ur + 4);
+                }
+              }
+            }
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+              if (nr[b] < 0) continue;
+              const int nrow = nr[b], sb = off[b] >> 8, c = off[b] & 255;
+              const int slot = x_tok[nrow];
+              int sgi = 0;
+              while (x_list[sgi] != slot) ++sgi;  // slot is in the list by construction
+              const float sc = x_scale[sgi];
+              const float f[8] = {lo[b].x * sc, lo[b].y * sc, lo[b].z * sc, lo[b].w * sc,
+                                  hi[b].x * sc, hi[b].y * sc, hi[b].z * sc, hi[b].w * sc};
+              const int sw = rb == 128 ? (nrow & 7) : rb == 64 ? ((nrow >> 1) & 3) : ((nrow >> 2) & 1);
+              *reinterpret_cast<uint4*>(s_cache + (sgi * p.n_sub + sb) * BN * rb + nrow * rb + ((c ^ sw) << 4)) = pack8(f);
+            }
           }
         }
         for (int sgi = 0; sgi < n_seg && ok && !cached; ++sgi) {
@@ -589,6 +659,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
     bool ok = true;
     while (it < rg.it1 && ok) {
       const Segment sg = next_segment(p, it, rg.it1);
+      if (sg.tile < 0) break;
       const int row_tile = sg.tile % p.row_tiles, tok_tile = sg.tile / p.row_tiles;
       const int buf = j & 1;
       const uint32_t d_tmem = tmem_base + buf * BN;
@@ -701,6 +772,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
 
     while (it < rg.it1) {
       const Segment sg = next_segment(p, it, rg.it1);
+      if (sg.tile < 0) break;
       const int row_tile = sg.tile % p.row_tiles, tok_tile = sg.tile / p.row_tiles;
       const int row = row_tile * BM + etid;
       const int t0 = tok_tile * BN;
@@ -881,7 +953,7 @@ int sm_count() {
 }
 
 struct Plan {
-  int bn, row_tiles, tok_tiles, k_blocks, grid, per_cta;
+  int bn, row_tiles, tok_tiles, k_blocks, grid, per_cta, wave_gt, wave_full, wave_ch, wave_ch_last;
 };
 
 Plan make_plan(int T, int in, int out) {
@@ -892,6 +964,27 @@ Plan make_plan(int T, int in, int out) {
   pl.k_blocks = (in + BK - 1) / BK;
   const long long total = (long long)pl.row_tiles * pl.tok_tiles * pl.k_blocks;
   long long grid = sm_count();
+  pl.wave_gt = pl.wave_full = pl.wave_ch = pl.wave_ch_last = 0;
+  const long long n_tiles = (long long)pl.row_tiles * pl.tok_tiles;
+  if (pl.tok_tiles >= 4 && n_tiles >= 8 * grid) {
+    // enough whole tiles that the unfilled last wave costs little: waves of (token tiles x row tiles)
+    int gt = (int)grid;
+    for (int d = 1; d <= 48 && d <= (int)grid; ++d)
+      if (grid % d == 0) gt = d;  // largest divisor of the grid up to 48 (148 SMs -> 37)
+    static const int forced = [] {
+      const char* e = getenv("MLORA_WAVE_GT");  // experiments: token tiles per wave
+      return e ? atoi(e) : 0;
+    }();
+    if (forced > 0) gt = forced;
+    pl.wave_gt = gt < pl.tok_tiles ? gt : pl.tok_tiles;
+    pl.wave_full = pl.tok_tiles / pl.wave_gt;
+    const int gt_last = pl.tok_tiles - pl.wave_full * pl.wave_gt;
+    pl.wave_ch = (int)(((long long)pl.row_tiles * pl.wave_gt + grid - 1) / grid);
+    pl.wave_ch_last = (int)(((long long)pl.row_tiles * gt_last + grid - 1) / grid);
+    pl.per_cta = (pl.wave_full * pl.wave_ch + pl.wave_ch_last) * pl.k_blocks;
+    pl.grid = (int)grid;
+    return pl;
+  }
   // at least 4 k-blocks (64 KB of weights) per CTA, so tiny problems do not pay for 148 partial tiles
   if (grid > (total + 3) / 4) grid = (total + 3) / 4;
   if (grid < 1) grid = 1;
@@ -943,6 +1036,11 @@ int launch(const LinearArgs& a, const Plan& pl, void* work, const void* lora_A, 
   p.k_blocks = pl.k_blocks;
   p.row_tiles = pl.row_tiles;
   p.n_tiles = pl.row_tiles * pl.tok_tiles;
+  p.tok_tiles = pl.tok_tiles;
+  p.wave_gt = pl.wave_gt;
+  p.wave_full = pl.wave_full;
+  p.wave_ch = pl.wave_ch;
+  p.wave_ch_last = pl.wave_ch_last;
   p.per_cta = pl.per_cta;
   // output through TMA when the tensor satisfies its alignment rules (16-byte base and row pitch)
   CUtensorMap my = mx;
@@ -1051,8 +1149,9 @@ int launch_pack_weight(const void* W, int out, int in, void* Wp, cudaStream_t st
 }
 
 bool linear_tc_can_fuse_shrink(const LinearArgs& a) {
-  // the shrink runs inside the projection kernel only where the expand runs on the tensor cores
-  if (a.u == nullptr) return false;
+  // the shrink runs inside the projection kernel only where the expand runs on the tensor cores, at decode
+  // sizes (stream-K ranges: every CTA of the grid has work and takes part in the publish)
+  if (a.u == nullptr || a.T > 128) return false;
   for (int m = 1; m < a.n_mod; ++m)
     if (a.mod_off[m] % BM != 0) return false;
   return a.r_max == 16 || a.r_max == 32 || a.r_max == 64 || a.r_max == 128;

@@ -520,3 +520,30 @@ def test_prefill_shrink_on_tensor_cores(ops, cuda, T, K, r, n_mod, mixing):
         if 0 <= s < n_ad:
             want[t] = A[s].float() @ x[t].float()
     torch.testing.assert_close(u.cpu(), want, atol=2e-3, rtol=1e-4)
+
+
+@pytest.mark.parametrize("T,K,N,lora", [(2048, 256, 12288, False), (2000, 320, 12288, True), (5000, 128, 6144, True)])
+def test_prefill_size_projection_in_waves(ops, cuda, T, K, N, lora):
+    """Enough tiles that the projection kernel deals whole tiles in L2-friendly waves instead of stream-K ranges
+    (ragged last token tile, narrower last token-tile group), with the LoRA expand and the grouped-GEMM shrink."""
+    g = torch.Generator().manual_seed(T)
+    x = torch.randn(T, K, generator=g).bfloat16().to(cuda)
+    W = (torch.randn(N, K, generator=g) * 0.05).bfloat16().to(cuda)
+    want = x.float() @ W.float().t()
+    st = slots = None
+    if lora:
+        n_ad, r, third = 6, 16, N // 3
+        A = (torch.randn(n_ad, 3 * r, K, generator=g) * 0.05).bfloat16().to(cuda)
+        B = (torch.randn(n_ad, N, r, generator=g) * 0.05).bfloat16().to(cuda)
+        slots = (torch.arange(T) // 300 % (n_ad + 1) - 1).int().to(cuda)  # runs of 300 rows, some without adapter
+        st = ops.LoraStack(A, B, _i32([r] * n_ad, cuda), torch.full((n_ad,), 2.0, device=cuda), r, 3,
+                           (0, third, 2 * third, N)).pack_b()
+        for s in range(n_ad):
+            rows = (slots == s).nonzero().flatten()
+            for m in range(3):
+                u = x[rows].float() @ A[s, m * r:(m + 1) * r].float().t()
+                want[rows, m * third:(m + 1) * third] += 2.0 * (u @ B[s, m * third:(m + 1) * third].float().t())
+    y = ops.linear(x, ops.PackedWeight(W), st, slots)
+    torch.cuda.synchronize()
+    assert int(ops.workspace(4, cuda, "linear")[:4].view(torch.int32)) == 0, "a bounded wait expired"
+    torch.testing.assert_close(y.float(), want, atol=ATOL, rtol=RTOL)
