@@ -148,7 +148,7 @@ extern "C" int mlora_lora_shrink(const void* d_x, int64_t ldx, const void* d_A_a
     return launch_lora_shrink_tc(d_x, ldx, d_A_all, d_slots, n_adapters, T, in, r_tot, d_u, (cudaStream_t)stream);
   MLORA_REQUIRE(T <= 65535, "lora_shrink: T=%d exceeds 65535 rows per call", T);
   dim3 grid((r_tot + 7) / 8, T);
-  launch_pdl(lora_shrink_kernel, grid, 256, 0, (cudaStream_t)stream, (const bf16*)d_x, ldx, (const bf16*)d_A_all, d_ranks,
+  launch_pdl_if(pdl_enabled_shrink(), lora_shrink_kernel, grid, 256, 0, (cudaStream_t)stream, (const bf16*)d_x, ldx, (const bf16*)d_A_all, d_ranks,
              d_slots, n_adapters, in, r_max, r_tot, d_u);
   count_launch();
   MLORA_CHECK_LAUNCH("lora_shrink_kernel");

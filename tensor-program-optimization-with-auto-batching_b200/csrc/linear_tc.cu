@@ -207,18 +207,21 @@ __device__ __forceinline__ int wave_tile(const TcParams& p, int lt) {
   const int j = q / p.row_tiles;
   return (group * p.wave_gt + j) * p.row_tiles + (q - j * p.row_tiles);
 }
+template <bool WAVE>
 __device__ __forceinline__ Range cta_range(const TcParams& p, int cta) {
-  if (p.wave_gt > 0) return Range{0, (p.wave_full * p.wave_ch + p.wave_ch_last) * p.k_blocks};
+  if (WAVE && p.wave_gt > 0) return Range{0, (p.wave_full * p.wave_ch + p.wave_ch_last) * p.k_blocks};
   const long long total = (long long)p.n_tiles * p.k_blocks;
   long long a = (long long)cta * p.per_cta, b = a + p.per_cta;
   if (a > total) a = total;
   if (b > total) b = total;
   return Range{(int)a, (int)b};
 }
-// Next piece of work of this CTA; tile < 0: none left.
+// Next piece of work of this CTA; tile < 0: none left.  WAVE = false compiles the whole-tile walk out (the
+// decode-size instantiations are sensitive to code size).
+template <bool WAVE>
 __device__ __forceinline__ Segment next_segment(const TcParams& p, int& it, int it1) {
   Segment s;
-  if (p.wave_gt > 0) {
+  if (WAVE && p.wave_gt > 0) {
     s.tile = -1;
     s.kb0 = 0;
     s.kb1 = p.k_blocks;
@@ -272,7 +275,8 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
   __shared__ int s_nseg0;  // distinct adapters of the CTA's first token tile (listed before the roles start)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const Range rg = cta_range(p, blockIdx.x);
+  constexpr bool WAVE = BN >= 128;  // prefill-size token tiles only
+  const Range rg = cta_range<WAVE>(p, blockIdx.x);
   if (rg.it0 >= rg.it1) return;  // whole CTA idle (uniform)
   const LinearArgs& a = p.a;
   const int r_tot = a.r_max * a.n_mod;
@@ -309,7 +313,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
   // kernels before it have completed.
   pdl_launch_dependents();
   int first_it = rg.it0;
-  const int first_tile = next_segment(p, first_it, rg.it1).tile;
+  const int first_tile = next_segment<WAVE>(p, first_it, rg.it1).tile;
   const int tok_tile0 = (first_tile < 0 ? 0 : first_tile) / p.row_tiles;
   const bool stage_u2 = p.lora_mode == 2 && (size_t)BN * r_tot * sizeof(float) <= (size_t)kStageUMax;
   if (warp != 0) pdl_wait();
@@ -432,8 +436,8 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
     bool got_preload = false;
     bool ok = true;
     while (it < rg.it1 && ok) {
-      const Segment sg = next_segment(p, it, rg.it1);
-      if (sg.tile < 0) break;
+      const Segment sg = next_segment<WAVE>(p, it, rg.it1);
+      if (WAVE && sg.tile < 0) break;
       const int row_tile = sg.tile % p.row_tiles, tok_tile = sg.tile / p.row_tiles;
       if (lane == 0) {
         int nn = n;
@@ -506,8 +510,8 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
     bool got_preload = false;
     bool ok = true;
     while (it < rg.it1 && ok) {
-      const Segment sg = next_segment(p, it, rg.it1);
-      if (sg.tile < 0) break;
+      const Segment sg = next_segment<WAVE>(p, it, rg.it1);
+      if (WAVE && sg.tile < 0) break;
       const int row_tile = sg.tile % p.row_tiles, tok_tile = sg.tile / p.row_tiles;
       if (lane == 0) {
         int nn = n;
@@ -568,38 +572,57 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
           for (int i = lane; i < n_vec; i += 32) reinterpret_cast<uint4*>(s_cache)[i] = make_uint4(0u, 0u, 0u, 0u);
           __syncwarp();
           const int per_row = chunks * p.n_sub;
-          // four items per lane and step, their shrink outputs requested before the first is used (the
-          // loads are L2 round trips when the outputs are not staged in shared memory)
-          for (int base = lane; base < BN * per_row; base += 32 * 4) {
-            float4 lo[4], hi[4];
-            int nr[4], off[4];
+          if constexpr (BN >= 128) {
+            // four items per lane and step, their shrink outputs requested before the first is used (the
+            // loads are L2 round trips when the outputs are not staged in shared memory)
+            for (int base = lane; base < BN * per_row; base += 32 * 4) {
+              float4 lo[4], hi[4];
+              int nr[4], off[4];
 #pragma unroll
-            for (int b = 0; b < 4; ++b) {
-              const int idx = base + b * 32;
-              nr[b] = -1;
-              if (idx < BN * per_row) {
-                const int nrow = idx / per_row, rem = idx - nrow * per_row;
-                const int sb = rem / chunks, c = rem - sb * chunks;
-                if (x_tok[nrow] >= 0) {
-                  nr[b] = nrow;
-                  off[b] = sb * 256 + c;
-                  const float* ur = (stage_u ? s_u + nrow * r_tot : a.u + (size_t)(t0 + nrow) * r_tot) + u_off +
-                                    sb * p.lora_sub + c * 8;
-                  lo[b] = *reinterpret_cast<const float4*>(ur);
-                  hi[b] = *reinterpret_cast<const float4*>(ur + 4);
+              for (int b = 0; b < 4; ++b) {
+                const int idx = base + b * 32;
+                nr[b] = -1;
+                if (idx < BN * per_row) {
+                  const int nrow = idx / per_row, rem = idx - nrow * per_row;
+                  const int sb = rem / chunks, c = rem - sb * chunks;
+                  if (x_tok[nrow] >= 0) {
+                    nr[b] = nrow;
+                    off[b] = sb * 256 + c;
+                    const float* ur = (stage_u ? s_u + nrow * r_tot : a.u + (size_t)(t0 + nrow) * r_tot) + u_off +
+                                      sb * p.lora_sub + c * 8;
+                    lo[b] = *reinterpret_cast<const float4*>(ur);
+                    hi[b] = *reinterpret_cast<const float4*>(ur + 4);
+                  }
                 }
               }
-            }
 #pragma unroll
-            for (int b = 0; b < 4; ++b) {
-              if (nr[b] < 0) continue;
-              const int nrow = nr[b], sb = off[b] >> 8, c = off[b] & 255;
+              for (int b = 0; b < 4; ++b) {
+                if (nr[b] < 0) continue;
+                const int nrow = nr[b], sb = off[b] >> 8, c = off[b] & 255;
+                const int slot = x_tok[nrow];
+                int sgi = 0;
+                while (x_list[sgi] != slot) ++sgi;  // slot is in the list by construction
+                const float sc = x_scale[sgi];
+                const float f[8] = {lo[b].x * sc, lo[b].y * sc, lo[b].z * sc, lo[b].w * sc,
+                                    hi[b].x * sc, hi[b].y * sc, hi[b].z * sc, hi[b].w * sc};
+                const int sw = rb == 128 ? (nrow & 7) : rb == 64 ? ((nrow >> 1) & 3) : ((nrow >> 2) & 1);
+                *reinterpret_cast<uint4*>(s_cache + (sgi * p.n_sub + sb) * BN * rb + nrow * rb + ((c ^ sw) << 4)) = pack8(f);
+              }
+            }
+          } else {
+            for (int idx = lane; idx < BN * per_row; idx += 32) {
+              const int nrow = idx / per_row, rem = idx - nrow * per_row;
+              const int sb = rem / chunks, c = rem - sb * chunks;
               const int slot = x_tok[nrow];
+              if (slot < 0) continue;
               int sgi = 0;
               while (x_list[sgi] != slot) ++sgi;  // slot is in the list by construction
               const float sc = x_scale[sgi];
-              const float f[8] = {lo[b].x * sc, lo[b].y * sc, lo[b].z * sc, lo[b].w * sc,
-                                  hi[b].x * sc, hi[b].y * sc, hi[b].z * sc, hi[b].w * sc};
+              const float* ur = (stage_u ? s_u + nrow * r_tot : a.u + (size_t)(t0 + nrow) * r_tot) + u_off +
+                                sb * p.lora_sub + c * 8;
+              float f[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) f[e] = ur[e] * sc;
               const int sw = rb == 128 ? (nrow & 7) : rb == 64 ? ((nrow >> 1) & 3) : ((nrow >> 2) & 1);
               *reinterpret_cast<uint4*>(s_cache + (sgi * p.n_sub + sb) * BN * rb + nrow * rb + ((c ^ sw) << 4)) = pack8(f);
             }
@@ -658,8 +681,8 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
     bool got_preload = false;
     bool ok = true;
     while (it < rg.it1 && ok) {
-      const Segment sg = next_segment(p, it, rg.it1);
-      if (sg.tile < 0) break;
+      const Segment sg = next_segment<WAVE>(p, it, rg.it1);
+      if (WAVE && sg.tile < 0) break;
       const int row_tile = sg.tile % p.row_tiles, tok_tile = sg.tile / p.row_tiles;
       const int buf = j & 1;
       const uint32_t d_tmem = tmem_base + buf * BN;
@@ -771,8 +794,8 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
     int it = rg.it0, j = 0;
 
     while (it < rg.it1) {
-      const Segment sg = next_segment(p, it, rg.it1);
-      if (sg.tile < 0) break;
+      const Segment sg = next_segment<WAVE>(p, it, rg.it1);
+      if (WAVE && sg.tile < 0) break;
       const int row_tile = sg.tile % p.row_tiles, tok_tile = sg.tile / p.row_tiles;
       const int row = row_tile * BM + etid;
       const int t0 = tok_tile * BN;

@@ -29,12 +29,13 @@ static int pdl_mode() {
   static const int mode = [] {
     const char* e = getenv("MLORA_PDL");
     if (!e) return 2;
-    return strcmp(e, "0") == 0 ? 0 : strcmp(e, "1") == 0 ? 1 : 2;
+    return strcmp(e, "0") == 0 ? 0 : strcmp(e, "1") == 0 ? 1 : strcmp(e, "3") == 0 ? 3 : 2;
   }();
   return mode;
 }
 bool pdl_enabled() { return pdl_mode() == 1; }
 bool pdl_enabled_gemm() { return pdl_mode() >= 1; }
+bool pdl_enabled_shrink() { return pdl_mode() == 1 || pdl_mode() == 3; }  // "3": projection and LoRA shrink
 
 void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
 
