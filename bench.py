@@ -365,11 +365,11 @@ def kernel_rooflines(eng, pm, kv, B, slots, ops, torch, ctx, n_uniq, peak, reps=
                 st = lw.lora.get(key)
                 if st is not None:
                     ops.linear(src, W, st, sl, u=u_for(st), flags=fl, out=dst)
-                else:
-                    ops.linear(src, W, flags=fl, out=dst)
+                else:  # as the engine issues it: same kernel variant as the LoRA projections around it
+                    ops.linear(src, W, flags=fl | ops.SHARE_LORA_KERNEL, out=dst)
                 n += 1
                 total += lin_bytes(W, st, silu=bool(fl & ops.SILU_MUL))
-        ops.linear(x, pm.lm_head, flags=ops.OUT_F32, out=eng.logits[:T])
+        ops.linear(x, pm.lm_head, flags=ops.OUT_F32 | ops.SHARE_LORA_KERNEL, out=eng.logits[:T])
         return n + 1, total + lin_bytes(pm.lm_head, None, out_f32=True)
 
     def attentions():
@@ -411,8 +411,8 @@ def kernel_rooflines(eng, pm, kv, B, slots, ops, torch, ctx, n_uniq, peak, reps=
 
 def run_operator_case(ops, synth, dev, torch):
     """The operator micro-benchmark: y = x W^T + 2 (x A[id]) B[id], W [4096,4096], 16 rank-16 adapters,
-    T in {1, 8, 32, 128} (shapes of tvm/lora_only/single_rank.py).  CUDA-event time of the one-launch
-    shrink + projection + expand (and of the two-launch form) in a graph over 20 weight copies (671 MB, beyond L2); one JSON line."""
+    T in {1, 8, 32, 128} (shapes of tvm/lora_only/single_rank.py).  CUDA-event time of the shrink +
+    projection pair (one mlora_lora_linear call) in a graph over 20 weight copies (671 MB, beyond L2); one JSON line."""
     peak, src = measured_peak()
     rows = []
     for T in (1, 8, 32, 128):
@@ -424,13 +424,11 @@ def run_operator_case(ops, synth, dev, torch):
         out = torch.empty(T, 4096, dtype=torch.bfloat16, device=dev)
         res = {}
         u = torch.empty(T, RANK, dtype=torch.float32, device=dev)
-        for name in ("lora", "lora_two_launches", "base"):
+        for name in ("lora", "base"):
             def body():
                 for W in Ws:
-                    if name == "lora":  # one launch: shrink, projection and expand
+                    if name == "lora":  # mlora_lora_linear: shrink kernel, then projection with the expand fused in
                         ops.linear(c["x"], W, st, slots, u=u, out=out, fuse_shrink=True)
-                    elif name == "lora_two_launches":  # shrink kernel, then projection with fused expand
-                        ops.linear(c["x"], W, st, slots, out=out)
                     else:
                         ops.linear(c["x"], W, out=out)
             body()
@@ -450,8 +448,7 @@ def run_operator_case(ops, synth, dev, torch):
             res[name] = 1e3 * e0.elapsed_time(e1) / (5 * len(Ws))
         n_uniq = len(set(slots.tolist()))
         by = 2 * 4096 * 4096 + n_uniq * 2 * RANK * (4096 + 4096) + 2 * T * 4096 * 2 + 4 * T
-        rows.append({"T": T, "us_with_lora": res["lora"], "us_with_lora_two_launches": res["lora_two_launches"],
-                     "us_base_only": res["base"],
+        rows.append({"T": T, "us_with_lora": res["lora"], "us_base_only": res["base"],
                      "lora_overhead_frac": res["lora"] / res["base"] - 1.0, "algorithmic_bytes": by,
                      "achieved_gbs": by / (res["lora"] * 1e3), "frac_of_peak": by / (res["lora"] * 1e3) / peak})
     print(json.dumps({"kernel_case": "operator", "peak_gbs": peak, "peak_source": src, "rows": rows}))

@@ -34,6 +34,10 @@ extern "C" {
 #define MLORA_FORCE_SIMT 4  /* use the CUDA-core warp-per-row kernel whatever the shape */
 #define MLORA_W_PACKED 8    /* d_W is the tiled layout written by mlora_pack_weight */
 #define MLORA_B_PACKED 16   /* d_B_all is the tiled layout written by mlora_pack_lora_b */
+#define MLORA_SHARE_LORA_KERNEL 32 /* hint for a call WITHOUT LoRA operands that sits between calls with them
+                               (gate/up/down when only q/k/v/o carry adapters): run the kernel variant the LoRA
+                               calls use, so one code footprint stays hot in the instruction caches for the whole
+                               step; results are identical either way */
 
 int mlora_version(void);
 const char* mlora_last_error(void);
@@ -131,13 +135,11 @@ int mlora_linear(const void* d_x, int64_t ldx, const void* d_W, void* d_y, int64
                  int32_t flags, void* d_work, size_t work_bytes, void* stream);
 /* mlora_lora_shrink + mlora_linear as ONE call, i.e. the whole of
  * base_layer(x) + bmm(bmm(x, A), B*scaling) (huggingface/custom_peft/lora_gatherbmm_linear_layer.py:15-20).
- * d_A_all as for mlora_lora_shrink (rows beyond an adapter's rank zero); d_u [T, n_mod*r_max] float32 is
- * scratch the call writes before it reads it.  Where the tensor-core kernel takes the call and its LoRA
- * expand runs on the tensor cores (rank pitch 16/32/64/128, module boundaries multiples of 128), this is
- * one launch: the otherwise idle output warps of every CTA compute a slice of u while the weight
- * stream starts, and a bounded grid-wide counter in d_work publishes it (status bit 8 = that wait gave
- * up).  Everywhere else it is the two launches.  d_work as for mlora_linear, and the same buffer must
- * not be used by two calls that may run concurrently. */
+ * d_A_all as for mlora_lora_shrink; d_u [T, n_mod*r_max] float32 is scratch the call writes before it
+ * reads it.  It issues the shrink kernel and the projection kernel back to back on `stream` (a single
+ * kernel that computed the shrink in the projection's idle output warps and published it with a
+ * grid-wide counter was measured slower than this pair under programmatic dependent launch, and is
+ * not kept). */
 int mlora_lora_linear(const void* d_x, int64_t ldx, const void* d_W, void* d_y, int64_t ldy, int32_t T,
                       int32_t in, int32_t out, const void* d_A_all, float* d_u, const void* d_B_all,
                       const int32_t* d_ranks, const float* d_scales, const int32_t* d_slots,

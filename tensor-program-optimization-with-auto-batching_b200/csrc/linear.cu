@@ -7,8 +7,7 @@ extern "C" size_t mlora_linear_workspace(int32_t T, int32_t in, int32_t out) {
   return linear_tc_workspace(T, in, out);
 }
 
-// d_A_all != NULL: the shrink is part of this call (one launch when the tensor-core kernel can take it,
-// else the shrink kernel first).
+// d_A_all != NULL: the shrink is part of this call (its kernel is launched first).
 static int linear_impl(const void* d_x, int64_t ldx, const void* d_W, void* d_y, int64_t ldy, int32_t T, int32_t in,
                        int32_t out, const void* d_A_all, const float* d_u, const void* d_B_all,
                        const int32_t* d_ranks, const float* d_scales, const int32_t* d_slots, int32_t n_adapters,
@@ -68,8 +67,6 @@ static int linear_impl(const void* d_x, int64_t ldx, const void* d_W, void* d_y,
   cudaStream_t st = (cudaStream_t)stream;
   if (d_A_all) {
     MLORA_REQUIRE(d_u && aligned16(d_A_all) && aligned16(d_u), "lora_linear: A_all and u must be non-null and 16-byte aligned");
-    const bool tc = !(flags & MLORA_FORCE_SIMT) && d_work && linear_tc_supported(a);
-    if (tc && linear_tc_can_fuse_shrink(a)) return launch_linear_tc(a, d_work, work_bytes, d_A_all, st);
     const int rc = mlora_lora_shrink(d_x, ldx, d_A_all, d_ranks, d_slots, n_adapters, T, in, r_max, n_mod,
                                      const_cast<float*>(d_u), stream);
     if (rc != MLORA_OK) return rc;
@@ -79,10 +76,10 @@ static int linear_impl(const void* d_x, int64_t ldx, const void* d_W, void* d_y,
   if (flags & (MLORA_W_PACKED | MLORA_B_PACKED)) {
     MLORA_REQUIRE(!(flags & MLORA_FORCE_SIMT) && d_work && linear_tc_supported(a),
                   "linear: a packed weight needs the tensor-core kernel (scratch buffer, 16-byte aligned operands)");
-    return launch_linear_tc(a, d_work, work_bytes, nullptr, st);
+    return launch_linear_tc(a, d_work, work_bytes, st);
   }
   if (!(flags & MLORA_FORCE_SIMT) && d_work && linear_tc_supported(a))
-    return launch_linear_tc(a, d_work, work_bytes, nullptr, st);
+    return launch_linear_tc(a, d_work, work_bytes, st);
   return launch_linear_simt(a, st);
 }
 

@@ -68,10 +68,7 @@ int launch_linear_simt(const LinearArgs& a, cudaStream_t st);
 // Tensor-core (tcgen05) weight-streaming kernel; returns MLORA_OK or an error.
 bool linear_tc_supported(const LinearArgs& a);
 size_t linear_tc_workspace(int T, int in, int out);
-// lora_A != nullptr: the kernel computes the shrink itself (u is then scratch it writes before use);
-// returns MLORA_OK or an error.
-int launch_linear_tc(const LinearArgs& a, void* work, size_t work_bytes, const void* lora_A, cudaStream_t st);
-bool linear_tc_can_fuse_shrink(const LinearArgs& a);
+int launch_linear_tc(const LinearArgs& a, void* work, size_t work_bytes, cudaStream_t st);
 // LoRA shrink as a segmented grouped GEMM on the tensor cores (prefill sizes).
 bool lora_shrink_tc_supported(const void* x, int64_t ldx, const void* A_all, const float* u, int T, int in, int r_tot);
 int launch_lora_shrink_tc(const void* x, int64_t ldx, const void* A_all, const int32_t* slots, int n_adapters, int T,

@@ -22,6 +22,8 @@
 // of the scratch buffer, stops issuing work, and leaves after freeing its TMEM.
 #include <stdlib.h>
 
+#include <atomic>
+
 #include "linear.cuh"
 #include "tc_ptx.cuh"
 
@@ -49,8 +51,6 @@ struct TcParams {
   int lora_sub;    // K elements of one LoRA stage (16, 32 or 64 = row bytes 32, 64, 128)
   int n_sub;       // LoRA stages per adapter segment (r_max / lora_sub)
   int prefetch;    // weight tiles requested into L2 ahead of the ring (0 = off)
-  int fused_shrink;  // 1: this launch also computes u = x . A[slot]^T (A_all below) before it is used
-  const bf16* A_all; // [N, r_tot, in]
   int tma_store;   // 1: output tiles leave through shared memory + one TMA store per 32-token chunk
   int32_t* status;  // scratch[0]
   int32_t* tickets; // [kMaxGrid], indexed by the first contributing CTA of a split tile
@@ -238,7 +238,12 @@ __device__ __forceinline__ Segment next_segment(const TcParams& p, int& it, int 
   return s;
 }
 
-template <int BN, bool SIMT_LORA>
+// LM: 0 = no LoRA code at all, 1 = expand on CUDA cores in the epilogue, 2 = expand as extra MMA stages when
+// p.lora_mode == 2 (this instantiation also serves base-only calls flagged MLORA_SHARE_LORA_KERNEL).  Separate
+// instantiations because the decode-size kernels are sensitive to code size: every launch starts with cold
+// instruction caches after 100+ MB of weights went through L2, so a step whose projections alternate between two
+// instantiations pays for two code footprints; one that uses a single instantiation throughout does not.
+template <int BN, int LM>
 __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                 const __grid_constant__ CUtensorMap map_x,
                                                                 const __grid_constant__ CUtensorMap map_b,
@@ -301,7 +306,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     if (!(a.flags & MLORA_W_PACKED)) tma_prefetch_desc(&map_w);
     tma_prefetch_desc(&map_x);
-    if (p.lora_mode == 2 && !(a.flags & MLORA_B_PACKED)) tma_prefetch_desc(&map_b);
+    if ((LM == 2 && p.lora_mode == 2) && !(a.flags & MLORA_B_PACKED)) tma_prefetch_desc(&map_b);
     if (p.tma_store) tma_prefetch_desc(&map_y);
   }
   if (warp == 1) tmem_alloc(tmem_slot, C::kTmemCols);
@@ -315,86 +320,9 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
   int first_it = rg.it0;
   const int first_tile = next_segment<WAVE>(p, first_it, rg.it1).tile;
   const int tok_tile0 = (first_tile < 0 ? 0 : first_tile) / p.row_tiles;
-  const bool stage_u2 = p.lora_mode == 2 && (size_t)BN * r_tot * sizeof(float) <= (size_t)kStageUMax;
+  const bool stage_u2 = (LM == 2 && p.lora_mode == 2) && (size_t)BN * r_tot * sizeof(float) <= (size_t)kStageUMax;
   if (warp != 0) pdl_wait();
-  if (p.fused_shrink && warp >= 2 && warp <= 5) {
-    // Fused LoRA shrink: u = x . A[slot]^T for ALL rows of the call is computed here, spread over the
-    // epilogue warps of every CTA (idle at start-up) while the weight producer already streams, then
-    // published through a grid-wide counter.  Work item = (row t, 4 adjacent rank rows); rank rows beyond
-    // an adapter's rank are zero in A_all, so they are simply computed.  All CTAs of this persistent
-    // grid are co-resident (grid <= SM count), and the wait below is bounded.
-    const int ew = (warp & 3), n_items = a.T * (r_tot / 4);
-    // CTAs that take part: those with work (the others returned above)
-    const int n_active = (int)min((long long)gridDim.x, ((long long)p.n_tiles * p.k_blocks + p.per_cta - 1) / p.per_cta);
-    int gen0 = 0;
-    if (warp == 4 && lane == 0) {  // epilogue thread 0: generation before anyone of this launch arrives
-      asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(gen0) : "l"(p.status + 2) : "memory");
-    }
-    for (int item = blockIdx.x * 4 + ew; item < n_items; item += n_active * 4) {
-      const int t = item / (r_tot / 4), j0 = (item - t * (r_tot / 4)) * 4;
-      const int slot = a.slots[t];
-      float acc[4] = {0.f, 0.f, 0.f, 0.f};
-      if (slot >= 0 && slot < a.n_adapters) {
-        const bf16* xr = a.x + (size_t)t * a.ldx;
-        const bf16* ar = p.A_all + ((size_t)slot * r_tot + j0) * a.in;
-        for (int k0 = lane * 8; k0 < a.in; k0 += 256 * 4) {
-          uint4 xv[4], av[4][4];
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            const int k = k0 + c * 256;
-            if (k < a.in) {
-              xv[c] = ld_cached(xr + k);
-#pragma unroll
-              for (int r = 0; r < 4; ++r) av[r][c] = ld_cached(ar + (size_t)r * a.in + k);
-            }
-          }
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            if (k0 + c * 256 < a.in) {
-              float xf[8];
-              unpack8(xv[c], xf);
-#pragma unroll
-              for (int r = 0; r < 4; ++r) {
-                float af[8];
-                unpack8(av[r][c], af);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) acc[r] = fmaf(af[e], xf[e], acc[r]);
-              }
-            }
-          }
-        }
-#pragma unroll
-        for (int r = 0; r < 4; ++r) acc[r] = warp_sum(acc[r]);
-      }
-      if (lane == 0)
-        *reinterpret_cast<float4*>(const_cast<float*>(a.u) + (size_t)t * r_tot + j0) =
-            make_float4(acc[0], acc[1], acc[2], acc[3]);
-    }
-    __threadfence();
-    epi_bar_sync();
-    if (warp == 4 && lane == 0) {
-      const int ticket = atomicAdd(p.status + 1, 1);
-      if (ticket == n_active - 1) {
-        p.status[1] = 0;  // ready for the next launch
-        __threadfence();
-        atomicAdd(p.status + 2, 1);
-      } else {
-        bool got = false;
-        for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
-          int gen;
-          asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(gen) : "l"(p.status + 2) : "memory");
-          if (gen != gen0) {
-            got = true;
-            break;
-          }
-          __nanosleep(100);
-        }
-        if (!got) atomicOr(p.status, 256);
-      }
-    }
-    epi_bar_sync();
-  }
-  if (p.lora_mode == 2 && warp >= 2 && warp <= 5) {
+  if ((LM == 2 && p.lora_mode == 2) && warp >= 2 && warp <= 5) {
     // The per-token LoRA operands of the CTA's first token tile (decode: the only one) are fetched now,
     // by the epilogue warps, which are idle at start-up, so that no pipeline role stops mid-stream for a
     // global load.  The roles pick the result up through `preload_bar` when they first need it.
@@ -416,7 +344,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
       for (int base = (warp - 3) * 32 + lane; base < n_vec; base += 96 * 8) {
 #pragma unroll
         for (int c = 0; c < 8; ++c)
-          if (base + c * 96 < n_vec) tmp[c] = __ldcg(src + base + c * 96);  // L2: may have been written by this launch
+          if (base + c * 96 < n_vec) tmp[c] = __ldg(src + base + c * 96);
 #pragma unroll
         for (int c = 0; c < 8; ++c)
           if (base + c * 96 < n_vec) reinterpret_cast<float4*>(s_u)[base + c * 96] = tmp[c];
@@ -459,7 +387,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
       }
       n += sg.kb1 - sg.kb0;
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      if (ok && p.lora_mode == 2 && sg.kb1 == p.k_blocks) {
+      if (ok && (LM == 2 && p.lora_mode == 2) && sg.kb1 == p.k_blocks) {
         if (!got_preload) {  // operands of the first token tile, staged by the epilogue warps at start-up
           mbar_wait(preload_bar, 0, &s_abort);
           n_seg = s_nseg0;
@@ -529,7 +457,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
       }
       n += sg.kb1 - sg.kb0;
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      if (ok && p.lora_mode == 2 && sg.kb1 == p.k_blocks) {
+      if (ok && (LM == 2 && p.lora_mode == 2) && sg.kb1 == p.k_blocks) {
         if (!got_preload) {  // operands of the first token tile, staged by the epilogue warps at start-up
           mbar_wait(preload_bar, 0, &s_abort);
           n_seg = s_nseg0;
@@ -688,7 +616,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
       const uint32_t d_tmem = tmem_base + buf * BN;
       int n_l = 0, group = 1;
       bool cached = false, new_build = false;
-      if (p.lora_mode == 2 && sg.kb1 == p.k_blocks) {
+      if ((LM == 2 && p.lora_mode == 2) && sg.kb1 == p.k_blocks) {
         if (!got_preload) {  // operands of the first token tile, staged by the epilogue warps at start-up
           mbar_wait(preload_bar, 0, &s_abort);
           n_seg = s_nseg0;
@@ -788,7 +716,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
     const int etid = q * 32 + lane;           // 0..127 = row inside the tile
     const bool silu = (a.flags & MLORA_SILU_MUL) != 0;
     const bool out_f32 = (a.flags & MLORA_OUT_F32) != 0;
-    constexpr bool simt_lora = SIMT_LORA;
+    constexpr bool simt_lora = LM == 1;
     const bool stage_u = simt_lora && (size_t)BN * r_tot * sizeof(float) <= (size_t)kStageUMax;
     int staged_tok_tile = -1;
     int it = rg.it0, j = 0;
@@ -816,7 +744,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
 
       // Adds the CUDA-core LoRA expand if any, applies SiLU*up, stores.  v[i] = (token t0+c0+i, row).
       auto finish = [&](float (&v)[32], int c0) {
-        if (SIMT_LORA) simt_lora_expand<BN>(a, v, c0, t0, row, r_tot, stage_u, s_slots, s_u);
+        if (LM == 1) simt_lora_expand<BN>(a, v, c0, t0, row, r_tot, stage_u, s_slots, s_u);
         if (p.tma_store) {
           // registers -> shared memory [tokens][outputs of the tile] -> one TMA store (which also clips
           // tokens >= T and outputs >= out); far fewer instructions than 32 strided stores per thread
@@ -1017,7 +945,7 @@ Plan make_plan(int T, int in, int out) {
 }
 
 template <int BN>
-int launch(const LinearArgs& a, const Plan& pl, void* work, const void* lora_A, cudaStream_t st) {
+int launch(const LinearArgs& a, const Plan& pl, void* work, cudaStream_t st) {
   using C = Cfg<BN>;
   CUtensorMap mw, mx;
   int rc = make_map(&mx, a.x, a.T, a.in, a.ldx, BN);
@@ -1055,7 +983,6 @@ int launch(const LinearArgs& a, const Plan& pl, void* work, const void* lora_A, 
       p.lora_mode = 1;
     }
   }
-  if (lora_A != nullptr && p.lora_mode != 2) return fail(MLORA_EINVAL, "linear: this shape cannot take the shrink in-kernel");
   p.k_blocks = pl.k_blocks;
   p.row_tiles = pl.row_tiles;
   p.n_tiles = pl.row_tiles * pl.tok_tiles;
@@ -1076,26 +1003,29 @@ int launch(const LinearArgs& a, const Plan& pl, void* work, const void* lora_A, 
       if (rc) return rc;
     }
   }
-  p.fused_shrink = (lora_A != nullptr && p.lora_mode == 2) ? 1 : 0;
-  p.A_all = (const bf16*)lora_A;
   p.prefetch = 0;  // measured: an L2 prefetch stream ahead of the ring slows the kernel down on B200
   p.status = (int32_t*)work;
   p.tickets = (int32_t*)((uint8_t*)work + kHeaderBytes);
   p.partials = (float*)((uint8_t*)work + kHeaderBytes + kMaxGrid * 4);
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(linear_tc_kernel<BN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         C::kSmemBytes);
+  // the shared-memory opt-in is a per-device attribute of each instantiation
+  static std::atomic<unsigned long long> attr_done{0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!((attr_done.load(std::memory_order_acquire) >> (dev & 63)) & 1ull)) {
+    cudaError_t e = cudaFuncSetAttribute(linear_tc_kernel<BN, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
     if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(linear_tc_kernel<BN, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               C::kSmemBytes);
+      e = cudaFuncSetAttribute(linear_tc_kernel<BN, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(linear_tc_kernel<BN, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
     if (e != cudaSuccess) return fail(MLORA_ECUDA, "linear: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    attr_set = true;
+    attr_done.fetch_or(1ull << (dev & 63), std::memory_order_release);
   }
   if (p.lora_mode == 1)
-    launch_pdl_if(pdl_enabled_gemm(), linear_tc_kernel<BN, true>, pl.grid, kThreads, C::kSmemBytes, st, mw, mx, mb, my, p);
+    launch_pdl_if(pdl_enabled_gemm(), linear_tc_kernel<BN, 1>, pl.grid, kThreads, C::kSmemBytes, st, mw, mx, mb, my, p);
+  else if (p.lora_mode == 2 || (a.flags & MLORA_SHARE_LORA_KERNEL))
+    launch_pdl_if(pdl_enabled_gemm(), linear_tc_kernel<BN, 2>, pl.grid, kThreads, C::kSmemBytes, st, mw, mx, mb, my, p);
   else
-    launch_pdl_if(pdl_enabled_gemm(), linear_tc_kernel<BN, false>, pl.grid, kThreads, C::kSmemBytes, st, mw, mx, mb, my, p);
+    launch_pdl_if(pdl_enabled_gemm(), linear_tc_kernel<BN, 0>, pl.grid, kThreads, C::kSmemBytes, st, mw, mx, mb, my, p);
   count_launch();
   MLORA_CHECK_LAUNCH("linear_tc_kernel");
   return MLORA_OK;
@@ -1171,15 +1101,6 @@ int launch_pack_weight(const void* W, int out, int in, void* Wp, cudaStream_t st
   return MLORA_OK;
 }
 
-bool linear_tc_can_fuse_shrink(const LinearArgs& a) {
-  // the shrink runs inside the projection kernel only where the expand runs on the tensor cores, at decode
-  // sizes (stream-K ranges: every CTA of the grid has work and takes part in the publish)
-  if (a.u == nullptr || a.T > 128) return false;
-  for (int m = 1; m < a.n_mod; ++m)
-    if (a.mod_off[m] % BM != 0) return false;
-  return a.r_max == 16 || a.r_max == 32 || a.r_max == 64 || a.r_max == 128;
-}
-
 bool linear_tc_supported(const LinearArgs& a) {
   // TMA needs 16-byte aligned bases and row pitches; everything else (ragged K, out, T) is handled by
   // zero-filled out-of-bounds boxes and masked stores.
@@ -1194,15 +1115,15 @@ size_t linear_tc_workspace(int T, int in, int out) {
   return kHeaderBytes + kMaxGrid * 4 + (size_t)kMaxGrid * 2 * bn * BM * sizeof(float);
 }
 
-int launch_linear_tc(const LinearArgs& a, void* work, size_t work_bytes, const void* lora_A, cudaStream_t st) {
+int launch_linear_tc(const LinearArgs& a, void* work, size_t work_bytes, cudaStream_t st) {
   const size_t need = linear_tc_workspace(a.T, a.in, a.out);
   if (work_bytes < need) return fail(MLORA_ESIZE, "linear: workspace of %zu bytes needed, %zu given", need, work_bytes);
   Plan pl = make_plan(a.T, a.in, a.out);
   switch (pl.bn) {
-    case 16: return launch<16>(a, pl, work, lora_A, st);
-    case 32: return launch<32>(a, pl, work, lora_A, st);
-    case 64: return launch<64>(a, pl, work, lora_A, st);
-    default: return launch<128>(a, pl, work, lora_A, st);
+    case 16: return launch<16>(a, pl, work, st);
+    case 32: return launch<32>(a, pl, work, st);
+    case 64: return launch<64>(a, pl, work, st);
+    default: return launch<128>(a, pl, work, st);
   }
 }
 

@@ -15,6 +15,8 @@
 // its copies in flight have landed and its TMEM is freed.
 #include <stdlib.h>
 
+#include <atomic>
+
 #include "linear.cuh"
 #include "tc_ptx.cuh"
 
@@ -250,11 +252,13 @@ int launch_lora_shrink_tc(const void* x, int64_t ldx, const void* A_all, const i
   rc = make_map(&ma, A_all, (long long)n_adapters * r_tot, in, in, p.n_pad);
   if (rc) return rc;
   const size_t smem = (size_t)p.stages * p.stage_bytes + 1024;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static std::atomic<unsigned long long> attr_done{0};  // per-device attribute
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!((attr_done.load(std::memory_order_acquire) >> (dev & 63)) & 1ull)) {
     cudaError_t e = cudaFuncSetAttribute(lora_shrink_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
     if (e != cudaSuccess) return fail(MLORA_ECUDA, "lora_shrink: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    attr_set = true;
+    attr_done.fetch_or(1ull << (dev & 63), std::memory_order_release);
   }
   launch_pdl_if(pdl_enabled(), lora_shrink_tc_kernel, dim3((T + kTok - 1) / kTok), dim3(kShrinkThreads), smem, st, mx, ma, p);
   count_launch();

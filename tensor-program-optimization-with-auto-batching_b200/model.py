@@ -28,7 +28,7 @@ import torch
 
 from . import ops
 from .kv_cache import PagedKVCache
-from .ops import LoraStack, OUT_F32, SILU_MUL
+from .ops import LoraStack, OUT_F32, SHARE_LORA_KERNEL, SILU_MUL
 
 ATTN_PROJ = ("q_proj", "k_proj", "v_proj", "o_proj")
 MLP_PROJ = ("gate_proj", "up_proj", "down_proj")
@@ -233,10 +233,6 @@ class Engine:
         ops.workspace(need, dev, "linear")
         ops.workspace(lib.mlora_paged_attention_workspace(T, m.Hq, m.D, 16), dev, "attn")
         self._graphs = {}
-        # MLORA_FUSED_SHRINK=1: shrink inside the projection kernel (one launch per projection).  Off by default:
-        # measured on the 7B decode step the two-launch form is faster (the shrink kernel overlaps the
-        # projection's start-up under programmatic dependent launch; in-kernel it delays the first LoRA stages).
-        self.fuse_shrink = os.environ.get("MLORA_FUSED_SHRINK", "0") == "1"
 
     # ------------------------------------------------------------------------------------------
     def _proj(self, x, W, stack, slots, out, flags=0):
@@ -244,11 +240,10 @@ class Engine:
         if stack is not None and slots is not None:
             r_tot = stack.r_max * stack.n_mod
             u = self.u.view(-1)[: T * r_tot].view(T, r_tot)
-            if self.fuse_shrink:
-                return ops.linear(x, W, stack, slots, u=u, flags=flags, out=out, fuse_shrink=True)
             ops.lora_shrink(x, stack, slots, out=u)
             return ops.linear(x, W, stack, slots, u=u, flags=flags, out=out)
-        return ops.linear(x, W, flags=flags, out=out)
+        # a projection without adapters inside a pass that has some: same kernel variant as its neighbours
+        return ops.linear(x, W, flags=flags | (SHARE_LORA_KERNEL if slots is not None else 0), out=out)
 
     def forward(self, T: int, fused_append: bool, use_lora: bool = True, lm_rows=None, n_lm=None, hidden=None):
         """One pass over the T rows staged in self.tokens / self.slots / self.row_slot /
@@ -287,7 +282,7 @@ class Engine:
             xl = ops.embed(lm_rows[:n_lm], xn, out_bf16=self.xn_last[:n_lm])  # row gather
         else:
             n_lm, xl = T, xn
-        ops.linear(xl, m.lm_head, flags=OUT_F32, out=self.logits[:n_lm])
+        ops.linear(xl, m.lm_head, flags=OUT_F32 | (SHARE_LORA_KERNEL if slots is not None else 0), out=self.logits[:n_lm])
         ops.argmax(self.logits[:n_lm], out=self.next_tok[:n_lm])
         if m.tp_size > 1:
             # vocabulary-parallel greedy token: every rank offers (its best logit, its global index); the

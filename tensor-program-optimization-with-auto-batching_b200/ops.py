@@ -13,7 +13,7 @@ import torch
 from . import _lib
 from ._lib import check
 
-OUT_F32, SILU_MUL, FORCE_SIMT, W_PACKED, B_PACKED = 1, 2, 4, 8, 16
+OUT_F32, SILU_MUL, FORCE_SIMT, W_PACKED, B_PACKED, SHARE_LORA_KERNEL = 1, 2, 4, 8, 16, 32
 
 
 def _ptr(t):
@@ -149,7 +149,7 @@ def linear(x, W, stack: LoraStack = None, slots=None, u=None, flags: int = 0, ou
            fuse_shrink=False):
     """y = x W^T (+ LoRA expand of ``u``) ; see ``mlora_linear`` in include/mlora.h.
     ``W`` is a bf16 [out,in] tensor or a :class:`PackedWeight`.  ``fuse_shrink``: ``u`` is scratch and
-    the shrink is part of the call (``mlora_lora_linear``: one launch where the kernel can take it)."""
+    the shrink is part of the call (``mlora_lora_linear``)."""
     _need_cuda(x, W)
     if x.dtype != torch.bfloat16 or W.dtype != torch.bfloat16:
         raise ValueError("mlora.linear needs bf16 x and W")

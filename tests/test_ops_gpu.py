@@ -435,10 +435,9 @@ def test_packed_lora_stack_equals_row_major(ops, cuda, T, r):
 
 @pytest.mark.parametrize("T,r,K,N", [(1, 16, 4096, 3072), (32, 16, 4096, 1536), (9, 32, 1024, 384), (70, 64, 688, 384),
                                      (200, 16, 512, 3072)])
-def test_shrink_inside_the_projection_kernel(ops, cuda, T, r, K, N):
-    """mlora_lora_linear (shrink computed by the projection kernel's own warps, published grid-wide) against
-    the two-launch form: the shrink sums in a different order, so equal within bf16 rounding; repeated calls on one
-    scratch buffer (the arrival counter resets itself) and no expired wait."""
+def test_lora_linear_one_call(ops, cuda, T, r, K, N):
+    """mlora_lora_linear (shrink + projection in one C call, u as caller scratch) against the two calls;
+    repeated calls on one scratch buffer and no expired wait."""
     g = torch.Generator().manual_seed(T * 7 + r)
     n_ad, third = 5, N // 3
     offs = (0, third, 2 * third, N)
@@ -466,7 +465,7 @@ def test_shrink_inside_the_projection_kernel(ops, cuda, T, r, K, N):
         torch.testing.assert_close(got.float(), want.float(), atol=ATOL, rtol=RTOL)
 
 
-def test_shrink_inside_the_projection_kernel_gate_up(ops, cuda):
+def test_lora_linear_one_call_gate_up(ops, cuda):
     """The same through the interleaved gate/up projection with SiLU*up in the output write."""
     g = torch.Generator().manual_seed(5)
     T, K, I, r, n_ad = 24, 512, 1024, 16, 4
