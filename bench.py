@@ -195,7 +195,7 @@ def run_ours(args, rank, world, local_rank):
     total_steps = 2 * (K + W) + 8
     max_len = PROMPT_LEN + total_steps + 1
     kv = kv_mod.PagedKVCache(pm.L, pm.Hkv, pm.D, B, B * max_len, PROMPT_LEN, PAGE, dev, max_seq_len=max_len)
-    eng = model_mod.Engine(pm, kv, max_rows=max(128, B))
+    eng = model_mod.Engine(pm, kv, max_rows=max(4096, B))  # prefill in passes of 4096 rows; decode uses B rows
     sids = list(range(B))
     for s in sids:
         kv.add_sequence(s)
@@ -337,6 +337,12 @@ def run_ours(args, rank, world, local_rank):
         print(json.dumps(line), flush=True)
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one captured launch / its algorithmic bytes
+NCU_TRAFFIC_RATIO = {"linear": (107.34 + 4.18) / 108.1, "attention": (302.82 + 3.75) / 303.3}
+NCU_TRAFFIC_NOTE = {"linear": "profiles/linear_tc_kernel_qkv_T32.md (q/k/v launch: 111.5 MB of DRAM traffic for 108.1 MB algorithmic)",
+                    "attention": "profiles/paged_attn_kernel_ctx576.md"}
+
+
 def kernel_rooflines(eng, pm, kv, B, slots, ops, torch, ctx, n_uniq, peak, reps=5):
     """CUDA-event timing of (a) every tensor-core projection launch of one decode step and (b) every
     paged-attention launch of one step, each captured alone in a graph and replayed back to back.
@@ -405,7 +411,11 @@ def kernel_rooflines(eng, pm, kv, B, slots, ops, torch, ctx, n_uniq, peak, reps=
         out[name] = {"bound": "hbm", "kernel": kernel, "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "peak_source": peak_src + " copy bandwidth",
                      "launches": n, "avg_launch_us": 1e3 * ms / n, "algorithmic_bytes_per_launch": total / n,
-                     "traffic": None}
+                     # DRAM read+write bytes per launch: ncu capture of one launch of this kernel at the benchmark's
+                     # shapes (profiles/), as a ratio to that launch's algorithmic bytes, applied to the step's
+                     # average launch (traffic grows in proportion: the weights / KV pages dominate both)
+                     "traffic": NCU_TRAFFIC_RATIO[name] * total / n,
+                     "traffic_source": NCU_TRAFFIC_NOTE[name]}
     return out
 
 
