@@ -487,6 +487,26 @@ def run_kernel_case(which):
         out = torch.empty(T, 12288, dtype=torch.bfloat16, device=dev)
         for i in range(6):
             ops.linear(c["x"], Ws[i % 4], st, slots, u=u, out=out)
+        # CUDA-event time of the same launch, warm, inside a graph (4 weight copies per replay)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for W in Ws:
+                ops.linear(c["x"], W, st, slots, u=u, out=out)
+        for _ in range(3):
+            g.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(10):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        us = 1e3 * e0.elapsed_time(e1) / 40
+        by = 2 * 12288 * 4096 + len(set(slots.tolist())) * 2 * 12288 * RANK + 2 * T * 4096 + 2 * T * 12288 + 4 * T + 4 * T * 3 * RANK
+        peak, src = measured_peak()
+        print(json.dumps({"kernel_case": which, "us_per_launch": us, "algorithmic_bytes": by, "achieved_gbs": by / us / 1e3,
+                          "frac_of_peak": by / us / 1e3 / peak, "peak_source": src, "launches": ops.launch_count()}))
+        return
     elif which == "prefill":
         # prefill-size q/k/v projection: 8192 prompt rows (16 requests x 512, one adapter per request), shrink as
         # a grouped GEMM + projection with the expand as extra MMA stages; CUDA-event TFLOP/s of the pair

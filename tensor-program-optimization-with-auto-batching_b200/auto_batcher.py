@@ -27,17 +27,12 @@ import os
 import numpy as np
 import torch
 
+from . import adapter_contract
 from . import adapters as adapter_files
 from . import vm as mvm
+from .adapter_contract import LoraConfig  # same fields as tvm/llama_auto_batcher/lora.py:5-8
 from .model import PackedLlama
 from .seq_info import LlamaSeqInfo
-
-
-@dataclasses.dataclass(frozen=True)
-class LoraConfig:
-    """Same fields as ``tvm/llama_auto_batcher/lora.py:5-8``."""
-    r: int
-    alpha: float
 
 
 @dataclasses.dataclass
@@ -320,8 +315,11 @@ class LlamaAutoBatcherClass:
             for wid in range(max(wids[t]) + 1 if wids[t] else 0):
                 # the raw weight id indexes the type's stack (compile_tvm.py:298-313): ids are dense per type
                 path = adapter_files.adapter_path(self.adapter_dir, cfg.r, wid)
-                adapters.append(adapter_files.load_adapter(path))
-                scales.append(cfg.alpha / cfg.r)
+                # the config's adapter class is validated and probed (adapter_contract), its optional
+                # weight_computation runs here, once, and its post_computation constant becomes the scale
+                lowered, scale = adapter_contract.lower_adapter_file(adapter_files.load_adapter(path), cfg, self.model_config)
+                adapters.append(lowered)
+                scales.append(scale)
         model = PackedLlama(self.model_config, self.weights, adapters, scales, device=self.device)
         self.vm = mvm.B200VM(model, type_slot_base=base or [0])
         self.graph.set_exec_vars(self.vm, self.device, self.vm.params, self.tokenizer, self.seq_info, self.exec_config)

@@ -157,3 +157,49 @@ def test_ragged_prompts_and_sequence_removal(synth, cuda):
     wl = oracle.decode(live, t_in, [ids[s] for s in live])
     lg2, _ = eng.decode(live, t_in, [ids[s] for s in live])
     _check_logits(lg2, wl)
+
+
+def test_plumbing_config_at_its_full_size(synth, cuda):
+    """The CPU-runnable configuration at its stated size: 4 requests x 512-token prompts (2048 rows in one
+    prefill pass: grouped-GEMM shrink, 128-token tiles), 4 rank-8 adapters on q/k/v/o, ids [0,1,2,3], 32 greedy
+    tokens (teacher-forced against the fp32 oracle)."""
+    cfg, w, ads = _tiny(synth)
+    scales = [2.0] * 4
+    P = synth.prompts(4, 512, cfg["vocab_size"])
+    ids, gen = [0, 1, 2, 3], 32
+    oracle = ollama.OracleLlama(cfg, w, ads, scales)
+    want_tok, want_logits = oracle.greedy([list(p) for p in P], ids, gen)
+    pm, kv, eng = _engine(cfg, w, ads, scales, 4, 512 + gen + 1, cuda, max_rows=2048)
+    for s in range(4):
+        kv.add_sequence(s)
+    lg, tok = eng.prefill([0, 1, 2, 3], [list(p) for p in P], ids)
+    _check_logits(lg, want_logits[0])
+    agree = int((tok.cpu() == want_tok[:, 0]).sum())
+    for step in range(1, gen):
+        lg, tok = eng.decode([0, 1, 2, 3], want_tok[:, step - 1].tolist(), ids)
+        _check_logits(lg, want_logits[step])
+        agree += int((tok.cpu() == want_tok[:, step]).sum())
+    assert agree >= 0.95 * 4 * gen, f"greedy agreement {agree}/{4 * gen}"
+
+
+def test_prefill_heavy_skewed_adapters_on_all_projections(synth, cuda):
+    """Shape of the prefill-heavy configuration at small scale: rank-64 adapters on all seven projections, adapter
+    ids drawn Zipf(1.1) (skewed segment sizes, several requests per adapter), one prefill pass of 12 x 100 rows
+    (tiles that mix two adapters), then a few decode steps."""
+    n_ad, n_req = 8, 12
+    cfg, w, ads = _tiny(synth, n_adapters=n_ad, rank=64, targets=synth.ATTN_PROJ + synth.MLP_PROJ)
+    scales = [0.5] * n_ad
+    P = synth.prompts(n_req, 100, cfg["vocab_size"])
+    ids = [int(i) for i in synth.adapter_ids_zipf(n_req, n_ad)]
+    assert len(set(ids)) < n_req  # skewed: adapters are shared
+    oracle = ollama.OracleLlama(cfg, w, ads, scales)
+    want_tok, want_logits = oracle.greedy([list(p) for p in P], ids, 4)
+    pm, kv, eng = _engine(cfg, w, ads, scales, n_req, 100 + 8, cuda, max_rows=1280)
+    for s in range(n_req):
+        kv.add_sequence(s)
+    lg, tok = eng.prefill(list(range(n_req)), [list(p) for p in P], ids)
+    _check_logits(lg, want_logits[0])
+    for step in range(1, 4):
+        lg, tok = eng.decode(list(range(n_req)), want_tok[:, step - 1].tolist(), ids)
+        _check_logits(lg, want_logits[step])
+    assert int(load("ops").workspace(4, cuda, "linear")[:4].view(torch.int32)) == 0
