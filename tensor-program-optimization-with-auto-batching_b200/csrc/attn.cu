@@ -374,16 +374,16 @@ extern "C" int mlora_paged_attention(const void* d_qkv, int64_t ld, void* d_k_pa
   dim3 grid(Hq, T, n_splits);
   cudaStream_t st = (cudaStream_t)stream;
   if (D == 128 && page_size == 16)
-    launch_pdl(paged_attn_kernel<128, 8>, grid, 128, 0, st, a);
+    launch_pdl_if(pdl_enabled_attn(), paged_attn_kernel<128, 8>, grid, 128, 0, st, a);
   else if (D == 128 && page_size == 32)
-    launch_pdl(paged_attn_kernel<128, 16>, grid, 128, 0, st, a);
+    launch_pdl_if(pdl_enabled_attn(), paged_attn_kernel<128, 16>, grid, 128, 0, st, a);
   else if (D == 64 && page_size == 16)
-    launch_pdl(paged_attn_kernel<64, 4>, grid, 128, 0, st, a);
+    launch_pdl_if(pdl_enabled_attn(), paged_attn_kernel<64, 4>, grid, 128, 0, st, a);
   else
-    launch_pdl(paged_attn_kernel<64, 8>, grid, 128, 0, st, a);
+    launch_pdl_if(pdl_enabled_attn(), paged_attn_kernel<64, 8>, grid, 128, 0, st, a);
   count_launch();
   if (n_splits > 1) {
-    launch_pdl(attn_merge_kernel, dim3(Hq, T), D, 0, st, (const float*)d_work, Hq, D, n_splits, (bf16*)d_out, ld_out);
+    launch_pdl_if(pdl_enabled_attn(), attn_merge_kernel, dim3(Hq, T), D, 0, st, (const float*)d_work, Hq, D, n_splits, (bf16*)d_out, ld_out);
     count_launch();
   }
   MLORA_CHECK_LAUNCH("paged_attn_kernel");

@@ -78,6 +78,8 @@ void count_launch(int n = 1);
 bool pdl_enabled();
 bool pdl_enabled_gemm();
 bool pdl_enabled_shrink();
+bool pdl_enabled_attn();
+bool pdl_enabled_norm();
 
 // Programmatic dependent launch.  Every kernel of the decode step is launched with the
 // "programmatic stream serialization" attribute and begins with pdl_launch_dependents(), so the next

@@ -184,7 +184,7 @@ extern "C" int mlora_residual_rmsnorm(const void* d_delta, float* d_res, const v
   MLORA_REQUIRE(aligned16(d_res) && aligned16(d_w) && aligned16(d_out) && aligned16(d_delta),
                 "residual_rmsnorm: pointers must be 16-byte aligned");
   if (T == 0) return MLORA_OK;
-  launch_pdl(residual_rmsnorm_kernel, T, kNormThreads, 0, (cudaStream_t)stream, (const bf16*)d_delta, d_res,
+  launch_pdl_if(pdl_enabled_norm(), residual_rmsnorm_kernel, T, kNormThreads, 0, (cudaStream_t)stream, (const bf16*)d_delta, d_res,
              (const bf16*)d_w, eps, (bf16*)d_out, H);
   count_launch();
   MLORA_CHECK_LAUNCH("residual_rmsnorm_kernel");

@@ -260,7 +260,7 @@ int launch_lora_shrink_tc(const void* x, int64_t ldx, const void* A_all, const i
     if (e != cudaSuccess) return fail(MLORA_ECUDA, "lora_shrink: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     attr_done.fetch_or(1ull << (dev & 63), std::memory_order_release);
   }
-  launch_pdl_if(pdl_enabled(), lora_shrink_tc_kernel, dim3((T + kTok - 1) / kTok), dim3(kShrinkThreads), smem, st, mx, ma, p);
+  launch_pdl_if(pdl_enabled_shrink(), lora_shrink_tc_kernel, dim3((T + kTok - 1) / kTok), dim3(kShrinkThreads), smem, st, mx, ma, p);
   count_launch();
   MLORA_CHECK_LAUNCH("lora_shrink_tc_kernel");
   return MLORA_OK;

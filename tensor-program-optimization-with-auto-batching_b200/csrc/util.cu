@@ -33,9 +33,21 @@ static int pdl_mode() {
   }();
   return mode;
 }
-bool pdl_enabled() { return pdl_mode() == 1; }
-bool pdl_enabled_gemm() { return pdl_mode() >= 1; }
-bool pdl_enabled_shrink() { return pdl_mode() == 1 || pdl_mode() == 3; }  // "3": projection and LoRA shrink
+// MLORA_PDL_MASK (experiments) overrides the mode: bit 0 projection, 1 LoRA shrink, 2 attention, 3 RMSNorm, 4 the rest.
+static int pdl_mask() {
+  static const int mask = [] {
+    const char* e = getenv("MLORA_PDL_MASK");
+    if (e) return atoi(e);
+    const int m = pdl_mode();
+    return m == 0 ? 0 : m == 1 ? 31 : m == 3 ? 3 : 1;
+  }();
+  return mask;
+}
+bool pdl_enabled() { return (pdl_mask() & 16) != 0; }
+bool pdl_enabled_gemm() { return (pdl_mask() & 1) != 0; }
+bool pdl_enabled_shrink() { return (pdl_mask() & 2) != 0; }
+bool pdl_enabled_attn() { return (pdl_mask() & 4) != 0; }
+bool pdl_enabled_norm() { return (pdl_mask() & 8) != 0; }
 
 void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
 
