@@ -387,13 +387,16 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
       }
       n += sg.kb1 - sg.kb0;
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      if (ok && (LM == 2 && p.lora_mode == 2) && sg.kb1 == p.k_blocks) {
+      if (ok && (LM == 2 && p.lora_mode == 2) && sg.kb0 == 0) {
         if (!got_preload) {  // operands of the first token tile, staged by the epilogue warps at start-up
           mbar_wait(preload_bar, 0, &s_abort);
           n_seg = s_nseg0;
           got_preload = true;
         }
-        // The tile's last k-block is ours: append the LoRA stages.  One stage per (adapter present in
+        // The tile's first k-blocks are ours: this CTA also runs the tile's LoRA stages, after them.  (For a split
+        // tile that is the CTA that finishes it, at the END of its range, when the shrink outputs have long been
+        // staged and the operands built; the CTA holding the tile's last k-blocks reaches them at the very start
+        // of its range and would have to wait for all that first.)  One stage per (adapter present in
         // the token tile, 64-wide slice of the rank); its A operand is B_all[slot, rows of the tile, slice].
         // When the B operands are cached in shared memory, up to `group` such slices share one ring slot.
         if (tok_tile != cur_tok_tile) {
@@ -457,7 +460,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
       }
       n += sg.kb1 - sg.kb0;
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      if (ok && (LM == 2 && p.lora_mode == 2) && sg.kb1 == p.k_blocks) {
+      if (ok && (LM == 2 && p.lora_mode == 2) && sg.kb0 == 0) {
         if (!got_preload) {  // operands of the first token tile, staged by the epilogue warps at start-up
           mbar_wait(preload_bar, 0, &s_abort);
           n_seg = s_nseg0;
@@ -616,7 +619,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
       const uint32_t d_tmem = tmem_base + buf * BN;
       int n_l = 0, group = 1;
       bool cached = false, new_build = false;
-      if ((LM == 2 && p.lora_mode == 2) && sg.kb1 == p.k_blocks) {
+      if ((LM == 2 && p.lora_mode == 2) && sg.kb0 == 0) {
         if (!got_preload) {  // operands of the first token tile, staged by the epilogue warps at start-up
           mbar_wait(preload_bar, 0, &s_abort);
           n_seg = s_nseg0;
