@@ -77,7 +77,7 @@ int mlora_bucket_sort(const int32_t* d_tids, const int32_t* d_wids, int32_t n, i
  * GatherBMMLinear.forward (huggingface/custom_peft/lora_gatherbmm_linear_layer.py:16-19).
  *   d_x [T, in] bf16 (row stride ldx elements); d_A_all [N, n_mod*r_max, in] bf16;
  *   d_ranks [N] int32 (rank of each adapter slot, <= r_max; rows of A_all at or beyond the rank
- *   must be zero: the decode-size kernel skips them, the prefill-size kernel multiplies them);
+ *   must be zero: both kernels multiply them rather than look the rank up);
  *   d_slots [T] int32 (adapter slot of each row; < 0 or >= n_adapters = none -> u row is zero);
  *   d_u [T, n_mod*r_max] float32.  n_mod modules share the input (q,k,v or gate,up).
  * T < 256: one warp per (row, rank index) on CUDA cores.  T >= 256 (prefill) with n_mod*r_max <= 256:

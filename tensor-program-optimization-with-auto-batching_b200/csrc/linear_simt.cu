@@ -22,7 +22,9 @@ __global__ void __launch_bounds__(256) lora_shrink_kernel(const bf16* __restrict
   if (j >= r_tot) return;
   const int slot = slots[t];
   float acc = 0.f;
-  if (slot >= 0 && slot < n_adapters && (j % r_max) < ranks[slot]) {
+  // (rows of A at or beyond an adapter's rank are zero by contract: multiplied, not looked up -- one dependent
+  // global load less in a kernel that is nothing but a chain of round trips)
+  if (slot >= 0 && slot < n_adapters) {
     const bf16* a = A_all + ((size_t)slot * r_tot + j) * in;
     const bf16* xr = x + (size_t)t * ldx;
     // 8 chunks of A and of x are requested before the first is used: the dot product is a chain of
