@@ -20,26 +20,20 @@ int fail(int code, const char* fmt, ...) {
   return code;
 }
 
-// Programmatic dependent launch policy (MLORA_PDL): default "2" = only the projection kernel is launched
-// programmatically dependent, so its weight producer streams while the small kernel before it (RMSNorm,
-// LoRA shrink, attention tail) still runs: measured 5 % faster on the benchmark's decode step.  "1" = every
-// decode kernel (measured 1-2 % slower than plain stream order: early-resident CTAs compete with the tail
-// of the kernel before them), "0" = off.
-static int pdl_mode() {
-  static const int mode = [] {
-    const char* e = getenv("MLORA_PDL");
-    if (!e) return 2;
-    return strcmp(e, "0") == 0 ? 0 : strcmp(e, "1") == 0 ? 1 : strcmp(e, "3") == 0 ? 3 : 2;
-  }();
-  return mode;
-}
-// MLORA_PDL_MASK (experiments) overrides the mode: bit 0 projection, 1 LoRA shrink, 2 attention, 3 RMSNorm, 4 the rest.
+// Programmatic dependent launch policy.  Which kernels are launched programmatically dependent (may become
+// resident, and run whatever does not depend on earlier kernels, while the kernel before them still runs) is a
+// bit mask: bit 0 projection (its weight producer streams ahead), 1 LoRA shrink, 2 attention, 3 RMSNorm, 4 the
+// rest.  Measured on the benchmark's decode step: projection only (1) 5.60 ms, projection + RMSNorm (9) 5.53 ms --
+// the default --, + shrink (3 / 11) 5.57, + attention (5 / 13) 5.79-5.84 (its early-resident CTAs take registers
+// and issue slots from the kernel before them), everything (31) slowest, none (0) 5.9.
+// MLORA_PDL_MASK=<mask> overrides; MLORA_PDL=0 / 1 / 2 / 3 are shorthands for masks 0 / 31 / 1 / 3.
 static int pdl_mask() {
   static const int mask = [] {
     const char* e = getenv("MLORA_PDL_MASK");
     if (e) return atoi(e);
-    const int m = pdl_mode();
-    return m == 0 ? 0 : m == 1 ? 31 : m == 3 ? 3 : 1;
+    e = getenv("MLORA_PDL");
+    if (!e) return 9;
+    return strcmp(e, "0") == 0 ? 0 : strcmp(e, "1") == 0 ? 31 : strcmp(e, "3") == 0 ? 3 : 1;
   }();
   return mask;
 }
