@@ -787,6 +787,54 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
         }
       };
 
+      // Split tile: who contributes, and is this CTA the one that finishes it?
+      long long ts = 0, te = 0;
+      int c_first = 0, c_last = 0;
+      if (!full_seg) {
+        ts = (long long)sg.tile * p.k_blocks;
+        te = ts + p.k_blocks;
+        c_first = (int)(ts / p.per_cta);
+        c_last = (int)((te - 1) / p.per_cta);
+      }
+      const bool finisher = !full_seg && (int)blockIdx.x == c_first;
+      // Single-chunk token tiles: the finisher collects the other contributors' partial sums NOW, while its own
+      // last MMAs are still running (the contributors met this tile at the very start of their ranges, so their
+      // partials have been in L2 for a long time), instead of after them in the kernel's tail.
+      float pre[32];
+      bool pre_have = true;
+      if constexpr (BN <= 32) {
+        if (finisher) {
+          if (etid == 0) {
+            const int need = c_last - c_first;
+            bool got = false;
+            for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+              int seen;
+              asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(p.tickets + c_first) : "memory");
+              if (seen >= need) {
+                got = true;
+                break;
+              }
+              __nanosleep(64);
+            }
+            p.tickets[c_first] = 0;  // ready for the next call
+            s_last = got ? 1 : 0;
+            if (!got) atomicOr(p.status, 128);
+          }
+          epi_bar_sync();
+          pre_have = s_last != 0;
+#pragma unroll
+          for (int i = 0; i < C::kChunk; ++i) pre[i] = 0.f;
+          if (pre_have) {
+            for (int cc = c_first + 1; cc <= c_last; ++cc) {  // CTA order: deterministic
+              const float* ps = p.partials + ((size_t)cc * 2) * (size_t)(BN * BM);
+#pragma unroll
+              for (int i = 0; i < C::kChunk; ++i) pre[i] += __ldcg(ps + (size_t)i * BM + etid);
+            }
+          }
+          epi_bar_sync();  // s_last is reused by the next split segment
+        }
+      }
+
       if (!mbar_wait(&acc_full[buf], (j >> 1) & 1, &s_abort)) {
         if (!s_abort) {
           s_abort = 1;
@@ -816,9 +864,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
         // finishes the tile: the others publish an fp32 partial in scratch and bump the tile's counter;
         // the finisher waits (bounded) for the counter, adds the partials to its own accumulator in CTA
         // order -- deterministic -- and runs the epilogue.  It never writes a partial of its own.
-        const long long ts = (long long)sg.tile * p.k_blocks, te = ts + p.k_blocks;
-        const int c_first = (int)(ts / p.per_cta), c_last = (int)((te - 1) / p.per_cta);
-        if ((int)blockIdx.x != c_first) {
+        if (!finisher) {
           // slot 0 if this CTA's range starts inside the tile (always, except for c_first), kept general
           const bool starts_here = rg.it0 >= ts;
           float* part = p.partials + ((size_t)blockIdx.x * 2 + (starts_here ? 0 : 1)) * (size_t)(BN * BM);
@@ -835,6 +881,17 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
           __threadfence();
           epi_bar_sync();
           if (etid == 0) atomicAdd(&p.tickets[c_first], 1);
+        } else if constexpr (BN <= 32) {
+          float v[32];
+          if (BN >= 32) tmem_ld32(t_addr, v); else tmem_ld16(t_addr, v);
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&acc_empty[buf]);
+          if (pre_have) {
+#pragma unroll
+            for (int i = 0; i < C::kChunk; ++i) v[i] += pre[i];
+            finish(v, 0);
+          }
         } else {
           if (etid == 0) {
             const int need = c_last - c_first;

@@ -121,13 +121,32 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
   const float* l = logits + (size_t)blockIdx.x * ld;
   float best = -FLT_MAX;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    float v = l[i];
-    if (v > best) {  // strided ascending scan: first max per thread
+  auto take = [&](float v, int i) {  // maximum, lowest index on ties (any visiting order)
+    if (v > best || (v == best && i < bi)) {
       best = v;
       bi = i;
     }
+  };
+  // 128-bit loads, four per thread in flight: a row is 128 KB read by one CTA, i.e. a chain of L2 round trips
+  const int V4 = ((reinterpret_cast<uintptr_t>(l) & 15) == 0) ? V / 4 : 0;
+  const float4* l4 = reinterpret_cast<const float4*>(l);
+  for (int i = threadIdx.x; i < V4; i += blockDim.x * 4) {
+    float4 q[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (i + u * (int)blockDim.x < V4) q[u] = l4[i + u * blockDim.x];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int idx = i + u * (int)blockDim.x;
+      if (idx < V4) {
+        take(q[u].x, 4 * idx);
+        take(q[u].y, 4 * idx + 1);
+        take(q[u].z, 4 * idx + 2);
+        take(q[u].w, 4 * idx + 3);
+      }
+    }
   }
+  for (int i = 4 * V4 + threadIdx.x; i < V; i += blockDim.x) take(l[i], i);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     float ov = __shfl_xor_sync(0xffffffffu, best, o);

@@ -35,3 +35,29 @@ def test_host_side_argument_checks_need_no_gpu():
     assert rc == -1 and b"head_dim" in h.mlora_last_error()
     assert h.mlora_bucket_sort_workspace(1024, 4, 64) == 0
     assert h.mlora_bucket_sort_workspace(5000, 1, 16) == 5 * 17 * 4
+
+
+def test_every_entry_point_rejects_nonsense_on_the_host():
+    """Negative sizes and null pointers come back as a negative status with a message, from every launching entry
+    point, on a machine without a GPU: nothing is launched and nothing is dereferenced."""
+    import ctypes as C
+
+    lib = load("_lib")
+    h = lib.lib()
+    seen = 0
+    for name, (res, args) in sorted(lib.PROTOTYPES.items()):
+        if res is not C.c_int or name == "mlora_version":
+            continue
+        vals = []
+        for a in args:
+            if a is C.c_void_p or hasattr(a, "contents") or (hasattr(a, "_type_") and not isinstance(a._type_, str)):
+                vals.append(None)
+            elif a in (C.c_float, C.c_double):
+                vals.append(0.0)
+            else:
+                vals.append(-1)
+        rc = getattr(h, name)(*vals)
+        assert rc < 0, f"{name} accepted negative sizes / null pointers"
+        assert len(h.mlora_last_error()) > 0
+        seen += 1
+    assert seen >= 12
