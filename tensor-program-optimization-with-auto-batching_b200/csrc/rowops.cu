@@ -42,14 +42,14 @@ __global__ void __launch_bounds__(kNormThreads) residual_rmsnorm_kernel(const bf
   const bf16* d = delta ? delta + row * H : nullptr;
   float keep[kNormChunks][8];
   float ss = 0.f;
-  // pass 1: add the delta, store the new residual, accumulate the sum of squares
-  auto load_add = [&](int k, float (&v)[8]) {
-    float4 a = *reinterpret_cast<const float4*>(r + k);
-    float4 b = *reinterpret_cast<const float4*>(r + k + 4);
+  // pass 1: add the delta, store the new residual, accumulate the sum of squares.  The loads of all of a
+  // thread's chunks are issued before the first store (the stores go to the array the loads read, so the
+  // compiler keeps their order): one round trip for the row instead of one per chunk.
+  auto add_store = [&](int k, const float4& a, const float4& b, const uint4& draw, float (&v)[8]) {
     v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
     if (d) {
       float df[8];
-      unpack8(ld_cached(d + k), df);
+      unpack8(draw, df);
 #pragma unroll
       for (int i = 0; i < 8; ++i) v[i] += df[i];
       *reinterpret_cast<float4*>(r + k) = make_float4(v[0], v[1], v[2], v[3]);
@@ -58,21 +58,43 @@ __global__ void __launch_bounds__(kNormThreads) residual_rmsnorm_kernel(const bf
 #pragma unroll
     for (int i = 0; i < 8; ++i) ss = fmaf(v[i], v[i], ss);
   };
+  {
+    float4 ra[kNormChunks], rb[kNormChunks];
+    uint4 rd[kNormChunks];
 #pragma unroll
-  for (int c = 0; c < kNormChunks; ++c) {
-    const int k = (c * kNormThreads + threadIdx.x) * 8;
-    if (k < H) load_add(k, keep[c]);
+    for (int c = 0; c < kNormChunks; ++c) {
+      const int k = (c * kNormThreads + threadIdx.x) * 8;
+      if (k < H) {
+        ra[c] = *reinterpret_cast<const float4*>(r + k);
+        rb[c] = *reinterpret_cast<const float4*>(r + k + 4);
+        if (d) rd[c] = ld_cached(d + k);
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < kNormChunks; ++c) {
+      const int k = (c * kNormThreads + threadIdx.x) * 8;
+      if (k < H) add_store(k, ra[c], rb[c], rd[c], keep[c]);
+    }
   }
   for (int k = (kNormChunks * kNormThreads + threadIdx.x) * 8; k < H; k += kNormThreads * 8) {
     float v[8];
-    load_add(k, v);
+    const float4 a = *reinterpret_cast<const float4*>(r + k), b = *reinterpret_cast<const float4*>(r + k + 4);
+    uint4 dr = make_uint4(0u, 0u, 0u, 0u);
+    if (d) dr = ld_cached(d + k);
+    add_store(k, a, b, dr, v);
+  }
+  uint4 wq[kNormChunks];  // norm weights: requested before the block-wide reduction, used after it
+#pragma unroll
+  for (int c = 0; c < kNormChunks; ++c) {
+    const int k = (c * kNormThreads + threadIdx.x) * 8;
+    if (k < H) wq[c] = ld_cached(w + k);
   }
   ss = block_sum(ss, sm);
   const float inv = rsqrtf(ss / (float)H + eps);
   // pass 2: scale and write
-  auto write = [&](int k, const float (&v)[8]) {
+  auto write = [&](int k, const float (&v)[8], const uint4& wraw) {
     float wf[8], o[8];
-    unpack8(ld_cached(w + k), wf);
+    unpack8(wraw, wf);
 #pragma unroll
     for (int i = 0; i < 8; ++i) o[i] = v[i] * inv * wf[i];
     *reinterpret_cast<uint4*>(out + row * H + k) = pack8(o);
@@ -80,13 +102,13 @@ __global__ void __launch_bounds__(kNormThreads) residual_rmsnorm_kernel(const bf
 #pragma unroll
   for (int c = 0; c < kNormChunks; ++c) {
     const int k = (c * kNormThreads + threadIdx.x) * 8;
-    if (k < H) write(k, keep[c]);
+    if (k < H) write(k, keep[c], wq[c]);
   }
   for (int k = (kNormChunks * kNormThreads + threadIdx.x) * 8; k < H; k += kNormThreads * 8) {
     float4 a = *reinterpret_cast<const float4*>(r + k);
     float4 b = *reinterpret_cast<const float4*>(r + k + 4);
     float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-    write(k, v);
+    write(k, v, ld_cached(w + k));
   }
 }
 
