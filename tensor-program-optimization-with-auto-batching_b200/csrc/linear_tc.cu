@@ -156,9 +156,12 @@ struct Cfg {
   // barriers | 7 integer lists of BN (token slots / distinct adapters per role) | staged shrink outputs
   // LoRA B operands (scaled, masked shrink outputs) of a token tile; prefill-size tiles get room for a rank-128
   // pitch (interleaved gate/up at rank 64) so the operands are built once per token tile, not once per tile
-  static constexpr int kCacheBytes = (BN >= 128 ? 48 : 16) * 1024;
-  static constexpr int kOutBytes = 32 * BM * 4;  // staging of one 32-token output chunk (fp32 worst case)
-  static constexpr int kAuxBytes = 1024 + 8 * BN * 4 + kStageUMax + kCacheBytes + kOutBytes;
+  static constexpr int kCacheBytes = (BN >= 128 ? 64 : 16) * 1024;  // 128-token tiles: 16 rank-16 adapters or 2 of pitch 128
+  // shrink outputs of a token tile staged in shared memory (decode-size tiles only; larger tiles read them from L2)
+  static constexpr int kStageU = BN >= 128 ? 0 : kStageUMax;
+  // staging of one 32-token output chunk; fp32 outputs of 128-token tiles leave through per-thread stores instead
+  static constexpr int kOutBytes = 32 * BM * (BN >= 128 ? 2 : 4);
+  static constexpr int kAuxBytes = 1024 + 8 * BN * 4 + kStageU + kCacheBytes + kOutBytes;
   static constexpr int kBudget = 227 * 1024 - 1024 /*alignment slack*/ - 64 /*static*/;
   static constexpr int kWStages0 = (kBudget - kAuxBytes - kXStages * kXBytes) / kWBytes;
   static constexpr int kWStages = kWStages0 > 10 ? 10 : kWStages0;  // measured: 5 stages already saturate
@@ -320,7 +323,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
   int first_it = rg.it0;
   const int first_tile = next_segment<WAVE>(p, first_it, rg.it1).tile;
   const int tok_tile0 = (first_tile < 0 ? 0 : first_tile) / p.row_tiles;
-  const bool stage_u2 = (LM == 2 && p.lora_mode == 2) && (size_t)BN * r_tot * sizeof(float) <= (size_t)kStageUMax;
+  const bool stage_u2 = (LM == 2 && p.lora_mode == 2) && (size_t)BN * r_tot * sizeof(float) <= (size_t)C::kStageU;
   if (warp != 0) pdl_wait();
   if ((LM == 2 && p.lora_mode == 2) && warp >= 2 && warp <= 5) {
     // The per-token LoRA operands of the CTA's first token tile (decode: the only one) are fetched now,
@@ -720,7 +723,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
     const bool silu = (a.flags & MLORA_SILU_MUL) != 0;
     const bool out_f32 = (a.flags & MLORA_OUT_F32) != 0;
     constexpr bool simt_lora = LM == 1;
-    const bool stage_u = simt_lora && (size_t)BN * r_tot * sizeof(float) <= (size_t)kStageUMax;
+    const bool stage_u = simt_lora && (size_t)BN * r_tot * sizeof(float) <= (size_t)C::kStageU;
     int staged_tok_tile = -1;
     int it = rg.it0, j = 0;
 
@@ -1057,7 +1060,7 @@ int launch(const LinearArgs& a, const Plan& pl, void* work, cudaStream_t st) {
   {
     const bool f32 = (a.flags & MLORA_OUT_F32) != 0, silu = (a.flags & MLORA_SILU_MUL) != 0;
     const int es = f32 ? 4 : 2, cols = silu ? a.out / 2 : a.out;
-    p.tma_store = aligned16(a.y) && (a.ldy * es) % 16 == 0 && (cols * es) % 16 == 0;
+    p.tma_store = !(BN >= 128 && f32) && aligned16(a.y) && (a.ldy * es) % 16 == 0 && (cols * es) % 16 == 0;
     if (p.tma_store) {
       rc = make_out_map(&my, a.y, a.T, cols, a.ldy, BN < 32 ? BN : 32, silu ? BM / 2 : BM, f32);
       if (rc) return rc;
