@@ -338,8 +338,8 @@ def run_ours(args, rank, world, local_rank):
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one captured launch / its algorithmic bytes
-NCU_TRAFFIC_RATIO = {"linear": (107.34 + 4.18) / 108.1, "attention": (302.82 + 3.75) / 303.3}
-NCU_TRAFFIC_NOTE = {"linear": "profiles/linear_tc_kernel_qkv_T32.md (q/k/v launch: 111.5 MB of DRAM traffic for 108.1 MB algorithmic)",
+NCU_TRAFFIC_RATIO = {"linear": (107.35 + 4.36) / 108.0, "attention": (302.82 + 3.75) / 303.3}
+NCU_TRAFFIC_NOTE = {"linear": "profiles/linear_tc_kernel_qkv_T32.md (q/k/v launch: 111.7 MB of DRAM traffic for 108.0 MB algorithmic)",
                     "attention": "profiles/paged_attn_kernel_ctx576.md"}
 
 
