@@ -154,6 +154,18 @@ int mlora_lora_linear(const void* d_x, int64_t ldx, const void* d_W, void* d_y, 
 int mlora_residual_rmsnorm(const void* d_delta, float* d_res, const void* d_w, float eps,
                            void* d_out, int32_t T, int32_t H, void* stream);
 
+/* The same with the LoRA shrink of the projection that reads the normalised row fused in:
+ *   res_out = res_in + delta;  out = RMSNorm(res_out) * w;  u[t, j] = A_all[slot[t], j, :] . out[t, :]
+ * (out as rounded to bf16, i.e. exactly what mlora_lora_shrink would read).  One launch instead of two for
+ * "input_layernorm -> q/k/v adapters" (llama_for_causal_lm.py:76-84 followed by compile_tvm.py:126-134).
+ * Several CTAs share a row and re-read the old residual while one of them writes the new one, so the
+ * residual moves from d_res_in to a DIFFERENT buffer d_res_out.  H <= 8192; d_A_all [N, r_tot, H] with
+ * zero rows beyond each adapter's rank; d_u [T, r_tot] float32. */
+int mlora_residual_rmsnorm_shrink(const void* d_delta, const float* d_res_in, float* d_res_out, const void* d_w,
+                                  float eps, void* d_out, int32_t T, int32_t H, const void* d_A_all,
+                                  const int32_t* d_slots, int32_t n_adapters, int32_t r_tot, float* d_u,
+                                  void* stream);
+
 /* ---- embedding gather: res[t,:] = float(E[ids[t], :]) ------------------------------------------
  * vm["embed"](input_ids, params) (tvm/llama_auto_batcher/llama_for_causal_lm.py:121-122).
  * Optionally also writes the gathered rows as bf16 to d_out_bf16 (the reference's return value). */

@@ -31,6 +31,7 @@ PROTOTYPES = {
     "mlora_lora_linear": (C.c_int, [_vp, _i64, _vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32,
                                     _i32, C.POINTER(_i32), _i32, _vp, _sz, _vp]),
     "mlora_residual_rmsnorm": (C.c_int, [_vp, _vp, _vp, _f32, _vp, _i32, _i32, _vp]),
+    "mlora_residual_rmsnorm_shrink": (C.c_int, [_vp, _vp, _vp, _vp, _f32, _vp, _i32, _i32, _vp, _vp, _i32, _i32, _vp, _vp]),
     "mlora_embed": (C.c_int, [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp]),
     "mlora_argmax": (C.c_int, [_vp, _i64, _i32, _i32, _vp, _vp]),
     "mlora_kv_append_rope": (C.c_int, [_vp, _i64, _vp, _vp, _vp, _i32, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _f32, _vp]),

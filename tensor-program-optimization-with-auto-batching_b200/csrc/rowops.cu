@@ -112,6 +112,158 @@ __global__ void __launch_bounds__(kNormThreads) residual_rmsnorm_kernel(const bf
   }
 }
 
+// ---- fused residual add + RMSNorm + LoRA shrink ---------------------------------------------------------------
+// The q/k/v (or gate/up) shrink reads exactly the row this kernel has just normalised, and both kernels are chains
+// of a few memory round trips with a launch in between.  Fused, every thread keeps its elements of the normalised
+// row in registers and multiplies them with the same positions of a group of A rows, all requested in ONE round
+// trip while the row statistics are still being reduced; the per-row dot products are then block-wide sums.
+// kNsSplit CTAs share a token row: each recomputes the (cheap) normalisation and takes a quarter of the rank
+// rows, so a CTA stays small -- and uses no shared memory to speak of -- and the projection launched behind it
+// can become resident beside it.  Only split 0 writes the residual and the normalised row; because the other
+// splits read the OLD residual while it does, the residual goes from res_in to a different buffer res_out.
+constexpr int kNsThreads = 256;
+constexpr int kNsSplit = 4;
+constexpr int kNsMaxH = 8192;
+
+template <int NCH>  // chunks of 8 per thread: 2 (H <= 4096) or 4 (H <= 8192)
+__global__ void __launch_bounds__(kNsThreads) rmsnorm_shrink_kernel(const bf16* __restrict__ delta,
+                                                                    const float* __restrict__ res_in,
+                                                                    float* __restrict__ res_out,
+                                                                    const bf16* __restrict__ w, float eps,
+                                                                    bf16* __restrict__ out, int H,
+                                                                    const bf16* __restrict__ A_all,
+                                                                    const int32_t* __restrict__ slots, int n_adapters,
+                                                                    int r_tot, float* __restrict__ u) {
+  constexpr int GROUP = 24 / NCH;  // A rows requested together: 24 128-bit loads in flight per thread
+  __shared__ float sm[33];
+  __shared__ float sred[kNsThreads / 32][GROUP];
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t row = blockIdx.y;
+  const int split = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int slot = slots[row];
+  const bool has = slot >= 0 && slot < n_adapters;
+  const int per = (r_tot + kNsSplit - 1) / kNsSplit;
+  const int j0 = split * per, j1 = min(r_tot, j0 + per);  // rank rows of this CTA
+  const float* r = res_in + row * H;
+  const bf16* d = delta ? delta + row * H : nullptr;
+  // ---- residual add, sum of squares (every split) ----
+  float keep[NCH][8];
+  float ss = 0.f;
+  {
+    float4 ra[NCH], rb[NCH];
+    uint4 rd[NCH];
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      const int k = (c * kNsThreads + threadIdx.x) * 8;
+      if (k < H) {
+        ra[c] = *reinterpret_cast<const float4*>(r + k);
+        rb[c] = *reinterpret_cast<const float4*>(r + k + 4);
+        if (d) rd[c] = ld_cached(d + k);
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      const int k = (c * kNsThreads + threadIdx.x) * 8;
+      float (&v)[8] = keep[c];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = 0.f;
+      if (k < H) {
+        v[0] = ra[c].x, v[1] = ra[c].y, v[2] = ra[c].z, v[3] = ra[c].w;
+        v[4] = rb[c].x, v[5] = rb[c].y, v[6] = rb[c].z, v[7] = rb[c].w;
+        if (d) {
+          float df[8];
+          unpack8(rd[c], df);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] += df[i];
+        }
+        if (split == 0) {
+          *reinterpret_cast<float4*>(res_out + row * H + k) = make_float4(v[0], v[1], v[2], v[3]);
+          *reinterpret_cast<float4*>(res_out + row * H + k + 4) = make_float4(v[4], v[5], v[6], v[7]);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss = fmaf(v[i], v[i], ss);
+      }
+    }
+  }
+  uint4 wq[NCH];
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    const int k = (c * kNsThreads + threadIdx.x) * 8;
+    if (k < H) wq[c] = ld_cached(w + k);
+  }
+  // A rows of the first group: requested before the block-wide reduction
+  uint4 av[GROUP][NCH];
+  auto request = [&](int jb) {
+#pragma unroll
+    for (int jj = 0; jj < GROUP; ++jj) {
+      if (jb + jj < j1) {
+        const bf16* a = A_all + ((size_t)slot * r_tot + jb + jj) * H;
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) {
+          const int k = (c * kNsThreads + threadIdx.x) * 8;
+          if (k < H) av[jj][c] = ld_cached(a + k);
+        }
+      }
+    }
+  };
+  if (has) request(j0);
+  ss = block_sum(ss, sm);
+  const float inv = rsqrtf(ss / (float)H + eps);
+  // ---- normalised row: written by split 0, kept (as rounded to bf16) by everyone ----
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    const int k = (c * kNsThreads + threadIdx.x) * 8;
+    if (k < H) {
+      float wf[8], o[8];
+      unpack8(wq[c], wf);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = keep[c][i] * inv * wf[i];
+      const uint4 packed = pack8(o);
+      if (split == 0) *reinterpret_cast<uint4*>(out + row * H + k) = packed;
+      unpack8(packed, keep[c]);  // exactly what the projection (and a separate shrink) would read
+    }
+  }
+  // ---- shrink: u[row, j] = A[slot, j, :] . xn ----
+  for (int jb = j0; jb < j1; jb += GROUP) {
+    float part[GROUP];
+    if (has) {
+      if (jb != j0) request(jb);
+#pragma unroll
+      for (int jj = 0; jj < GROUP; ++jj) {
+        float acc = 0.f;
+        if (jb + jj < j1) {
+#pragma unroll
+          for (int c = 0; c < NCH; ++c) {
+            if ((c * kNsThreads + (int)threadIdx.x) * 8 < H) {
+              float af[8];
+              unpack8(av[jj][c], af);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) acc = fmaf(af[i], keep[c][i], acc);
+            }
+          }
+        }
+        part[jj] = warp_sum(acc);
+      }
+      if (lane == 0) {
+#pragma unroll
+        for (int jj = 0; jj < GROUP; ++jj) sred[warp][jj] = part[jj];
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x < GROUP && jb + (int)threadIdx.x < j1) {
+      float acc = 0.f;
+      if (has) {
+#pragma unroll
+        for (int wv = 0; wv < kNsThreads / 32; ++wv) acc += sred[wv][threadIdx.x];
+      }
+      u[row * r_tot + jb + threadIdx.x] = acc;
+    }
+    __syncthreads();
+  }
+}
+
 __global__ void __launch_bounds__(256) embed_kernel(const int32_t* __restrict__ ids, const bf16* __restrict__ E,
                                                     int H, int vocab, float* __restrict__ res,
                                                     bf16* __restrict__ out_bf16) {
@@ -229,6 +381,33 @@ extern "C" int mlora_residual_rmsnorm(const void* d_delta, float* d_res, const v
              (const bf16*)d_w, eps, (bf16*)d_out, H);
   count_launch();
   MLORA_CHECK_LAUNCH("residual_rmsnorm_kernel");
+  return MLORA_OK;
+}
+
+extern "C" int mlora_residual_rmsnorm_shrink(const void* d_delta, const float* d_res_in, float* d_res_out, const void* d_w,
+                                             float eps, void* d_out, int32_t T, int32_t H, const void* d_A_all,
+                                             const int32_t* d_slots, int32_t n_adapters, int32_t r_tot, float* d_u,
+                                             void* stream) {
+  MLORA_REQUIRE(T >= 0 && H > 0 && H % 8 == 0 && H <= kNsMaxH, "residual_rmsnorm_shrink: H must be a multiple of 8 up to %d (H=%d)",
+                kNsMaxH, H);
+  MLORA_REQUIRE(d_res_in && d_res_out && d_w && d_out && d_A_all && d_slots && d_u, "residual_rmsnorm_shrink: null pointer");
+  MLORA_REQUIRE((const void*)d_res_in != (const void*)d_res_out, "residual_rmsnorm_shrink: res_in and res_out must be different buffers");
+  MLORA_REQUIRE(n_adapters > 0 && r_tot > 0, "residual_rmsnorm_shrink: bad adapter sizes");
+  MLORA_REQUIRE(aligned16(d_res_in) && aligned16(d_res_out) && aligned16(d_w) && aligned16(d_out) && aligned16(d_A_all) &&
+                    (!d_delta || aligned16(d_delta)),
+                "residual_rmsnorm_shrink: pointers must be 16-byte aligned");
+  if (T == 0) return MLORA_OK;
+  MLORA_REQUIRE(T <= 65535, "residual_rmsnorm_shrink: T=%d exceeds 65535 rows per call", T);
+  if (H <= 2 * kNsThreads * 8)
+    launch_pdl_if(pdl_enabled_norm(), rmsnorm_shrink_kernel<2>, dim3(kNsSplit, T), dim3(kNsThreads), 0, (cudaStream_t)stream,
+                  (const bf16*)d_delta, d_res_in, d_res_out, (const bf16*)d_w, eps, (bf16*)d_out, H, (const bf16*)d_A_all,
+                  d_slots, n_adapters, r_tot, d_u);
+  else
+    launch_pdl_if(pdl_enabled_norm(), rmsnorm_shrink_kernel<4>, dim3(kNsSplit, T), dim3(kNsThreads), 0, (cudaStream_t)stream,
+                  (const bf16*)d_delta, d_res_in, d_res_out, (const bf16*)d_w, eps, (bf16*)d_out, H, (const bf16*)d_A_all,
+                  d_slots, n_adapters, r_tot, d_u);
+  count_launch();
+  MLORA_CHECK_LAUNCH("rmsnorm_shrink_kernel");
   return MLORA_OK;
 }
 

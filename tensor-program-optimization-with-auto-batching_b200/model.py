@@ -211,6 +211,7 @@ class Engine:
         f32 = dict(dtype=torch.float32, device=dev)
         qkv_out = (m.Hq + 2 * m.Hkv) * m.D
         self.res = torch.zeros(T, m.H, **f32)
+        self.res2 = torch.zeros(T, m.H, **f32)  # the fused norm + shrink moves the residual between two buffers
         self.xn = torch.zeros(T, m.H, **bf)
         self.qkv = torch.zeros(T, qkv_out, **bf)
         self.attn = torch.zeros(T, m.Hq * m.D, **bf)
@@ -233,6 +234,7 @@ class Engine:
         ops.workspace(need, dev, "linear")
         ops.workspace(lib.mlora_paged_attention_workspace(T, m.Hq, m.D, 16), dev, "attn")
         self._graphs = {}
+        self.fuse_norm_shrink = os.environ.get("MLORA_FUSE_NORM_SHRINK", "1") != "0"
 
     # ------------------------------------------------------------------------------------------
     def _proj(self, x, W, stack, slots, out, flags=0):
@@ -259,9 +261,19 @@ class Engine:
         else:  # hidden states handed in by the caller (the VM's separate "embed" function): bf16 [T,H] -> fp32 residual
             ops.embed(self.iota[:T], hidden, res=res)
         delta = None
+        res_other = self.res2[:T]
         for l, lw in enumerate(m.layers):
-            ops.residual_rmsnorm(delta, res, lw.ln1, m.eps, out=xn)
-            self._proj(xn, lw.w_qkv, lw.lora.get("qkv"), slots, qkv)
+            st = lw.lora.get("qkv")
+            if st is not None and slots is not None and T < 256 and m.H <= 8192 and self.fuse_norm_shrink:
+                # one launch: residual add + RMSNorm + the shrink that reads the normalised rows
+                r_tot = st.r_max * st.n_mod
+                u = self.u.view(-1)[: T * r_tot].view(T, r_tot)
+                ops.residual_rmsnorm_shrink(delta, res, res_other, lw.ln1, m.eps, xn, st, slots, u)
+                res, res_other = res_other, res
+                ops.linear(xn, lw.w_qkv, st, slots, u=u, out=qkv)
+            else:
+                ops.residual_rmsnorm(delta, res, lw.ln1, m.eps, out=xn)
+                self._proj(xn, lw.w_qkv, st, slots, qkv)
             kp, vp = kv.k_pages(l), kv.v_pages(l)
             if not fused_append:
                 ops.kv_append_rope(qkv, kp, vp, kv.block_table, row_slot, row_pos, m.Hq, m.Hkv, m.D, kv.page_size,

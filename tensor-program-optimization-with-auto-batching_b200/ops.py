@@ -199,6 +199,16 @@ def residual_rmsnorm(delta, res, w, eps: float, out=None):
     return out
 
 
+def residual_rmsnorm_shrink(delta, res_in, res_out, w, eps: float, out, stack: LoraStack, slots, u):
+    """Fused residual add + RMSNorm + LoRA shrink of the projection that reads ``out`` (see include/mlora.h)."""
+    _need_cuda(res_in, w)
+    T, H = res_in.shape
+    check(_lib.lib().mlora_residual_rmsnorm_shrink(
+        _ptr(delta), _ptr(res_in), _ptr(res_out), _ptr(w), eps, _ptr(out), T, H, _ptr(stack.A_all), _ptr(slots),
+        stack.A_all.shape[0], stack.r_max * stack.n_mod, _ptr(u), _stream()), "mlora_residual_rmsnorm_shrink")
+    return out
+
+
 def embed(ids, E, res=None, out_bf16=None):
     _need_cuda(ids, E)
     T = ids.numel()

@@ -546,3 +546,36 @@ def test_prefill_size_projection_in_waves(ops, cuda, T, K, N, lora):
     torch.cuda.synchronize()
     assert int(ops.workspace(4, cuda, "linear")[:4].view(torch.int32)) == 0, "a bounded wait expired"
     torch.testing.assert_close(y.float(), want, atol=ATOL, rtol=RTOL)
+
+
+@pytest.mark.parametrize("T,H,r,n_mod", [(1, 4096, 16, 3), (32, 4096, 16, 3), (7, 5120, 64, 1), (40, 256, 8, 3), (3, 8192, 32, 2)])
+def test_fused_rmsnorm_and_shrink(ops, cuda, T, H, r, n_mod):
+    """mlora_residual_rmsnorm_shrink against the two kernels it replaces: new residual, normalised rows and shrink
+    outputs (the shrink reads the bf16-rounded normalised row in both forms, so the results differ only by fp32
+    summation order); the input residual buffer is left untouched."""
+    g = torch.Generator().manual_seed(T + H)
+    n_ad = 5
+    res = torch.randn(T, H, generator=g).to(cuda)
+    delta = torch.randn(T, H, generator=g).bfloat16().to(cuda)
+    w = (1.0 + 0.1 * torch.randn(H, generator=g)).bfloat16().to(cuda)
+    A = (torch.randn(n_ad, n_mod * r, H, generator=g) * 0.05).bfloat16().to(cuda)
+    B = torch.zeros(n_ad, 128 * n_mod, r, dtype=torch.bfloat16, device=cuda)
+    st = ops.LoraStack(A, B, _i32([r] * n_ad, cuda), torch.ones(n_ad, device=cuda), r, n_mod,
+                       tuple(range(0, 128 * n_mod + 1, 128)) if n_mod > 1 else None)
+    slots = torch.randint(-1, n_ad, (T,), generator=g).int().to(cuda)
+    # reference: the two separate kernels
+    res_ref = res.clone()
+    xn_ref = ops.residual_rmsnorm(delta, res_ref, w, 1e-5)
+    u_ref = ops.lora_shrink(xn_ref, st, slots)
+    # fused
+    res_in, res_out = res.clone(), torch.full_like(res, float("nan"))
+    xn = torch.empty(T, H, dtype=torch.bfloat16, device=cuda)
+    u = torch.full((T, n_mod * r), float("nan"), device=cuda)
+    ops.residual_rmsnorm_shrink(delta, res_in, res_out, w, 1e-5, xn, st, slots, u)
+    torch.cuda.synchronize()
+    assert torch.equal(res_in, res)
+    assert torch.equal(res_out, res_ref)
+    assert torch.equal(xn, xn_ref)
+    rows = (slots >= 0).nonzero().flatten()
+    torch.testing.assert_close(u[rows], u_ref[rows], atol=1e-3, rtol=1e-4)
+    assert float(u[(slots < 0).nonzero().flatten()].abs().sum()) == 0.0
