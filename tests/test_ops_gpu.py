@@ -579,3 +579,25 @@ def test_fused_rmsnorm_and_shrink(ops, cuda, T, H, r, n_mod):
     rows = (slots >= 0).nonzero().flatten()
     torch.testing.assert_close(u[rows], u_ref[rows], atol=1e-3, rtol=1e-4)
     assert float(u[(slots < 0).nonzero().flatten()].abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("tp", [1, 2, 8])
+def test_projection_on_13b_tensor_parallel_shapes(ops, cuda, tp):
+    """Llama-2-13B projections (hidden 5120, intermediate 13824) as a rank sees them under tensor parallelism 1/2/8
+    -- row and k-block counts that are not powers of two, e.g. in = 640 or 1728 -- at decode and prefill sizes."""
+    H, I = 5120, 13824
+    shapes = {"qkv": (3 * H // tp, H), "o": (H, H // tp), "gu": (2 * I // tp, H), "down": (H, I // tp)}
+    for name, (out_f, in_f) in shapes.items():
+        g = torch.Generator(device=cuda).manual_seed(out_f + in_f)
+        W = (torch.randn(out_f, in_f, device=cuda, generator=g) * 0.02).bfloat16()
+        Wp = ops.PackedWeight(W)
+        for T in (1, 32, 600):
+            x = torch.randn(T, in_f, device=cuda, generator=g).bfloat16()
+            y = ops.linear(x, Wp, flags=ops.SILU_MUL if name == "gu" else 0).float()
+            ref = x.float() @ W.float().t()
+            if name == "gu":
+                r = ref.view(T, out_f // 16, 2, 8)
+                ref = (torch.nn.functional.silu(r[:, :, 0]) * r[:, :, 1]).reshape(T, out_f // 2)
+            torch.cuda.synchronize()
+            assert int(ops.workspace(4, cuda, "linear")[:4].view(torch.int32)) == 0, "a bounded wait expired"
+            torch.testing.assert_close(y, ref, atol=2e-2 + 1e-2 * float(ref.abs().max()), rtol=0)
