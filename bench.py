@@ -438,7 +438,7 @@ def run_operator_case(ops, synth, dev, torch):
             def body():
                 for W in Ws:
                     if name == "lora":  # mlora_lora_linear: shrink kernel, then projection with the expand fused in
-                        ops.linear(c["x"], W, st, slots, u=u, out=out, fuse_shrink=True)
+                        ops.linear(c["x"], W, st, slots, u=u, out=out, with_shrink=True)
                     else:
                         ops.linear(c["x"], W, out=out)
             body()

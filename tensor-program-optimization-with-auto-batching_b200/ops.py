@@ -146,9 +146,9 @@ class PackedWeight:
 
 
 def linear(x, W, stack: LoraStack = None, slots=None, u=None, flags: int = 0, out=None, use_workspace=True,
-           fuse_shrink=False):
+           with_shrink=False):
     """y = x W^T (+ LoRA expand of ``u``) ; see ``mlora_linear`` in include/mlora.h.
-    ``W`` is a bf16 [out,in] tensor or a :class:`PackedWeight`.  ``fuse_shrink``: ``u`` is scratch and
+    ``W`` is a bf16 [out,in] tensor or a :class:`PackedWeight`.  ``with_shrink``: ``u`` is scratch and
     the shrink is part of the call (``mlora_lora_linear``)."""
     _need_cuda(x, W)
     if x.dtype != torch.bfloat16 or W.dtype != torch.bfloat16:
@@ -164,7 +164,7 @@ def linear(x, W, stack: LoraStack = None, slots=None, u=None, flags: int = 0, ou
         out = torch.empty(T, cols, dtype=torch.float32 if flags & OUT_F32 else torch.bfloat16, device=x.device)
     mod = None
     if stack is not None and u is None:
-        if fuse_shrink:
+        if with_shrink:
             u = torch.empty(T, stack.r_max * stack.n_mod, dtype=torch.float32, device=x.device)
         else:
             u = lora_shrink(x, stack, slots)
@@ -172,7 +172,7 @@ def linear(x, W, stack: LoraStack = None, slots=None, u=None, flags: int = 0, ou
         mod = (C.c_int32 * (stack.n_mod + 1))(*stack.mod_offsets)
     wb = _lib.lib().mlora_linear_workspace(T, K, N) if use_workspace else 0
     ws = workspace(wb, x.device, "linear") if wb else None
-    if stack is not None and fuse_shrink:
+    if stack is not None and with_shrink:
         check(_lib.lib().mlora_lora_linear(
             _ptr(x), x.stride(0), _ptr(W), _ptr(out), out.stride(0), T, K, N, _ptr(stack.A_all), _ptr(u),
             _ptr(stack.B_all), _ptr(stack.ranks), _ptr(stack.scales), _ptr(slots), stack.A_all.shape[0],

@@ -457,7 +457,7 @@ def test_lora_linear_one_call(ops, cuda, T, r, K, N):
     u_want = ops.lora_shrink(x, st, slots)
     for _ in range(3):
         u = torch.full((T, 3 * st.r_max), float("nan"), device=cuda)
-        got = ops.linear(x, Wp, st, slots, u=u, fuse_shrink=True)
+        got = ops.linear(x, Wp, st, slots, u=u, with_shrink=True)
         torch.cuda.synchronize()
         assert int(ops.workspace(4, cuda, "linear")[:4].view(torch.int32)) == 0, "a bounded wait expired"
         rows = (slots >= 0).nonzero().flatten()
@@ -482,7 +482,7 @@ def test_lora_linear_one_call_gate_up(ops, cuda):
     slots = torch.randint(-1, n_ad, (T,), generator=g).int().to(cuda)
     st = ops.LoraStack(A.to(cuda), B.to(cuda), _i32([r] * n_ad, cuda), torch.full((n_ad,), 2.0, device=cuda), r, 2, None)
     want = ops.linear(x, W, st, slots, flags=ops.SILU_MUL)
-    got = ops.linear(x, W, st, slots, flags=ops.SILU_MUL, fuse_shrink=True)
+    got = ops.linear(x, W, st, slots, flags=ops.SILU_MUL, with_shrink=True)
     torch.cuda.synchronize()
     assert int(ops.workspace(4, cuda, "linear")[:4].view(torch.int32)) == 0, "a bounded wait expired"
     torch.testing.assert_close(got.float(), want.float(), atol=ATOL, rtol=RTOL)
