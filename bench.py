@@ -127,7 +127,7 @@ def run_reference(args, rank, world):
         "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def workload_config(n_gpus):
@@ -334,7 +334,7 @@ def run_ours(args, rank, world, local_rank):
         dist.barrier()
         dist.destroy_process_group()
     if line is not None:
-        print(json.dumps(line), flush=True)
+        emit(line)
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one captured launch / its algorithmic bytes
@@ -461,7 +461,7 @@ def run_operator_case(ops, synth, dev, torch):
         rows.append({"T": T, "us_with_lora": res["lora"], "us_base_only": res["base"],
                      "lora_overhead_frac": res["lora"] / res["base"] - 1.0, "algorithmic_bytes": by,
                      "achieved_gbs": by / (res["lora"] * 1e3), "frac_of_peak": by / (res["lora"] * 1e3) / peak})
-    print(json.dumps({"kernel_case": "operator", "peak_gbs": peak, "peak_source": src, "rows": rows}))
+    emit({"kernel_case": "operator", "peak_gbs": peak, "peak_source": src, "rows": rows})
 
 
 def run_kernel_case(which):
@@ -504,8 +504,8 @@ def run_kernel_case(which):
         us = 1e3 * e0.elapsed_time(e1) / 40
         by = 2 * 12288 * 4096 + len(set(slots.tolist())) * 2 * 12288 * RANK + 2 * T * 4096 + 2 * T * 12288 + 4 * T + 4 * T * 3 * RANK
         peak, src = measured_peak()
-        print(json.dumps({"kernel_case": which, "us_per_launch": us, "algorithmic_bytes": by, "achieved_gbs": by / us / 1e3,
-                          "frac_of_peak": by / us / 1e3 / peak, "peak_source": src, "launches": ops.launch_count()}))
+        emit({"kernel_case": which, "us_per_launch": us, "algorithmic_bytes": by, "achieved_gbs": by / us / 1e3,
+                          "frac_of_peak": by / us / 1e3 / peak, "peak_source": src, "launches": ops.launch_count()})
         return
     elif which == "prefill":
         # prefill-size q/k/v projection: 8192 prompt rows (16 requests x 512, one adapter per request), shrink as
@@ -536,10 +536,10 @@ def run_kernel_case(which):
         fl = 2.0 * T * 4096 * 12288
         peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
         tpk = float(peaks.get("bf16_tflops", 1590.0))  # burst figure: the kernel is timed alone
-        print(json.dumps({"kernel_case": which, "T": T, "ms_base": res["base"], "ms_with_lora": res["lora"],
+        emit({"kernel_case": which, "T": T, "ms_base": res["base"], "ms_with_lora": res["lora"],
                           "tflops_base": fl / res["base"] / 1e9, "tflops_with_lora": (fl + 2.0 * T * 48 * (4096 + 4096)) / res["lora"] / 1e9,
                           "peak_tflops": tpk, "frac_base": fl / res["base"] / 1e9 / tpk,
-                          "status": int(ops.workspace(4, dev, "linear")[:4].view(torch.int32)), "launches": ops.launch_count()}))
+                          "status": int(ops.workspace(4, dev, "linear")[:4].view(torch.int32)), "launches": ops.launch_count()})
         return
     else:
         # one layer's attention at context 576: 32 rows x 32 heads, 302 MB of KV
@@ -555,7 +555,20 @@ def run_kernel_case(which):
         for _ in range(4):
             ops.paged_attention(qkv, kp, vp, bt, slot, pos, Hq, Hkv, D, PAGE, 10000.0, True)
     torch.cuda.synchronize()
-    print(json.dumps({"kernel_case": which, "launches": ops.launch_count()}))
+    emit({"kernel_case": which, "launches": ops.launch_count()})
+
+
+_RESULT_FD = None
+
+
+def emit(line: dict):
+    """The result line, on the process's original stdout."""
+    data = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, data)
 
 
 def main():
@@ -575,6 +588,12 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    # stdout carries exactly one line, the JSON: whatever libraries write to file descriptor 1 meanwhile (NCCL prints its
+    # version banner there) goes to stderr
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
     if args.kernel_case:
         run_kernel_case(args.kernel_case)
     elif args.impl == "reference":
