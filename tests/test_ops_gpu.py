@@ -601,3 +601,31 @@ def test_projection_on_13b_tensor_parallel_shapes(ops, cuda, tp):
             torch.cuda.synchronize()
             assert int(ops.workspace(4, cuda, "linear")[:4].view(torch.int32)) == 0, "a bounded wait expired"
             torch.testing.assert_close(y, ref, atol=2e-2 + 1e-2 * float(ref.abs().max()), rtol=0)
+
+
+@pytest.mark.parametrize("T,n_ad,r,K,N", [(128, 128, 64, 512, 640), (32, 32, 64, 1024, 256), (100, 60, 32, 256, 384), (16, 16, 64, 256, 128)])
+def test_every_row_its_own_adapter(ops, cuda, T, n_ad, r, K, N):
+    """More distinct adapters in a token tile than the shared-memory operand cache holds (every request with its own
+    adapter, ranks cycling 8/16/32/64 padded to the pitch): the expand is served in rounds of the cache."""
+    g = torch.Generator().manual_seed(T + n_ad)
+    x = torch.randn(T, K, generator=g).bfloat16()
+    W = (torch.randn(N, K, generator=g) * 0.05).bfloat16()
+    ranks = [min(r, (8, 16, 32, 64)[i % 4]) for i in range(n_ad)]
+    A = (torch.randn(n_ad, r, K, generator=g) * 0.05).bfloat16()
+    B = (torch.randn(n_ad, N, r, generator=g) * 0.05).bfloat16()
+    for i, rk in enumerate(ranks):
+        A[i, rk:] = 0
+        B[i, :, rk:] = 0
+    slots = torch.randperm(n_ad, generator=g)[:T].int() if n_ad >= T else torch.randint(0, n_ad, (T,), generator=g).int()
+    slots[T // 2] = -1
+    st = ops.LoraStack(A.to(cuda), B.to(cuda), _i32(ranks, cuda), torch.full((n_ad,), 0.5, device=cuda), r, 1, (0, N)).pack_b()
+    want = x.float() @ W.float().t()
+    for t in range(T):
+        s = int(slots[t])
+        if s >= 0:
+            want[t] += 0.5 * (B[s].float() @ (A[s].float() @ x[t].float()))
+    for _ in range(2):  # twice: the cache hand-shake counters carry over nothing between launches
+        y = ops.linear(x.to(cuda), ops.PackedWeight(W.to(cuda)), st, slots.to(cuda)).float().cpu()
+        torch.cuda.synchronize()
+        assert int(ops.workspace(4, cuda, "linear")[:4].view(torch.int32)) == 0, "a bounded wait expired"
+        torch.testing.assert_close(y, want, atol=ATOL, rtol=RTOL)
