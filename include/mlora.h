@@ -34,6 +34,11 @@ extern "C" {
 #define MLORA_FORCE_SIMT 4  /* use the CUDA-core warp-per-row kernel whatever the shape */
 #define MLORA_W_PACKED 8    /* d_W is the tiled layout written by mlora_pack_weight */
 #define MLORA_B_PACKED 16   /* d_B_all is the tiled layout written by mlora_pack_lora_b */
+#define MLORA_LORA_PER_ROW 64 /* the batch has many distinct adapters per token tile (e.g. every request its own):
+                               run the base projection, then add the expand with a kernel laid out by (row, output
+                               feature) that streams each row's B_all[slot] up to the adapter's own rank, instead of
+                               one masked tensor-core stage per distinct adapter.  Not with MLORA_SILU_MUL (ignored
+                               there).  bf16 outputs are rounded twice (projection, then sum) */
 #define MLORA_SHARE_LORA_KERNEL 32 /* hint for a call WITHOUT LoRA operands that sits between calls with them
                                (gate/up/down when only q/k/v/o carry adapters): run the kernel variant the LoRA
                                calls use, so one code footprint stays hot in the instruction caches for the whole

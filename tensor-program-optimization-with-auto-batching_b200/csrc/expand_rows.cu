@@ -1,0 +1,100 @@
+// Per-row LoRA expand for batches in which (almost) every row has its own adapter:
+//   y[t, o] += scale[s] * sum_j u[t, m(o)*r_max + j] * B_all[s, o, j],   s = slot[t]
+// The tensor-core projection adds the expand as one masked MMA stage per DISTINCT adapter of a token tile, which
+// is the right shape when a few adapters serve many rows; when 128 rows bring 128 adapters, each stage multiplies
+// a tile that is zero except for one row.  Here the work is laid out by (row, output feature) instead: one thread
+// per output feature reads that feature's B row of the token's adapter -- consecutive threads read consecutive
+// B rows, i.e. the kernel streams B_all[slot] -- up to the adapter's own rank only, and adds the product to the
+// projection's output in place.  Both B layouts are read: row-major [N, out, r_max] and the pre-tiled one of
+// mlora_pack_lora_b (128-row tiles per 64-wide rank slice, 16-byte chunks XOR-swizzled inside a row).
+#include "linear.cuh"
+
+namespace mlora {
+namespace {
+
+constexpr int kExpThreads = 256;
+constexpr int kExpMaxRtot = 1024;
+
+__global__ void __launch_bounds__(kExpThreads) lora_expand_rows_kernel(LinearArgs a, int packed) {
+  __shared__ float su[kExpMaxRtot];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.y;
+  const int o = blockIdx.x * kExpThreads + threadIdx.x;
+  const int slot = a.slots[t];
+  if (slot < 0 || slot >= a.n_adapters) return;  // uniform over the CTA
+  const int r_tot = a.r_max * a.n_mod;
+  for (int i = threadIdx.x; i < r_tot; i += kExpThreads) su[i] = a.u[(size_t)t * r_tot + i];
+  __syncthreads();
+  if (o >= a.out) return;
+  int rank = a.full_rank ? a.r_max : a.ranks[slot];
+  rank = rank < a.r_max ? rank : a.r_max;
+  const float* um = su + module_of(a, o) * a.r_max;
+  const int n_chunks = (rank + 7) / 8;
+  float acc = 0.f;
+  if (!packed) {
+    const bf16* b = a.B_all + ((size_t)slot * a.out + o) * a.r_max;
+    for (int c0 = 0; c0 < n_chunks; c0 += 8) {  // up to 8 x 128-bit loads in flight
+      uint4 v[8];
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+        if (c0 + c < n_chunks) v[c] = ld_stream(b + (c0 + c) * 8);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        if (c0 + c < n_chunks) {
+          float bf[8];
+          unpack8(v[c], bf);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc = fmaf(um[(c0 + c) * 8 + e], bf[e], acc);
+        }
+      }
+    }
+  } else {
+    const int lora_sub = a.r_max < 64 ? a.r_max : 64, n_sub = a.r_max / lora_sub;
+    const int chunks = lora_sub / 8, rb = lora_sub * 2;
+    const int row_tiles = (a.out + 127) / 128, row_tile = o >> 7, r = o & 127;
+    const int sw = rb == 128 ? (r & 7) : rb == 64 ? ((r >> 1) & 3) : ((r >> 2) & 1);
+    const uint4* base = reinterpret_cast<const uint4*>(a.B_all) + ((size_t)slot * row_tiles + row_tile) * n_sub * (128 * chunks) +
+                        (size_t)r * chunks;
+    for (int sb = 0; sb * chunks < n_chunks; ++sb) {
+      uint4 v[8];
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+        if (c < chunks && sb * chunks + c < n_chunks) v[c] = ld_stream(base + (size_t)sb * (128 * chunks) + (c ^ sw));
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        if (c < chunks && sb * chunks + c < n_chunks) {
+          float bf[8];
+          unpack8(v[c], bf);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc = fmaf(um[(sb * chunks + c) * 8 + e], bf[e], acc);
+        }
+      }
+    }
+  }
+  acc *= a.scales[slot];
+  if (a.flags & MLORA_OUT_F32) {
+    float* y = reinterpret_cast<float*>(a.y) + (size_t)t * a.ldy + o;
+    *y += acc;
+  } else {
+    bf16* y = reinterpret_cast<bf16*>(a.y) + (size_t)t * a.ldy + o;
+    *y = __float2bfloat16_rn(__bfloat162float(*y) + acc);
+  }
+}
+
+}  // namespace
+
+bool lora_expand_rows_supported(const LinearArgs& a) {
+  return a.u != nullptr && !(a.flags & MLORA_SILU_MUL) && a.r_max % 8 == 0 && a.r_max * a.n_mod <= kExpMaxRtot &&
+         (!(a.flags & MLORA_B_PACKED) || a.r_max == 16 || a.r_max == 32 || a.r_max == 64 || a.r_max == 128) && a.T <= 65535;
+}
+
+int launch_lora_expand_rows(const LinearArgs& a, cudaStream_t st) {
+  dim3 grid((a.out + kExpThreads - 1) / kExpThreads, a.T);
+  launch_pdl_if(pdl_enabled(), lora_expand_rows_kernel, grid, dim3(kExpThreads), 0, st, a, (a.flags & MLORA_B_PACKED) ? 1 : 0);
+  count_launch();
+  MLORA_CHECK_LAUNCH("lora_expand_rows_kernel");
+  return MLORA_OK;
+}
+
+}  // namespace mlora

@@ -71,6 +71,25 @@ static int linear_impl(const void* d_x, int64_t ldx, const void* d_W, void* d_y,
                                      const_cast<float*>(d_u), stream);
     if (rc != MLORA_OK) return rc;
   }
+  if ((flags & MLORA_LORA_PER_ROW) && d_u && lora_expand_rows_supported(a)) {
+    // many distinct adapters per token tile: base projection first, then the expand laid out by (row, output feature)
+    LinearArgs b = a;
+    b.u = nullptr;
+    b.B_all = nullptr;
+    b.flags &= ~(MLORA_B_PACKED | MLORA_LORA_PER_ROW);
+    int rc;
+    if (flags & MLORA_W_PACKED) {
+      MLORA_REQUIRE(!(flags & MLORA_FORCE_SIMT) && d_work && linear_tc_supported(b),
+                    "linear: a packed weight needs the tensor-core kernel (scratch buffer, 16-byte aligned operands)");
+      rc = launch_linear_tc(b, d_work, work_bytes, st);
+    } else if (!(flags & MLORA_FORCE_SIMT) && d_work && linear_tc_supported(b)) {
+      rc = launch_linear_tc(b, d_work, work_bytes, st);
+    } else {
+      rc = launch_linear_simt(b, st);
+    }
+    if (rc != MLORA_OK) return rc;
+    return launch_lora_expand_rows(a, st);
+  }
   if (flags & MLORA_B_PACKED)
     MLORA_REQUIRE(d_u && !(flags & MLORA_FORCE_SIMT) && d_work, "linear: a packed B_all needs the tensor-core kernel");
   if (flags & (MLORA_W_PACKED | MLORA_B_PACKED)) {

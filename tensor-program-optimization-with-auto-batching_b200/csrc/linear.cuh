@@ -69,6 +69,9 @@ int launch_linear_simt(const LinearArgs& a, cudaStream_t st);
 bool linear_tc_supported(const LinearArgs& a);
 size_t linear_tc_workspace(int T, int in, int out);
 int launch_linear_tc(const LinearArgs& a, void* work, size_t work_bytes, cudaStream_t st);
+// LoRA expand laid out by (row, output feature), added to y in place (batches with many distinct adapters).
+bool lora_expand_rows_supported(const LinearArgs& a);
+int launch_lora_expand_rows(const LinearArgs& a, cudaStream_t st);
 // LoRA shrink as a segmented grouped GEMM on the tensor cores (prefill sizes).
 bool lora_shrink_tc_supported(const void* x, int64_t ldx, const void* A_all, const float* u, int T, int in, int r_tot);
 int launch_lora_shrink_tc(const void* x, int64_t ldx, const void* A_all, const int32_t* slots, int n_adapters, int T,

@@ -28,7 +28,7 @@ import torch
 
 from . import ops
 from .kv_cache import PagedKVCache
-from .ops import LoraStack, OUT_F32, SHARE_LORA_KERNEL, SILU_MUL
+from .ops import LoraStack, LORA_PER_ROW, OUT_F32, SHARE_LORA_KERNEL, SILU_MUL
 
 ATTN_PROJ = ("q_proj", "k_proj", "v_proj", "o_proj")
 MLP_PROJ = ("gate_proj", "up_proj", "down_proj")
@@ -234,16 +234,27 @@ class Engine:
         ops.workspace(need, dev, "linear")
         ops.workspace(lib.mlora_paged_attention_workspace(T, m.Hq, m.D, 16), dev, "attn")
         self._graphs = {}
+        self.n_distinct = 0  # distinct adapters among the rows staged for the next pass (set with self.slots)
         self.fuse_norm_shrink = os.environ.get("MLORA_FUSE_NORM_SHRINK", "1") != "0"
 
     # ------------------------------------------------------------------------------------------
+    def _lora_flags(self, T, stack, flags):
+        """The tensor-core expand holds the operands of a token tile's distinct adapters in a shared-memory cache
+        (16 KB, 64 KB at 128-token tiles); a decode batch that brings more distinct adapters than fit (e.g. every
+        request its own) takes the expand laid out by (row, output feature) instead."""
+        if flags & SILU_MUL or T > 128:
+            return flags
+        bn = 16 if T <= 16 else 32 if T <= 32 else 64 if T <= 64 else 128
+        cap = ((64 if bn == 128 else 16) * 1024) // (bn * stack.r_max * 2)
+        return flags | LORA_PER_ROW if self.n_distinct > max(cap, 1) else flags
+
     def _proj(self, x, W, stack, slots, out, flags=0):
         T = x.shape[0]
         if stack is not None and slots is not None:
             r_tot = stack.r_max * stack.n_mod
             u = self.u.view(-1)[: T * r_tot].view(T, r_tot)
             ops.lora_shrink(x, stack, slots, out=u)
-            return ops.linear(x, W, stack, slots, u=u, flags=flags, out=out)
+            return ops.linear(x, W, stack, slots, u=u, flags=self._lora_flags(T, stack, flags), out=out)
         # a projection without adapters inside a pass that has some: same kernel variant as its neighbours
         return ops.linear(x, W, flags=flags | (SHARE_LORA_KERNEL if slots is not None else 0), out=out)
 
@@ -270,7 +281,7 @@ class Engine:
                 u = self.u.view(-1)[: T * r_tot].view(T, r_tot)
                 ops.residual_rmsnorm_shrink(delta, res, res_other, lw.ln1, m.eps, xn, st, slots, u)
                 res, res_other = res_other, res
-                ops.linear(xn, lw.w_qkv, st, slots, u=u, out=qkv)
+                ops.linear(xn, lw.w_qkv, st, slots, u=u, flags=self._lora_flags(T, st, 0), out=qkv)
             else:
                 ops.residual_rmsnorm(delta, res, lw.ln1, m.eps, out=xn)
                 self._proj(xn, lw.w_qkv, st, slots, qkv)
@@ -341,6 +352,7 @@ class Engine:
             row_slot, row_pos = kv.begin_forward([seq_ids[i] for i, _, _ in chunk], [n for _, _, n in chunk])
             self._stage(self.tokens, toks, torch.int32)
             self._stage(self.slots, slots, torch.int32)
+            self.n_distinct = len({int(s) for s in slots if s >= 0})
             self.row_slot[:T].copy_(row_slot)
             self.row_pos[:T].copy_(row_pos)
             ends, fin, a = [], [], 0
@@ -367,6 +379,7 @@ class Engine:
         row_slot, row_pos = self.kv.begin_forward(seq_ids, [1] * B)
         self._stage(self.tokens, tokens, torch.int32)
         self._stage(self.slots, adapter_slots, torch.int32)
+        self.n_distinct = len({int(s) for s in adapter_slots if s >= 0})
         self.row_slot[:B].copy_(row_slot)
         self.row_pos[:B].copy_(row_pos)
         out = self.forward(B, True, use_lora)
@@ -382,6 +395,7 @@ class Engine:
             kv.reserve(sid, kv.length(sid) + reserve_tokens + 1)
         self._stage(self.row_slot, [kv.slot(s) for s in seq_ids], torch.int32)
         self._stage(self.slots, adapter_slots, torch.int32)
+        self.n_distinct = len({int(s) for s in adapter_slots if s >= 0})
         torch.cuda.synchronize()
         saved = kv.seq_lens.clone()
 

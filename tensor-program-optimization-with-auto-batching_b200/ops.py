@@ -13,7 +13,7 @@ import torch
 from . import _lib
 from ._lib import check
 
-OUT_F32, SILU_MUL, FORCE_SIMT, W_PACKED, B_PACKED, SHARE_LORA_KERNEL = 1, 2, 4, 8, 16, 32
+OUT_F32, SILU_MUL, FORCE_SIMT, W_PACKED, B_PACKED, SHARE_LORA_KERNEL, LORA_PER_ROW = 1, 2, 4, 8, 16, 32, 64
 
 
 def _ptr(t):

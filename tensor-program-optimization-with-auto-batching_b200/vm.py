@@ -162,6 +162,7 @@ class B200VM:
                 else:
                     slots[_tensor(sids, m.device, torch.int64).reshape(-1)] = w
             eng.slots[:T].copy_(slots.repeat_interleave(S) if S > 1 else slots)
+            eng.n_distinct = int(torch.unique(slots[slots >= 0]).numel())
         h2 = h.reshape(T, m.H).contiguous()
         if prefill:
             # the reference keeps only the last token before lm_head (llama_for_causal_lm.py:130-137)

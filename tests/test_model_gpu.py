@@ -203,3 +203,27 @@ def test_prefill_heavy_skewed_adapters_on_all_projections(synth, cuda):
         lg, tok = eng.decode(list(range(n_req)), want_tok[:, step - 1].tolist(), ids)
         _check_logits(lg, want_logits[step])
     assert int(load("ops").workspace(4, cuda, "linear")[:4].view(torch.int32)) == 0
+
+
+def test_every_request_its_own_adapter_takes_the_per_row_expand(synth, cuda):
+    """12 requests, 12 rank-64 adapters: more distinct adapters per decode batch than the tensor-core expand caches,
+    so the engine asks for the expand laid out by (row, output feature); same parity bars against the oracle."""
+    n = 12
+    cfg, w, ads = _tiny(synth, n_adapters=n, ranks=[8, 16, 32, 64])
+    scales = [1.0] * n
+    P = synth.prompts(n, 40, cfg["vocab_size"])
+    ids = list(range(n))
+    oracle = ollama.OracleLlama(cfg, w, ads, scales)
+    want_tok, want_logits = oracle.greedy([list(p) for p in P], ids, 5)
+    pm, kv, eng = _engine(cfg, w, ads, scales, n, 40 + 8, cuda, max_rows=512)
+    for s in range(n):
+        kv.add_sequence(s)
+    lg, tok = eng.prefill(list(range(n)), [list(p) for p in P], ids)
+    _check_logits(lg, want_logits[0])
+    agree = int((tok.cpu() == want_tok[:, 0]).sum())
+    for step in range(1, 5):
+        lg, tok = eng.decode(list(range(n)), want_tok[:, step - 1].tolist(), ids)
+        assert eng._lora_flags(n, pm.layers[0].lora["qkv"], 0) & load("ops").LORA_PER_ROW
+        _check_logits(lg, want_logits[step])
+        agree += int((tok.cpu() == want_tok[:, step]).sum())
+    assert agree >= 0.95 * n * 5

@@ -629,3 +629,35 @@ def test_every_row_its_own_adapter(ops, cuda, T, n_ad, r, K, N):
         torch.cuda.synchronize()
         assert int(ops.workspace(4, cuda, "linear")[:4].view(torch.int32)) == 0, "a bounded wait expired"
         torch.testing.assert_close(y, want, atol=ATOL, rtol=RTOL)
+    # the same through the per-row expand (base projection, then a kernel laid out by (row, output feature)), with
+    # the pre-tiled and the row-major B stack, bf16 and fp32 outputs
+    st_rm = ops.LoraStack(A.to(cuda), B.to(cuda), _i32(ranks, cuda), torch.full((n_ad,), 0.5, device=cuda), r, 1, (0, N))
+    for stack in (st, st_rm):
+        y = ops.linear(x.to(cuda), ops.PackedWeight(W.to(cuda)), stack, slots.to(cuda), flags=ops.LORA_PER_ROW).float().cpu()
+        torch.testing.assert_close(y, want, atol=ATOL, rtol=RTOL)
+    y32 = ops.linear(x.to(cuda), W.to(cuda), st_rm, slots.to(cuda), flags=ops.LORA_PER_ROW | ops.OUT_F32).cpu()
+    torch.testing.assert_close(y32, want, atol=ATOL, rtol=RTOL)
+
+
+def test_per_row_expand_with_fused_modules(ops, cuda):
+    """Per-row expand over a fused q/k/v stack (three modules, each reading its own slice of u), rank pitches 16 and 32."""
+    for r in (16, 32):
+        g = torch.Generator().manual_seed(r)
+        T, K, n_ad, offs = 50, 256, 40, (0, 256, 384, 512)
+        x = torch.randn(T, K, generator=g).bfloat16()
+        W = (torch.randn(512, K, generator=g) * 0.05).bfloat16()
+        A = (torch.randn(n_ad, 3 * r, K, generator=g) * 0.05).bfloat16()
+        B = (torch.randn(n_ad, 512, r, generator=g) * 0.05).bfloat16()
+        slots = torch.randint(-1, n_ad, (T,), generator=g).int()
+        st = _stack(ops, A, B, [r] * n_ad, [1.5] * n_ad, cuda, 3, offs)
+        want = x.float() @ W.float().t()
+        for t in range(T):
+            s = int(slots[t])
+            if s >= 0:
+                for m in range(3):
+                    u = A[s, m * r:(m + 1) * r].float() @ x[t].float()
+                    want[t, offs[m]:offs[m + 1]] += 1.5 * (B[s, offs[m]:offs[m + 1]].float() @ u)
+        y = ops.linear(x.to(cuda), W.to(cuda), st, slots.to(cuda), flags=ops.LORA_PER_ROW).float().cpu()
+        y2 = ops.linear(x.to(cuda), ops.PackedWeight(W.to(cuda)), st.pack_b(), slots.to(cuda), flags=ops.LORA_PER_ROW).float().cpu()
+        torch.testing.assert_close(y, want, atol=ATOL, rtol=RTOL)
+        torch.testing.assert_close(y2, want, atol=ATOL, rtol=RTOL)
