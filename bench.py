@@ -112,6 +112,66 @@ def cpu_reference_step(cfg, synth, steps, warmup):
     return N_REQ / r["full_step_s"], cores, sample, r
 
 
+def run_13b_shape(args):
+    """Side measurement, not the benchmark line: one GPU holding the whole Llama-2-13B shape (tensor parallel size 1)
+    with the adapter mix of the 13B configuration -- 128 requests, 128 adapters whose ranks cycle 8/16/32/64 on
+    q/k/v/o, every request its own adapter -- at a short context (128-token prompts: 128 x 1 K tokens of KV would
+    not leave room beside 26 GB of weights and 27 GB of adapters).  Decode steps in a CUDA graph, CUDA-event timed."""
+    import numpy as np
+    import torch
+
+    ops, synth, model_mod, kv_mod = load("ops"), load("synth"), load("model"), load("kv_cache")
+    load("build").build()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    cfg = synth.llama_config("llama2-13b")
+    L = args.layers or cfg["num_hidden_layers"]
+    cfg = dict(cfg, num_hidden_layers=L)
+    n_req = n_ad = 128
+    prompt_len, steps, warm = 128, max(8, min(args.steps, 32)), 3
+    w = synth.base_weights(cfg, dtype=torch.bfloat16, device=dev)
+    ads = synth.lora_adapters(cfg, n_ad, [8, 16, 32, 64], dtype=torch.bfloat16, device=dev)
+    pm = model_mod.PackedLlama(cfg, w, ads, [2.0] * n_ad, device=dev)
+    del w, ads
+    torch.cuda.empty_cache()
+    max_len = prompt_len + 2 * (steps + warm) + 8
+    kv = kv_mod.PagedKVCache(pm.L, pm.Hkv, pm.D, n_req, n_req * max_len, prompt_len, PAGE, dev, max_seq_len=max_len)
+    eng = model_mod.Engine(pm, kv, max_rows=4096)
+    sids = list(range(n_req))
+    for sid in sids:
+        kv.add_sequence(sid)
+    prompts = [p.tolist() for p in synth.prompts(n_req, prompt_len, cfg["vocab_size"])]
+    slots = [int(i) for i in np.random.default_rng(synth.SEED_IDS).permutation(n_ad)]
+    _, first_tok = eng.prefill(sids, prompts, slots)
+    res = {}
+    for name, use_lora in (("lora", True), ("base", False)):
+        graph = eng.capture_decode(sids, slots, use_lora=use_lora, reserve_tokens=steps + warm + 2)
+        eng.tokens[:n_req].copy_(first_tok)
+        len0, len0_host = kv.seq_lens.clone(), kv._len_host.copy()
+        for _ in range(warm):
+            graph.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        res[name] = e0.elapsed_time(e1) / steps
+        kv.seq_lens.copy_(len0)
+        kv._len_host[:] = len0_host
+    peak, src = measured_peak()
+    wbytes = L * 2 * (4 * 5120 * 5120 + 3 * 5120 * 13824) + 2 * 32000 * 5120
+    kvbytes = n_req * (prompt_len + warm + steps // 2) * 2 * 5120 * 2 * L
+    abytes = sum(L * 2 * r * (3 * 5120 + 3 * 5120 + 5120 + 5120) for r in ([8, 16, 32, 64] * 32))
+    emit({"side_measurement": "llama2-13b shape on ONE GPU (tensor parallel size 1), 128 requests x 128 adapters (ranks 8/16/32/64), "
+                              "128-token prompts", "layers": L, "ms_per_step_with_lora": res["lora"],
+          "ms_per_step_base_only": res["base"], "tokens_per_s": n_req / res["lora"] * 1e3,
+          "lora_overhead_frac": res["lora"] / res["base"] - 1.0,
+          "algorithmic_gb_per_step": (wbytes + kvbytes + abytes) / 1e9,
+          "hbm_frac_of_measured": (wbytes + kvbytes + abytes) / (res["lora"] * 1e6) / peak, "peak_source": src,
+          "status": int(ops.workspace(4, dev, "linear")[:4].view(torch.int32))})
+
+
 def run_reference(args, rank, world):
     if rank != 0:
         return
@@ -584,6 +644,8 @@ def main():
                          "(the number is then not a bench value)")
     ap.add_argument("--kernel-case", default="", choices=["", "linear", "attention", "operator", "prefill"],
                     help="profiling aid: launch one kernel a few times on a small case (> L2, < 1 GB) and exit")
+    ap.add_argument("--workload", default="", choices=["", "13b-shape"],
+                    help="side measurement (own JSON line, not the benchmark's): the 13B shape and adapter mix on one GPU")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -594,7 +656,9 @@ def main():
     sys.stdout.flush()
     _RESULT_FD = os.dup(1)
     os.dup2(2, 1)
-    if args.kernel_case:
+    if args.workload == "13b-shape":
+        run_13b_shape(args)
+    elif args.kernel_case:
         run_kernel_case(args.kernel_case)
     elif args.impl == "reference":
         run_reference(args, rank, world)

@@ -82,7 +82,8 @@ int mlora_bucket_sort(const int32_t* d_tids, const int32_t* d_wids, int32_t n, i
  * GatherBMMLinear.forward (huggingface/custom_peft/lora_gatherbmm_linear_layer.py:16-19).
  *   d_x [T, in] bf16 (row stride ldx elements); d_A_all [N, n_mod*r_max, in] bf16;
  *   d_ranks [N] int32 (rank of each adapter slot, <= r_max; rows of A_all at or beyond the rank
- *   must be zero: both kernels multiply them rather than look the rank up);
+ *   must be zero: the kernels multiply them rather than look the rank up, except that the decode-size
+ *   kernel skips rows beyond the first 16 of a module that lie beyond the adapter's rank);
  *   d_slots [T] int32 (adapter slot of each row; < 0 or >= n_adapters = none -> u row is zero);
  *   d_u [T, n_mod*r_max] float32.  n_mod modules share the input (q,k,v or gate,up).
  * T < 256: one warp per (row, rank index) on CUDA cores.  T >= 256 (prefill) with n_mod*r_max <= 256:
@@ -165,7 +166,8 @@ int mlora_residual_rmsnorm(const void* d_delta, float* d_res, const void* d_w, f
  * "input_layernorm -> q/k/v adapters" (llama_for_causal_lm.py:76-84 followed by compile_tvm.py:126-134).
  * Several CTAs share a row and re-read the old residual while one of them writes the new one, so the
  * residual moves from d_res_in to a DIFFERENT buffer d_res_out.  H <= 8192; d_A_all [N, r_tot, H] with
- * zero rows beyond each adapter's rank; d_u [T, r_tot] float32. */
+ * zero rows beyond each adapter's rank (all r_tot rows are read and multiplied: for stacks whose adapters are
+ * much narrower than the pitch the two separate calls read less); d_u [T, r_tot] float32. */
 int mlora_residual_rmsnorm_shrink(const void* d_delta, const float* d_res_in, float* d_res_out, const void* d_w,
                                   float eps, void* d_out, int32_t T, int32_t H, const void* d_A_all,
                                   const int32_t* d_slots, int32_t n_adapters, int32_t r_tot, float* d_u,

@@ -22,9 +22,12 @@ __global__ void __launch_bounds__(256) lora_shrink_kernel(const bf16* __restrict
   if (j >= r_tot) return;
   const int slot = slots[t];
   float acc = 0.f;
-  // (rows of A at or beyond an adapter's rank are zero by contract: multiplied, not looked up -- one dependent
-  // global load less in a kernel that is nothing but a chain of round trips)
-  if (slot >= 0 && slot < n_adapters) {
+  // Rows of A at or beyond an adapter's rank are zero by contract.  The first 16 rank rows of a module are
+  // multiplied without looking the rank up (one dependent global load less in a kernel that is nothing but a chain
+  // of round trips: the common rank-16 stacks never pay for it); further rows of wide pitches are skipped when the
+  // adapter's own rank is lower, so a rank-8 adapter in a pitch-64 stack does not stream 56 rows of zeros.
+  const int jm = j % r_max;
+  if (slot >= 0 && slot < n_adapters && (jm < 16 || jm < ranks[slot])) {
     const bf16* a = A_all + ((size_t)slot * r_tot + j) * in;
     const bf16* xr = x + (size_t)t * ldx;
     // 8 chunks of A and of x are requested before the first is used: the dot product is a chain of

@@ -238,6 +238,15 @@ class Engine:
         self.fuse_norm_shrink = os.environ.get("MLORA_FUSE_NORM_SHRINK", "1") != "0"
 
     # ------------------------------------------------------------------------------------------
+    @staticmethod
+    def _full_rank(stack):
+        """Do all adapters of the stack fill its rank pitch?  (Looked up once per stack.)"""
+        v = getattr(stack, "_all_full_rank", None)
+        if v is None:
+            v = bool((stack.ranks == stack.r_max).all().item())
+            stack._all_full_rank = v
+        return v
+
     def _lora_flags(self, T, stack, flags):
         """The tensor-core expand holds the operands of a token tile's distinct adapters in a shared-memory cache
         (16 KB, 64 KB at 128-token tiles); a decode batch that brings more distinct adapters than fit (e.g. every
@@ -275,7 +284,8 @@ class Engine:
         res_other = self.res2[:T]
         for l, lw in enumerate(m.layers):
             st = lw.lora.get("qkv")
-            if st is not None and slots is not None and T < 256 and m.H <= 8192 and self.fuse_norm_shrink:
+            if (st is not None and slots is not None and T < 256 and m.H <= 8192 and self.fuse_norm_shrink
+                    and self._full_rank(st)):  # (the fused kernel reads every rank row of the pitch)
                 # one launch: residual add + RMSNorm + the shrink that reads the normalised rows
                 r_tot = st.r_max * st.n_mod
                 u = self.u.view(-1)[: T * r_tot].view(T, r_tot)
