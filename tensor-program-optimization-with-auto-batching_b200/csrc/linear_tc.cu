@@ -3,23 +3,26 @@
 // is the 128-row M operand, the token rows are the N operand ("swap-AB"), so a 128 x BN fp32
 // accumulator lives in BN TMEM columns and one thread issues all MMAs.
 //
-// Persistent, warp-specialised, stream-K:
+// Persistent and warp-specialised:
 //   * one CTA per SM (grid <= SM count), 224 threads: warp 0 = weight producer, warp 1 = MMA issuer
 //     (one thread each), warps 2..5 = epilogue (one TMEM lane = one output row per thread), warp 6 =
-//     token-tile producer.  Weights stream from HBM through a deep ring (12 x 16 KB) plus an L2
-//     prefetch running further ahead; token tiles come from L2 through their own shallow ring;
-//   * the iteration space (tile, k-block) -- tiles = row tiles x token tiles, k-blocks of 64 -- is
-//     cut into equal contiguous ranges, one per CTA, so every SM streams the same number of bytes
-//     whatever the shape; a range covers a tail of one tile, whole tiles, and a head of another;
+//     token-tile producer and builder of the LoRA operands.  Weights stream from HBM through a ring of
+//     up to 10 x 16 KB stages (one bulk copy per pre-tiled stage); token tiles come from L2 through
+//     their own shallow ring;
+//   * decode sizes (stream-K): the iteration space (tile, k-block) -- tiles = row tiles x token tiles,
+//     k-blocks of 64 -- is cut into equal contiguous ranges, one per CTA, so every SM streams the same
+//     number of bytes whatever the shape; a range covers a tail of one tile, whole tiles, and a head of
+//     another.  Prefill sizes: whole tiles only, dealt in token-tile groups (see wave_tile);
 //   * two TMEM accumulators: the epilogue of one segment overlaps the MMAs of the next, and the
 //     shared-memory ring keeps filling across segment boundaries;
-//   * a tile whose k-blocks are spread over several CTAs is finished by whichever CTA arrives
-//     last on the tile's ticket: every contributor writes its fp32 partial tile to scratch, the last
-//     one sums the partials in CTA order (deterministic) and runs the epilogue (LoRA expand, SiLU*up,
-//     store).  Nobody waits for another CTA.
+//   * a tile whose k-blocks are spread over several CTAs is finished by the CTA that holds its FIRST
+//     k-blocks (it reaches them last, at the end of its range): the other contributors write their fp32
+//     partial tile to scratch and bump the tile's counter; the finisher waits (bounded) for the counter,
+//     sums the partials in CTA order (deterministic) while its own last MMAs still run, and runs the
+//     epilogue (SiLU*up, staging, TMA store).  The tile's LoRA stages run in the finisher as well.
 //
-// Every mbarrier wait is bounded; on expiry the CTA records a code in the status word at the start
-// of the scratch buffer, stops issuing work, and leaves after freeing its TMEM.
+// Every wait is bounded; on expiry the CTA records a code in the status word at the start of the
+// scratch buffer, stops issuing work, and leaves after freeing its TMEM.
 #include <stdlib.h>
 
 #include <atomic>
