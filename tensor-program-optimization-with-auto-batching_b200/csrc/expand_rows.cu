@@ -27,6 +27,11 @@ __global__ void __launch_bounds__(kExpThreads) lora_expand_rows_kernel(LinearArg
   for (int i = threadIdx.x; i < r_tot; i += kExpThreads) su[i] = a.u[(size_t)t * r_tot + i];
   __syncthreads();
   if (o >= a.out) return;
+  // the output element is requested now, with the B row: one round trip for both
+  const bool f32 = (a.flags & MLORA_OUT_F32) != 0;
+  float* y32 = reinterpret_cast<float*>(a.y) + (size_t)t * a.ldy + o;
+  bf16* y16 = reinterpret_cast<bf16*>(a.y) + (size_t)t * a.ldy + o;
+  const float y_old = f32 ? *y32 : __bfloat162float(*y16);
   int rank = a.full_rank ? a.r_max : a.ranks[slot];
   rank = rank < a.r_max ? rank : a.r_max;
   const float* um = su + module_of(a, o) * a.r_max;
@@ -72,14 +77,11 @@ __global__ void __launch_bounds__(kExpThreads) lora_expand_rows_kernel(LinearArg
       }
     }
   }
-  acc *= a.scales[slot];
-  if (a.flags & MLORA_OUT_F32) {
-    float* y = reinterpret_cast<float*>(a.y) + (size_t)t * a.ldy + o;
-    *y += acc;
-  } else {
-    bf16* y = reinterpret_cast<bf16*>(a.y) + (size_t)t * a.ldy + o;
-    *y = __float2bfloat16_rn(__bfloat162float(*y) + acc);
-  }
+  const float y_new = fmaf(acc, a.scales[slot], y_old);
+  if (f32)
+    *y32 = y_new;
+  else
+    *y16 = __float2bfloat16_rn(y_new);
 }
 
 }  // namespace
