@@ -567,6 +567,51 @@ def run_kernel_case(which):
         emit({"kernel_case": which, "us_per_launch": us, "algorithmic_bytes": by, "achieved_gbs": by / us / 1e3,
                           "frac_of_peak": by / us / 1e3 / peak, "peak_source": src, "launches": ops.launch_count()})
         return
+    elif which == "expand":
+        # a 13B-shaped projection (5120 x 5120) over 128 rows that each bring their own adapter (128 adapters, ranks
+        # cycling 8/16/32/64 in a pitch-64 stack): base projection + per-row expand, CUDA-event timed in a graph
+        T, H, n_ad, rp = 128, 5120, 128, 64
+        g = torch.Generator(device=dev).manual_seed(0)
+        x = torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16)
+        Ws = [ops.PackedWeight((torch.randn(H, H, device=dev, generator=g) * 0.02).to(torch.bfloat16)) for _ in range(6)]
+        ranks = [(8, 16, 32, 64)[i % 4] for i in range(n_ad)]
+        A = (torch.randn(n_ad, rp, H, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+        B = (torch.randn(n_ad, H, rp, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+        for i, r in enumerate(ranks):
+            A[i, r:] = 0
+            B[i, :, r:] = 0
+        st = ops.LoraStack(A, B, torch.tensor(ranks, dtype=torch.int32, device=dev), torch.full((n_ad,), 0.5, device=dev),
+                           rp, 1, (0, H)).pack_b()
+        slots = torch.randperm(n_ad, device=dev, generator=g)[:T].to(torch.int32)
+        out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+        u = torch.empty(T, rp, dtype=torch.float32, device=dev)
+        res = {}
+        for name in ("base", "shrink", "per_row", "tensor_core_stages"):
+            def body():
+                for W in Ws:
+                    if name == "base":
+                        ops.linear(x, W, out=out)
+                    elif name == "shrink":
+                        ops.lora_shrink(x, st, slots, out=u)
+                    else:
+                        ops.linear(x, W, st, slots, u=u, out=out, flags=ops.LORA_PER_ROW if name == "per_row" else 0)
+            body()
+            torch.cuda.synchronize()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                body()
+            gr.replay()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(3):
+                gr.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            res[name] = 1e3 * e0.elapsed_time(e1) / (3 * len(Ws))
+        emit({"kernel_case": which, "us": res, "bytes_W": 2 * H * H, "bytes_B_by_rank": sum(2 * H * r for r in ranks),
+              "bytes_B_padded": n_ad * 2 * H * rp, "status": int(ops.workspace(4, dev, "linear")[:4].view(torch.int32)),
+              "launches": ops.launch_count()})
+        return
     elif which == "prefill":
         # prefill-size q/k/v projection: 8192 prompt rows (16 requests x 512, one adapter per request), shrink as
         # a grouped GEMM + projection with the expand as extra MMA stages; CUDA-event TFLOP/s of the pair
@@ -642,7 +687,7 @@ def main():
     ap.add_argument("--skip-prefill", action="store_true",
                     help="profiling aid: fill the KV cache with seeded random values instead of running prefill "
                          "(the number is then not a bench value)")
-    ap.add_argument("--kernel-case", default="", choices=["", "linear", "attention", "operator", "prefill"],
+    ap.add_argument("--kernel-case", default="", choices=["", "linear", "attention", "operator", "prefill", "expand"],
                     help="profiling aid: launch one kernel a few times on a small case (> L2, < 1 GB) and exit")
     ap.add_argument("--workload", default="", choices=["", "13b-shape"],
                     help="side measurement (own JSON line, not the benchmark's): the 13B shape and adapter mix on one GPU")
