@@ -169,7 +169,7 @@ def run_13b_shape(args):
           "lora_overhead_frac": res["lora"] / res["base"] - 1.0,
           "algorithmic_gb_per_step": (wbytes + kvbytes + abytes) / 1e9,
           "hbm_frac_of_measured": (wbytes + kvbytes + abytes) / (res["lora"] * 1e6) / peak, "peak_source": src,
-          "status": int(ops.workspace(4, dev, "linear")[:4].view(torch.int32))})
+          "status": eng.status_word()})
 
 
 def run_reference(args, rank, world):
@@ -305,7 +305,7 @@ def run_ours(args, rank, world, local_rank):
     ms_total = max_over_ranks(ev0.elapsed_time(ev1))
     clocks = sampler.stop() if rank == 0 else None
     ctx_end = PROMPT_LEN + W + K
-    status = int(ops.workspace(4, dev, "linear")[:4].view(torch.int32))
+    status = eng.status_word()
 
     # ---- timed region 2: end to end through the public step call, host buffers ---------------------------
     rewind()
@@ -386,10 +386,17 @@ def run_ours(args, rank, world, local_rank):
             "clocks": clocks, "prefill_seconds_untimed": prefill_s, "tc_status_word": status,
         }
         if world == 1 and not args.no_cpu:
+            # CPU leg (outside every timed region): the oracle as the timed baseline, and as the checker of the
+            # CUDA path at the benchmark's own widths (2-layer truncation, graph replays)
             tps, cores, sample, _ = cpu_reference_step(synth.llama_config("llama2-7b"), synth, 2, 1)
             line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample}
+            del graph, graph_base, eng, kv, pm
+            torch.cuda.empty_cache()
+            from oracle import parity as oparity
+            line["parity"] = oparity.decode_parity_at_benchmark_shape(load, dev)
         else:
             line["cpu_baseline"] = None
+            line["parity"] = None
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()

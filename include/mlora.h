@@ -5,7 +5,9 @@
  * call is asynchronous on `stream` (a cudaStream_t passed as void*), returns
  * 0 on success and a negative MLORA_E* code when the arguments are rejected
  * on the host (mlora_last_error() then holds a message).  bf16 tensors are
- * row-major with 16-byte aligned rows.  The library keeps no global state.
+ * row-major with 16-byte aligned rows.  Process-wide state is limited to: a launch counter, the
+ * thread-local message behind mlora_last_error(), per-device "attribute already set" marks of the
+ * kernels, and the 16 MiB device array of mlora_paged_attention_static (documented there).
  *
  * The citations name the interface of the reference project
  * (llm-db/tensor-program-optimization-with-auto-batching) that each entry
@@ -115,8 +117,14 @@ int mlora_lora_shrink(const void* d_x, int64_t ldx, const void* d_A_all, const i
  *   mlora_linear_workspace(T, in, out) bytes (may be NULL/0: then the CUDA-core kernel runs).  The
  *   buffer must be zero-filled once before its first use (arrival counters; they reset themselves)
  *   and may be shared by calls of any shape on one stream; concurrent calls need separate buffers.
- *   Its first int32 is a status word: non-zero after a kernel gave up a bounded wait (bit 0: TMA
- *   producer, bit 1: MMA issuer, bit 2: epilogue); the output of that call is then undefined. */
+ *   Its first int32 is a status word: non-zero after a kernel gave up a bounded wait -- bit 0 (1) weight
+ *   producer waiting for a free ring slot, 1 (2) MMA issuer waiting for operands, 2 (4) output warps
+ *   waiting for an accumulator, 3 (8) MMA issuer waiting for a free accumulator, 4 (16) token-tile
+ *   producer waiting for a free slot, 5 (32) LoRA operand builder waiting for the operand cache, 6 (64)
+ *   MMA issuer waiting for the operand cache, 7 (128) finishing CTA waiting for the partial sums of a
+ *   split tile.  The output of that call is then undefined, and because late contributors of a split
+ *   tile may still bump its arrival counter afterwards, the whole buffer must be zero-filled again
+ *   before its next use (the word is sticky: the caller clears it). */
 size_t mlora_linear_workspace(int32_t T, int32_t in, int32_t out);
 /* Weight pre-packing (load time).  Rewrites W [out,in] bf16 as tiles [ceil(out/128)][ceil(in/64)] of
  * 128 rows x 64 columns, each tile 16 KB contiguous and already in the 128-byte-swizzled K-major
@@ -227,8 +235,11 @@ int mlora_paged_attention(const void* d_qkv, int64_t ld, void* d_k_pages, void* 
  * library holds that array until the process ends.  The call allocates and frees nothing.
  *  - The first call on each device looks up the array's device address (one cudaGetSymbolAddress, with
  *    that device current) and remembers it; make that first call before any stream capture starts.
- *  - n_splits > 1 whose partials (T * Hq * n_splits * (D+2) * 4 bytes) exceed the array is rejected with
- *    MLORA_ESIZE; n_splits <= 0 picks a split count that fits.
+ *  - Arguments are validated first (MLORA_EINVAL).  n_splits > 1 whose partials (T * Hq * n_splits * (D+2) * 4
+ *    bytes) exceed the array is rejected with MLORA_ESIZE; n_splits <= 0 picks a split count, and every count
+ *    the library picks by itself fits.
+ *  - The array that is used is the one of the CURRENT device (cudaGetDevice) at the time of the call: `stream`
+ *    must belong to that device.
  *  - All calls on a device share the one array, and it keeps whatever the previous call left in it.
  *    Nothing in it needs clearing between calls (every partial is written before it is read), but two
  *    calls that overlap on the GPU (different streams) would overwrite each other: serialise them.

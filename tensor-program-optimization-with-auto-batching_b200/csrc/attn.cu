@@ -83,6 +83,9 @@ __global__ void __launch_bounds__(128) paged_attn_kernel(AttnArgs a) {
   const float qscale = rsqrtf((float)D) * kLog2e;
   const bool last_split = split == a.n_splits - 1;
   const bool has_new = a.fused && last_split;
+  // A position beyond the row's block-table entries (a step issued without reserved pages) is never
+  // dereferenced: the new k/v are not stored and the context is cut at the table's end.
+  const bool can_store = pos >= 0 && pos / PS < a.max_pages;
 
   // ---- prologue: rotate q (and the new k), stage the new k/v -----------------------------------
   if (tid < D / 2) {
@@ -105,7 +108,7 @@ __global__ void __launch_bounds__(128) paged_attn_kernel(AttnArgs a) {
     const bf16 r1 = __float2bfloat16_rn(k1 * cs - k2 * sn), r2 = __float2bfloat16_rn(k2 * cs + k1 * sn);
     sk[i] = __bfloat162float(r1);
     sk[i + D / 2] = __bfloat162float(r2);
-    if (h % rep == 0) {
+    if (h % rep == 0 && can_store) {
       const int page = bt[pos / PS];
       bf16* dst = a.k_pages + (((size_t)page * a.Hkv + kvh) * PS + pos % PS) * D;
       dst[i] = r1;
@@ -115,7 +118,7 @@ __global__ void __launch_bounds__(128) paged_attn_kernel(AttnArgs a) {
   if (has_new && tid < D) {
     const bf16 v = row[(size_t)(a.Hq + a.Hkv + kvh) * D + tid];
     sv[tid] = __bfloat162float(v);
-    if (h % rep == 0) {
+    if (h % rep == 0 && can_store) {
       const int page = bt[pos / PS];
       a.v_pages[(((size_t)page * a.Hkv + kvh) * PS + pos % PS) * D + tid] = v;
     }
@@ -128,7 +131,7 @@ __global__ void __launch_bounds__(128) paged_attn_kernel(AttnArgs a) {
   for (int e = 0; e < 8; ++e) qf[e] = sq[dl * 8 + e];
 
   // tokens read from the pages: [0, n_tok)
-  const int n_tok = a.fused ? pos : pos + 1;
+  const int n_tok = min(max(a.fused ? pos : pos + 1, 0), a.max_pages * PS);
   const int n_pg = (n_tok + PS - 1) / PS;
   const int per = (n_pg + a.n_splits - 1) / a.n_splits;
   const int pg_begin = min(split * per, n_pg), pg_end = min(pg_begin + per, n_pg);
@@ -273,6 +276,7 @@ __global__ void __launch_bounds__(256) kv_append_rope_kernel(bf16* __restrict__ 
   pdl_wait();
   const int t = blockIdx.x;
   const int slot = row_slot[t], pos = row_pos[t];
+  if (pos < 0 || pos / PS >= max_pages) return;  // no block-table entry for this position: nothing is written
   const int page = block_table[(size_t)slot * max_pages + pos / PS];
   bf16* row = qkv + (size_t)t * ld;
   const int half = D / 2;
@@ -434,6 +438,11 @@ extern "C" int mlora_paged_attention_static(const void* d_qkv, int64_t ld, void*
                                             int32_t Hq, int32_t Hkv, int32_t D, int32_t page_size, float rope_theta,
                                             int32_t fused_append, void* d_out, int64_t ld_out, int32_t n_splits,
                                             void* stream) {
+  // argument checks first (a negative size must come back as an invalid argument, not as a size problem)
+  int rc = check_kv_common("paged_attention_static", T, Hq, Hkv, D, page_size);
+  if (rc) return rc;
+  MLORA_REQUIRE(T <= 65535, "paged_attention_static: T=%d exceeds 65535 rows per call", T);
+  MLORA_REQUIRE(n_splits <= 64, "paged_attention_static: n_splits=%d exceeds 64", n_splits);
   if (n_splits > 1) {
     const size_t need = mlora_paged_attention_workspace(T, Hq, D, n_splits);
     if (need > kStaticScratchBytes)
@@ -443,7 +452,7 @@ extern "C" int mlora_paged_attention_static(const void* d_qkv, int64_t ld, void*
                   T, Hq, n_splits, need, kStaticScratchBytes);
   }
   void* scratch = nullptr;
-  int rc = static_scratch_for_current_device(&scratch);
+  rc = static_scratch_for_current_device(&scratch);
   if (rc) return rc;
   // n_splits <= 0: the library picks the split count and lowers it until the partials fit the array
   return mlora_paged_attention(d_qkv, ld, d_k_pages, d_v_pages, d_block_table, max_pages, d_row_slot, d_row_pos, T, Hq,

@@ -84,6 +84,10 @@ class PagedKVCache:
     def length(self, sid):
         return int(self._len_host[self._slot_of[sid]])
 
+    def tokens_reserved(self, sid):
+        """Tokens the pages held by ``sid`` have room for."""
+        return self._n_pages_of[sid] * self.page_size
+
     def reserve(self, sid, n_tokens):
         """Make sure pages exist for ``n_tokens`` total tokens of sequence ``sid``."""
         slot = self._slot_of[sid]

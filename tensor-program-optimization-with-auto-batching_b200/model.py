@@ -231,13 +231,29 @@ class Engine:
         lib = ops._lib.lib()
         need = max(lib.mlora_linear_workspace(T, k, n) for k, n in
                    ((m.H, qkv_out), (m.Hq * m.D, m.H), (m.H, 2 * m.I), (m.I, m.H), (m.H, m.V)))
-        ops.workspace(need, dev, "linear")
-        ops.workspace(lib.mlora_paged_attention_workspace(T, m.Hq, m.D, 16), dev, "attn")
+        # The engine owns its scratch: captured graphs hold these addresses, so the buffers live as long as the
+        # engine and are never shared with (or outgrown by) other callers on the device.
+        self.ws_linear = ops.new_workspace(need, dev)
+        self.ws_attn = ops.new_workspace(lib.mlora_paged_attention_workspace(T, m.Hq, m.D, 16), dev)
         self._graphs = {}
         self.n_distinct = 0  # distinct adapters among the rows staged for the next pass (set with self.slots)
         self.fuse_norm_shrink = os.environ.get("MLORA_FUSE_NORM_SHRINK", "1") != "0"
 
     # ------------------------------------------------------------------------------------------
+    def status_word(self) -> int:
+        """Status word of the projection kernels' scratch (synchronises): non-zero after a bounded wait expired
+        somewhere since the buffer was last cleared; the outputs since then are undefined."""
+        return ops.status_word(self.ws_linear)
+
+    def check_status(self):
+        """Raises if a projection kernel gave up a bounded wait, after re-zeroing the scratch (arrival counters of
+        split tiles may be stale after such a failure) so that the engine stays usable."""
+        st = self.status_word()
+        if st:
+            self.ws_linear.zero_()
+            raise RuntimeError(f"mlora: a projection kernel gave up a bounded wait (status bits {st:#x}); "
+                               "the results of this pass are undefined")
+
     @staticmethod
     def _full_rank(stack):
         """Do all adapters of the stack fill its rank pitch?  (Looked up once per stack.)"""
@@ -263,9 +279,11 @@ class Engine:
             r_tot = stack.r_max * stack.n_mod
             u = self.u.view(-1)[: T * r_tot].view(T, r_tot)
             ops.lora_shrink(x, stack, slots, out=u)
-            return ops.linear(x, W, stack, slots, u=u, flags=self._lora_flags(T, stack, flags), out=out)
+            return ops.linear(x, W, stack, slots, u=u, flags=self._lora_flags(T, stack, flags), out=out,
+                              work=self.ws_linear)
         # a projection without adapters inside a pass that has some: same kernel variant as its neighbours
-        return ops.linear(x, W, flags=flags | (SHARE_LORA_KERNEL if slots is not None else 0), out=out)
+        return ops.linear(x, W, flags=flags | (SHARE_LORA_KERNEL if slots is not None else 0), out=out,
+                          work=self.ws_linear)
 
     def forward(self, T: int, fused_append: bool, use_lora: bool = True, lm_rows=None, n_lm=None, hidden=None):
         """One pass over the T rows staged in self.tokens / self.slots / self.row_slot /
@@ -291,7 +309,7 @@ class Engine:
                 u = self.u.view(-1)[: T * r_tot].view(T, r_tot)
                 ops.residual_rmsnorm_shrink(delta, res, res_other, lw.ln1, m.eps, xn, st, slots, u)
                 res, res_other = res_other, res
-                ops.linear(xn, lw.w_qkv, st, slots, u=u, flags=self._lora_flags(T, st, 0), out=qkv)
+                ops.linear(xn, lw.w_qkv, st, slots, u=u, flags=self._lora_flags(T, st, 0), out=qkv, work=self.ws_linear)
             else:
                 ops.residual_rmsnorm(delta, res, lw.ln1, m.eps, out=xn)
                 self._proj(xn, lw.w_qkv, st, slots, qkv)
@@ -300,7 +318,7 @@ class Engine:
                 ops.kv_append_rope(qkv, kp, vp, kv.block_table, row_slot, row_pos, m.Hq, m.Hkv, m.D, kv.page_size,
                                    m.theta)
             ops.paged_attention(qkv, kp, vp, kv.block_table, row_slot, row_pos, m.Hq, m.Hkv, m.D, kv.page_size,
-                                m.theta, fused_append, out=attn)
+                                m.theta, fused_append, out=attn, work=self.ws_attn)
             self._proj(attn, lw.w_o, lw.lora.get("o"), slots, y)
             if m.tp_size > 1:
                 self.coll.all_reduce_sum(y)  # row-parallel partials (base + LoRA) -> full o_proj output
@@ -315,7 +333,8 @@ class Engine:
             xl = ops.embed(lm_rows[:n_lm], xn, out_bf16=self.xn_last[:n_lm])  # row gather
         else:
             n_lm, xl = T, xn
-        ops.linear(xl, m.lm_head, flags=OUT_F32 | (SHARE_LORA_KERNEL if slots is not None else 0), out=self.logits[:n_lm])
+        ops.linear(xl, m.lm_head, flags=OUT_F32 | (SHARE_LORA_KERNEL if slots is not None else 0), out=self.logits[:n_lm],
+                   work=self.ws_linear)
         ops.argmax(self.logits[:n_lm], out=self.next_tok[:n_lm])
         if m.tp_size > 1:
             # vocabulary-parallel greedy token: every rank offers (its best logit, its global index); the
@@ -381,6 +400,7 @@ class Engine:
                 self._stage(self.last_rows, [T - 1], torch.int32)
                 self.forward(T, False, use_lora, self.last_rows, 1)
             kv.end_forward()
+        self.check_status()  # (synchronises; prefill is not the latency-critical call)
         return out_logits, out_tok
 
     def decode(self, seq_ids, tokens, adapter_slots, use_lora=True):
@@ -432,9 +452,18 @@ class Engine:
 class DecodeGraph:
     def __init__(self, engine, graph, seq_ids, B):
         self.engine, self.graph, self.seq_ids, self.B = engine, graph, seq_ids, B
+        self._headroom = 0  # replays known to be covered by reserved pages (re-counted when it runs out)
 
     def replay(self):
         """One token for every row: consumes engine.tokens[:B], leaves greedy tokens in
-        engine.next_tok[:B] (and, when captured with feed_back, back in engine.tokens)."""
+        engine.next_tok[:B] (and, when captured with feed_back, back in engine.tokens).
+        The step appends one token per sequence through block-table entries that must exist already:
+        pages are reserved here when the host allocator still has some, else the replay is refused."""
+        kv = self.engine.kv
+        if self._headroom <= 0:
+            for sid in self.seq_ids:
+                kv.reserve(sid, kv.length(sid) + 1)  # raises when the pool or the row's table is exhausted
+            self._headroom = min(kv.tokens_reserved(sid) - kv.length(sid) for sid in self.seq_ids)
+        self._headroom -= 1
         self.graph.replay()
         self.engine.kv.note_device_decode(self.seq_ids)

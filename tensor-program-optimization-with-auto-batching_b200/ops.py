@@ -31,17 +31,34 @@ def _need_cuda(*ts):
 
 
 _workspaces = {}
+_retired = []  # outgrown buffers stay alive: a captured CUDA graph may still hold their address
 
 
 def workspace(nbytes: int, device, tag="default"):
-    """A cached scratch buffer per (device, tag), grown on demand.  Zero-filled when created:
-    the split-K arrival counters of ``mlora_linear`` must start at zero (they reset themselves)."""
-    key = (torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device(), tag)
+    """The fallback scratch buffer of calls that bring none: one per (device, current stream, tag), grown
+    on demand, never freed.  Zero-filled when created: the split-K arrival counters of ``mlora_linear``
+    must start at zero (they reset themselves).  Long-lived users (``model.Engine``) own their scratch
+    and pass it with ``work=`` instead."""
+    dev = torch.device(device)
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    key = (idx, torch.cuda.current_stream(idx).cuda_stream, tag)
     buf = _workspaces.get(key)
     if buf is None or buf.numel() < nbytes:
+        if buf is not None:
+            _retired.append(buf)
         buf = torch.zeros(max(int(nbytes), 256), dtype=torch.uint8, device=device)
         _workspaces[key] = buf
     return buf
+
+
+def new_workspace(nbytes: int, device):
+    """A zero-filled scratch buffer owned by the caller (see ``mlora_linear`` for the zero-fill rule)."""
+    return torch.zeros(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+
+
+def status_word(work) -> int:
+    """The status word at the start of a projection scratch buffer (0 = no bounded wait ever expired)."""
+    return int(work[:4].view(torch.int32).item())
 
 
 # ---------------------------------------------------------------- bucketing
@@ -146,10 +163,11 @@ class PackedWeight:
 
 
 def linear(x, W, stack: LoraStack = None, slots=None, u=None, flags: int = 0, out=None, use_workspace=True,
-           with_shrink=False):
+           with_shrink=False, work=None):
     """y = x W^T (+ LoRA expand of ``u``) ; see ``mlora_linear`` in include/mlora.h.
     ``W`` is a bf16 [out,in] tensor or a :class:`PackedWeight`.  ``with_shrink``: ``u`` is scratch and
-    the shrink is part of the call (``mlora_lora_linear``)."""
+    the shrink is part of the call (``mlora_lora_linear``).  ``work``: the caller's own zero-initialised
+    scratch buffer (default: the per-stream fallback buffer)."""
     _need_cuda(x, W)
     if x.dtype != torch.bfloat16 or W.dtype != torch.bfloat16:
         raise ValueError("mlora.linear needs bf16 x and W")
@@ -171,7 +189,12 @@ def linear(x, W, stack: LoraStack = None, slots=None, u=None, flags: int = 0, ou
     if stack is not None and stack.n_mod > 1 and not flags & SILU_MUL:
         mod = (C.c_int32 * (stack.n_mod + 1))(*stack.mod_offsets)
     wb = _lib.lib().mlora_linear_workspace(T, K, N) if use_workspace else 0
-    ws = workspace(wb, x.device, "linear") if wb else None
+    if work is not None and wb:
+        if work.numel() < wb:
+            raise ValueError(f"mlora.linear: scratch of {wb} bytes needed, {work.numel()} given")
+        ws, wb = work, work.numel()
+    else:
+        ws = workspace(wb, x.device, "linear") if wb else None
     if stack is not None and with_shrink:
         check(_lib.lib().mlora_lora_linear(
             _ptr(x), x.stride(0), _ptr(W), _ptr(out), out.stride(0), T, K, N, _ptr(stack.A_all), _ptr(u),
@@ -238,13 +261,16 @@ def kv_append_rope(qkv, k_pages, v_pages, block_table, row_slot, row_pos, Hq, Hk
 
 
 def paged_attention(qkv, k_pages, v_pages, block_table, row_slot, row_pos, Hq, Hkv, D, page_size, theta,
-                    fused_append: bool, out=None, n_splits: int = 0):
+                    fused_append: bool, out=None, n_splits: int = 0, work=None):
     _need_cuda(qkv, k_pages)
     T = qkv.shape[0]
     if out is None:
         out = torch.empty(T, Hq * D, dtype=torch.bfloat16, device=qkv.device)
-    wb = _lib.lib().mlora_paged_attention_workspace(T, Hq, D, n_splits)
-    ws = workspace(wb, qkv.device, "attn") if wb else None
+    if work is not None:
+        ws, wb = work, work.numel()
+    else:
+        wb = _lib.lib().mlora_paged_attention_workspace(T, Hq, D, n_splits)
+        ws = workspace(wb, qkv.device, "attn") if wb else None
     check(_lib.lib().mlora_paged_attention(
         _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
         _ptr(row_slot), _ptr(row_pos), T, Hq, Hkv, D, page_size, theta, int(fused_append), _ptr(out),

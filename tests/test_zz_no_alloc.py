@@ -11,6 +11,7 @@ import pytest
 import torch
 
 from conftest import load
+from oracle import ops as oops
 
 pytestmark = pytest.mark.gpu
 
@@ -31,6 +32,23 @@ def _case(seed, B, Hq, Hkv, D, ps, lens, dev):
     qkv = torch.randn(B, (Hq + 2 * Hkv) * D, generator=g).bfloat16().to(dev)
     i32 = lambda a: torch.as_tensor(np.asarray(a, dtype=np.int32), device=dev)
     return kp, vp, qkv, i32(bt), i32(np.arange(B)), i32(lens), max_pages
+
+
+def _oracle_decode(kp, vp, qkv, bt, lens, Hq, Hkv, D, ps, theta):
+    """What the call must produce, on the CPU: rotate q and the new k, append k/v at position len, attend."""
+    B = len(lens)
+    kp, vp, qkv, bt = kp.cpu().clone(), vp.cpu().clone(), qkv.cpu(), bt.cpu().numpy()
+    pos = torch.tensor(lens)
+    q = qkv[:, : Hq * D].view(B, Hq, D)
+    k = qkv[:, Hq * D:(Hq + Hkv) * D].view(B, Hkv, D)
+    v = qkv[:, (Hq + Hkv) * D:].view(B, Hkv, D)
+    qr = oops.rope_rotate_half(q, pos, theta)
+    kr = oops.rope_rotate_half(k, pos, theta).bfloat16()
+    for b in range(B):
+        page = bt[b, lens[b] // ps]
+        kp[page, :, lens[b] % ps] = kr[b]
+        vp[page, :, lens[b] % ps] = v[b]
+    return oops.paged_attention_decode(qr, kp, vp, bt, np.asarray(lens) + 1).reshape(B, Hq * D)
 
 
 def test_static_scratch_entry_matches_caller_scratch_entry(cuda):
@@ -62,6 +80,32 @@ def test_static_scratch_entry_matches_caller_scratch_entry(cuda):
         assert torch.equal(out_b, out_a)  # same kernels, same order of operations
         assert torch.equal(kp2, kp) and torch.equal(vp2, vp)  # the fused append wrote the same pages
         assert out_a.float().abs().sum() > 0
+        # and both equal the CPU oracle (bf16 result against fp32: the tolerance of the other attention tests)
+        kp0, vp0, _, _, _, _, _ = _case(10 + call, B, Hq, Hkv, D, ps, lens, cuda)
+        want = _oracle_decode(kp0, vp0, qkv, bt, lens, Hq, Hkv, D, ps, theta)
+        torch.testing.assert_close(out_b.float().cpu(), want, atol=2e-2, rtol=1e-2)
+
+    # n_splits = 0, the form an embedder uses: the library picks the split count itself (here 2: 48 rows x 8
+    # heads leave SMs idle unless every row's context is cut in two); its own choices always fit the array
+    # (at most 592 (row, head) pairs x 16 splits x (D+2) floats = 4.9 MB), so nothing is ever refused in this form
+    lens = [int(n) for n in np.random.default_rng(5).integers(200, 700, 48)]
+    B, Hq2 = len(lens), 8
+    kp, vp, qkv, bt, slot, pos, max_pages = _case(77, B, Hq2, Hkv, D, ps, lens, cuda)
+    kp0, vp0 = kp.clone(), vp.clone()
+    out = torch.zeros(B, Hq2 * D, dtype=torch.bfloat16, device=cuda)
+    rc = lib.mlora_paged_attention_static(ptr(qkv), qkv.stride(0), ptr(kp), ptr(vp), ptr(bt), max_pages, ptr(slot),
+                                          ptr(pos), B, Hq2, Hkv, D, ps, theta, 1, ptr(out), out.stride(0), 0, stream)
+    assert rc == 0, lib.mlora_last_error()
+    torch.cuda.synchronize()
+    want = _oracle_decode(kp0, vp0, qkv, bt, lens, Hq2, Hkv, D, ps, theta)
+    torch.testing.assert_close(out.float().cpu(), want, atol=2e-2, rtol=1e-2)
+
+    # invalid arguments are reported as such before any size is computed from them
+    for bad_T, bad_splits in ((-1, 4), (B, 65)):
+        rc = lib.mlora_paged_attention_static(ptr(qkv), qkv.stride(0), ptr(kp), ptr(vp), ptr(bt), max_pages,
+                                              ptr(slot), ptr(pos), bad_T, Hq2, Hkv, D, ps, theta, 1, ptr(out),
+                                              out.stride(0), bad_splits, stream)
+        assert rc == -1, (rc, lib.mlora_last_error())
 
     # a request whose partial results do not fit the built-in array is refused, with the sizes in the message
     rc = lib.mlora_paged_attention_static(ptr(qkv), qkv.stride(0), ptr(kp), ptr(vp), ptr(bt), max_pages, ptr(slot),
