@@ -160,6 +160,50 @@ int mlora_lora_linear(const void* d_x, int64_t ldx, const void* d_W, void* d_y, 
                       int32_t n_adapters, int32_t r_max, int32_t n_mod, const int32_t* h_mod_offsets,
                       int32_t flags, void* d_work, size_t work_bytes, void* stream);
 
+/* ---- a chain of decode-size projections in ONE persistent launch ------------------------------------
+ * Everything between two attention calls of the decoder layer
+ * (tvm/llama_auto_batcher/llama_for_causal_lm.py:71-84; the reference runs a whole step as one VM
+ * function, tvm/llama_auto_batcher/llama_exec_graph.py:126) as up to MLORA_CHAIN_MAX_PHASES phases:
+ *   phase = [res += delta; x = RMSNorm(res) * norm_w]  ->  [u = A_all[slot] . x]  ->  y = x Wp^T (+ expand of u)
+ * where both bracketed row operations are optional.  Phase i+1 reads what phase i wrote (d_x of phase
+ * i+1 = d_y of phase i, or d_delta of phase i+1 = d_y of phase i when it has a norm); the kernel orders
+ * them with grid-wide barriers instead of kernel boundaries and keeps streaming weights across them.
+ * Results are bit-identical to the same sequence of mlora_residual_rmsnorm / mlora_lora_shrink /
+ * mlora_linear calls (same tile split, same reduction orders).
+ *   d_x [T,in] bf16 (row stride ldx; written by the norm when d_res != NULL, then ldx == in, in <= 8192)
+ *   d_Wp: mlora_pack_weight layout.  d_y [T, out or out/2] bf16 (f32 with MLORA_OUT_F32), rows 16-byte multiples
+ *   flags: MLORA_OUT_F32 | MLORA_SILU_MUL only
+ *   d_res fp32 [T,in] in/out or NULL (no norm); d_delta bf16 [T,in] or NULL; d_norm_w bf16 [in]
+ *   d_Bp: mlora_pack_lora_b layout or NULL (no adapters on this phase); then d_A_all [N, n_mod*r_max, in],
+ *   d_u [T, n_mod*r_max] float32 (written by the shrink, read by the expand), mod_offsets as for mlora_linear
+ *   (n_mod <= 4, tile-aligned modules; ignored with MLORA_SILU_MUL, whose stack is the interleaved one)
+ * T <= 32 (decode batches).  d_slots / d_ranks / d_scales as for mlora_linear, shared by all phases.
+ * d_work: the scratch of mlora_linear (largest mlora_linear_workspace of the phases), zero-filled once; the
+ * status word is shared too, with bit 8 (256) = a grid barrier wait expired.  All CTAs of the launch must be
+ * co-resident: nothing else may occupy the device's SMs for the duration (a wait that cannot be satisfied
+ * expires and sets the status word; it does not hang). */
+#define MLORA_CHAIN_MAX_PHASES 6
+typedef struct mlora_chain_phase {
+  const void* d_x;
+  int64_t ldx;
+  const void* d_Wp;
+  void* d_y;
+  int64_t ldy;
+  int32_t in, out, flags;
+  float eps;
+  float* d_res;
+  const void* d_delta;
+  const void* d_norm_w;
+  const void* d_A_all;
+  float* d_u;
+  const void* d_Bp;
+  int32_t r_max, n_mod;
+  int32_t mod_offsets[5];
+} mlora_chain_phase;
+int mlora_decode_chain(const mlora_chain_phase* phases, int32_t n_phases, int32_t T, const int32_t* d_slots,
+                       const int32_t* d_ranks, const float* d_scales, int32_t n_adapters, void* d_work,
+                       size_t work_bytes, void* stream);
+
 /* ---- (b) fused residual add + RMSNorm ----------------------------------------------------------
  *   res[t,:] += delta[t,:] (skipped when d_delta == NULL);  out[t,:] = res * rsqrt(mean(res^2)+eps) * w
  * nn.RMSNorm + the "hidden_states += ..." of LlamaDecoderLayer.forward

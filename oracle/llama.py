@@ -30,8 +30,14 @@ class OracleLlama:
     ``layers.{L}.self_attn.q_proj.lora_A.weight`` [r,in], ``...lora_B.weight``
     [out,r]; scales[i] = alpha/r of adapter i."""
 
-    def __init__(self, cfg, weights, adapters=(), scales=()):
+    def __init__(self, cfg, weights, adapters=(), scales=(), act_dtype=None):
+        """``act_dtype`` (e.g. ``torch.bfloat16``): round every activation the CUDA path stores between two
+        kernels to that type (normalised rows, q/k/v, rotated keys, attention output, o/down outputs, the
+        SiLU product) while all arithmetic stays fp32.  This separates "what bf16 activation storage costs"
+        (fp32 oracle vs this) from "does the CUDA path compute the right thing" (CUDA vs this); the
+        reference itself runs fp16/bf16 activations throughout (``gen_lora.py:28``, ``compile_tvm.py:289``)."""
         self.cfg = cfg
+        self._r = (lambda t: t.to(act_dtype).float()) if act_dtype is not None else (lambda t: t)
         self.w = {k: v.float() for k, v in weights.items()}
         self.adapters = [{k: v.float() for k, v in a.items()} for a in adapters]
         self.scales = list(scales)
@@ -61,12 +67,13 @@ class OracleLlama:
         chunk (prefill: one range of S rows; decode: T ranges of 1 row)."""
         c = self.cfg
         D, Hq, Hkv = c["head_dim"], c["num_attention_heads"], c["num_key_value_heads"]
-        xn = ops.rmsnorm(h, self.w[f"model.layers.{layer}.input_layernorm.weight"], c["rms_norm_eps"])
-        q = self._proj(layer, "q_proj", xn, slots).view(-1, Hq, D)
-        k = self._proj(layer, "k_proj", xn, slots).view(-1, Hkv, D)
-        v = self._proj(layer, "v_proj", xn, slots).view(-1, Hkv, D)
+        r = self._r
+        xn = r(ops.rmsnorm(h, self.w[f"model.layers.{layer}.input_layernorm.weight"], c["rms_norm_eps"]))
+        q = r(self._proj(layer, "q_proj", xn, slots)).view(-1, Hq, D)
+        k = r(self._proj(layer, "k_proj", xn, slots)).view(-1, Hkv, D)
+        v = r(self._proj(layer, "v_proj", xn, slots)).view(-1, Hkv, D)
         q = ops.rope_rotate_half(q, positions, c["rope_theta"])
-        k = ops.rope_rotate_half(k, positions, c["rope_theta"])
+        k = r(ops.rope_rotate_half(k, positions, c["rope_theta"]))
         attn = torch.zeros(h.shape[0], Hq, D)
         for (a, b) in seg:
             sid = int(sids[a])
@@ -86,18 +93,18 @@ class OracleLlama:
             mask = torch.arange(n_all)[None, :] <= qpos
             s = s.masked_fill(~mask[None], float("-inf"))
             attn[a:b] = torch.einsum("hsn,nhd->shd", torch.softmax(s, -1), Vr)
-        h = h + self._proj(layer, "o_proj", attn.reshape(h.shape[0], Hq * D), slots)
-        xn = ops.rmsnorm(h, self.w[f"model.layers.{layer}.post_attention_layernorm.weight"], c["rms_norm_eps"])
+        h = h + r(self._proj(layer, "o_proj", r(attn).reshape(h.shape[0], Hq * D), slots))
+        xn = r(ops.rmsnorm(h, self.w[f"model.layers.{layer}.post_attention_layernorm.weight"], c["rms_norm_eps"]))
         g = self._proj(layer, "gate_proj", xn, slots)
         u = self._proj(layer, "up_proj", xn, slots)
-        h = h + self._proj(layer, "down_proj", ops.silu_mul(g, u), slots)
+        h = h + r(self._proj(layer, "down_proj", r(ops.silu_mul(g, u)), slots))
         return h
 
     def _body(self, tokens, sids, positions, slots, seg):
         h = self.w["model.embed_tokens.weight"][torch.as_tensor(tokens, dtype=torch.long)]
         for layer in range(self.cfg["num_hidden_layers"]):
             h = self._layer(layer, h, sids, positions, slots, seg)
-        return ops.rmsnorm(h, self.w["model.norm.weight"], self.cfg["rms_norm_eps"])
+        return self._r(ops.rmsnorm(h, self.w["model.norm.weight"], self.cfg["rms_norm_eps"]))
 
     # -- the two entry points of the executor (llama_exec_graph.py:58-141) ---
     def prefill(self, sid, tokens, slot):

@@ -13,6 +13,16 @@ LIB_PATH = os.path.join(HERE, "libmlora.so")
 
 _i32, _i64, _f32, _vp, _sz = C.c_int32, C.c_int64, C.c_float, C.c_void_p, C.c_size_t
 
+CHAIN_MAX_PHASES = 6
+
+
+class ChainPhase(C.Structure):
+    """``mlora_chain_phase`` of include/mlora.h."""
+    _fields_ = [("d_x", _vp), ("ldx", _i64), ("d_Wp", _vp), ("d_y", _vp), ("ldy", _i64), ("in_", _i32), ("out", _i32),
+                ("flags", _i32), ("eps", _f32), ("d_res", _vp), ("d_delta", _vp), ("d_norm_w", _vp), ("d_A_all", _vp),
+                ("d_u", _vp), ("d_Bp", _vp), ("r_max", _i32), ("n_mod", _i32), ("mod_offsets", _i32 * 5)]
+
+
 # name -> (restype, argtypes); must list every symbol declared in include/mlora.h
 PROTOTYPES = {
     "mlora_version": (C.c_int, []),
@@ -30,6 +40,7 @@ PROTOTYPES = {
                                C.POINTER(_i32), _i32, _vp, _sz, _vp]),
     "mlora_lora_linear": (C.c_int, [_vp, _i64, _vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32,
                                     _i32, C.POINTER(_i32), _i32, _vp, _sz, _vp]),
+    "mlora_decode_chain": (C.c_int, [C.POINTER(ChainPhase), _i32, _i32, _vp, _vp, _vp, _i32, _vp, _sz, _vp]),
     "mlora_residual_rmsnorm": (C.c_int, [_vp, _vp, _vp, _f32, _vp, _i32, _i32, _vp]),
     "mlora_residual_rmsnorm_shrink": (C.c_int, [_vp, _vp, _vp, _vp, _f32, _vp, _i32, _i32, _vp, _vp, _i32, _i32, _vp, _vp]),
     "mlora_embed": (C.c_int, [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp]),

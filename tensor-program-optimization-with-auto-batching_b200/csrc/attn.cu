@@ -35,11 +35,18 @@ struct AttnArgs {
   float* work;
 };
 
-__device__ __forceinline__ uint4 ld_kv(const void* p) {
+// K/V pages are read once per step: no L1 allocation, and first in line for L2 eviction (`pol`), so that gigabytes
+// of pages per step do not push the activations and the next kernel's instructions out of L2.
+__device__ __forceinline__ uint64_t kv_policy() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ uint4 ld_kv(const void* p, uint64_t pol) {
   uint4 v;
-  asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+  asm volatile("ld.global.L1::no_allocate.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
+               : "l"(p), "l"(pol));
   return v;
 }
 
@@ -140,6 +147,7 @@ __global__ void __launch_bounds__(128) paged_attn_kernel(AttnArgs a) {
 #pragma unroll
   for (int e = 0; e < 8; ++e) acc[e] = 0.f;
 
+  const uint64_t pol = kv_policy();
   for (int pg = pg_begin + warp; pg < pg_end; pg += 4) {
     const int page = bt[pg];
     const size_t base = ((size_t)page * a.Hkv + kvh) * PS * D + (size_t)g * D + dl * 8;
@@ -147,9 +155,9 @@ __global__ void __launch_bounds__(128) paged_attn_kernel(AttnArgs a) {
     const bf16* vp = a.v_pages + base;
     uint4 kr[IT], vr[IT];
 #pragma unroll
-    for (int it = 0; it < IT; ++it) kr[it] = ld_kv(kp + (size_t)it * TPW * D);
+    for (int it = 0; it < IT; ++it) kr[it] = ld_kv(kp + (size_t)it * TPW * D, pol);
 #pragma unroll
-    for (int it = 0; it < IT; ++it) vr[it] = ld_kv(vp + (size_t)it * TPW * D);
+    for (int it = 0; it < IT; ++it) vr[it] = ld_kv(vp + (size_t)it * TPW * D, pol);
     float s[IT];
     float mx = -INFINITY;
 #pragma unroll

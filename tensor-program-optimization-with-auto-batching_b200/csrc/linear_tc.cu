@@ -369,6 +369,10 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
     int it = rg.it0, n = 0, cur_tok_tile = tok_tile0, n_seg = 0;
     bool got_preload = false;
     bool ok = true;
+    // decode sizes read every weight byte once: "evict first", so that the stream does not push token tiles, partial
+    // sums and the kernel's instructions out of L2; prefill sizes re-read weight tiles from L2 and keep the default
+    const bool stream_once = !WAVE || p.wave_gt == 0;
+    const uint64_t pol = l2_policy_evict_first();
     while (it < rg.it1 && ok) {
       const Segment sg = next_segment<WAVE>(p, it, rg.it1);
       if (WAVE && sg.tile < 0) break;
@@ -385,7 +389,9 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
           }
           uint8_t* st = w_ring + s * C::kWBytes;
           mbar_expect_tx(&full_bar[s], C::kWBytes);
-          if (packed)  // one contiguous 16 KB tile, already in the swizzled K-major layout
+          if (packed && stream_once)  // one contiguous 16 KB tile, already in the swizzled K-major layout
+            bulk_load_hint(st, wp + ((size_t)row_tile * p.k_blocks + kb) * C::kWBytes, C::kWBytes, &full_bar[s], pol);
+          else if (packed)
             bulk_load(st, wp + ((size_t)row_tile * p.k_blocks + kb) * C::kWBytes, C::kWBytes, &full_bar[s]);
           else
             tma_load_2d(st, &map_w, kb * BK, row_tile * BM, &full_bar[s]);
@@ -654,23 +660,41 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
           ok = false;
         }
         tc_fence_after();
-        for (int l = 0; l < n_w && ok; ++l, ++w_i, ++x_i) {
-          const int s = w_i % C::kWStages, xs = x_i % C::kXStages;
-          if (!mbar_wait(&full_bar[s], (w_i / C::kWStages) & 1, &s_abort) ||
-              !mbar_wait(&xfull_bar[xs], (x_i / C::kXStages) & 1, &s_abort)) {
-            s_abort = 1;
-            atomicOr(p.status, 2);
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          const uint64_t adesc = make_smem_desc(smem_u32(w_ring + s * C::kWBytes));
-          const uint64_t bdesc = make_smem_desc(smem_u32(x_ring + xs * C::kXBytes));
+        {
+          // The stream's inner loop, one thread: ring positions, parities, barrier addresses and descriptors are
+          // kept in registers and advanced by additions (no division, no address conversion per stage).
+          int ws = w_i % C::kWStages, xs = x_i % C::kXStages;
+          uint32_t wpar = (w_i / C::kWStages) & 1, xpar = (x_i / C::kXStages) & 1;
+          const uint32_t full0 = smem_u32(full_bar), empty0 = smem_u32(empty_bar);
+          const uint32_t xfull0 = smem_u32(xfull_bar), xempty0 = smem_u32(xempty_bar);
+          const uint64_t adesc0 = make_smem_desc(smem_u32(w_ring)), bdesc0 = make_smem_desc(smem_u32(x_ring));
+          for (int l = 0; l < n_w && ok; ++l) {
+            if (!mbar_wait_a(full0 + 8 * ws, wpar, &s_abort) || !mbar_wait_a(xfull0 + 8 * xs, xpar, &s_abort)) {
+              s_abort = 1;
+              atomicOr(p.status, 2);
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const uint64_t adesc = adesc0 + (uint64_t)(ws * (C::kWBytes >> 4));  // start-address field, 16-byte units
+            const uint64_t bdesc = bdesc0 + (uint64_t)(xs * (C::kXBytes >> 4));
+            umma_bf16(d_tmem, adesc, bdesc, idesc, l > 0 ? 1u : 0u);
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k)  // +16 elements (32 bytes) along K = +2 in the address field
-            umma_bf16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (l > 0 || k > 0) ? 1u : 0u);
-          umma_commit(&empty_bar[s]);  // both stages are free once these MMAs have read them
-          umma_commit(&xempty_bar[xs]);
+            for (int k = 1; k < BK / 16; ++k)  // +16 elements (32 bytes) along K = +2 in the address field
+              umma_bf16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, 1u);
+            umma_commit_a(empty0 + 8 * ws);  // both stages are free once these MMAs have read them
+            umma_commit_a(xempty0 + 8 * xs);
+            if (++ws == C::kWStages) {
+              ws = 0;
+              wpar ^= 1;
+            }
+            if (++xs == C::kXStages) {
+              xs = 0;
+              xpar ^= 1;
+            }
+            ++w_i;
+            ++x_i;
+          }
         }
         if (cached && new_build && ok) {
           // every MMA that read the previous cache contents has been issued: let the builder overwrite

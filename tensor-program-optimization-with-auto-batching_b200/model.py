@@ -238,6 +238,9 @@ class Engine:
         self._graphs = {}
         self.n_distinct = 0  # distinct adapters among the rows staged for the next pass (set with self.slots)
         self.fuse_norm_shrink = os.environ.get("MLORA_FUSE_NORM_SHRINK", "1") != "0"
+        # decode-size passes can run everything between two attention calls as one persistent launch
+        # (mlora_decode_chain); measured slower than the separate launches on the benchmark's step, so off unless asked for
+        self.use_chain = os.environ.get("MLORA_CHAIN", "0") == "1"
 
     # ------------------------------------------------------------------------------------------
     def status_word(self) -> int:
@@ -285,6 +288,65 @@ class Engine:
         return ops.linear(x, W, flags=flags | (SHARE_LORA_KERNEL if slots is not None else 0), out=out,
                           work=self.ws_linear)
 
+    # ------------------------------------------------------------------------------------------
+    def _chain_plan(self, T, slots):
+        """The decode pass as chained launches: [norm + q/k/v of layer 0], then per layer one chain
+        [o, norm + gate|up, down, norm + q/k/v of the next layer (or the final norm + lm_head)] after its
+        attention call.  None when some phase does not fit ``mlora_decode_chain``."""
+        m = self.m
+        if not (self.use_chain and m.pack and m.tp_size == 1 and 0 < T <= 32):
+            return None
+        res, xn, qkv, attn, y, act = self.res[:T], self.xn[:T], self.qkv[:T], self.attn[:T], self.y[:T], self.act[:T]
+
+        def step(x, W, out, stack, flags=0, norm_w=None, delta=None):
+            st = ops.ChainStep(x=x, W=W, y=out, flags=flags)
+            if norm_w is not None:
+                st.res, st.delta, st.norm_w, st.eps = res, delta, norm_w, m.eps
+            if stack is not None and slots is not None:
+                if self._lora_flags(T, stack, flags) & LORA_PER_ROW:
+                    return None
+                r_tot = stack.r_max * stack.n_mod
+                st.stack, st.u = stack, self.u.view(-1)[: T * r_tot].view(T, r_tot)
+            return st
+
+        chains = []
+        lw0 = m.layers[0]
+        chains.append([step(xn, lw0.w_qkv, qkv, lw0.lora.get("qkv"), norm_w=lw0.ln1, delta=None)])
+        for l, lw in enumerate(m.layers):
+            ch = [step(attn, lw.w_o, y, lw.lora.get("o")),
+                  step(xn, lw.w_gu, act, lw.lora.get("gu"), flags=SILU_MUL, norm_w=lw.ln2, delta=y),
+                  step(act, lw.w_down, y, lw.lora.get("down"))]
+            if l + 1 < len(m.layers):
+                nx = m.layers[l + 1]
+                ch.append(step(xn, nx.w_qkv, qkv, nx.lora.get("qkv"), norm_w=nx.ln1, delta=y))
+            else:
+                ch.append(step(xn, m.lm_head, self.logits[:T], None, flags=OUT_F32, norm_w=m.norm, delta=y))
+            chains.append(ch)
+        for ch in chains:
+            if any(s is None for s in ch) or not ops.chain_supported(T, ch):
+                return None
+        # every u view shares one buffer: the q/k/v, o, gate|up and down shrinks of a chain run one after the other
+        return chains
+
+    def _forward_chained(self, T, chains, slots, hidden):
+        m, kv = self.m, self.kv
+        res, qkv, attn = self.res[:T], self.qkv[:T], self.attn[:T]
+        row_slot, row_pos = self.row_slot[:T], self.row_pos[:T]
+        if hidden is None:
+            ops.embed(self.tokens[:T], m.embed, res=res)
+        else:
+            ops.embed(self.iota[:T], hidden, res=res)
+        ranks = m.ranks if m.n_adapters else None
+        scales = m.scales if m.n_adapters else None
+        run = lambda ch: ops.decode_chain(ch, slots, ranks, scales, m.n_adapters, self.ws_linear)
+        run(chains[0])
+        for l in range(len(m.layers)):
+            ops.paged_attention(qkv, kv.k_pages(l), kv.v_pages(l), kv.block_table, row_slot, row_pos, m.Hq, m.Hkv, m.D,
+                                kv.page_size, m.theta, True, out=attn, work=self.ws_attn)
+            run(chains[l + 1])
+        ops.argmax(self.logits[:T], out=self.next_tok[:T])
+        return self.logits[:T], self.next_tok[:T]
+
     def forward(self, T: int, fused_append: bool, use_lora: bool = True, lm_rows=None, n_lm=None, hidden=None):
         """One pass over the T rows staged in self.tokens / self.slots / self.row_slot /
         self.row_pos.  Logits (fp32) land in self.logits[:n_lm], greedy tokens in self.next_tok.
@@ -292,6 +354,10 @@ class Engine:
         each sequence); None = every row.  ``hidden`` (bf16 [T,H]) replaces the embedding lookup."""
         m, kv = self.m, self.kv
         tok, slots = self.tokens[:T], (self.slots[:T] if (use_lora and m.n_adapters) else None)
+        if fused_append and lm_rows is None:
+            chains = self._chain_plan(T, slots)
+            if chains is not None:
+                return self._forward_chained(T, chains, slots, hidden)
         row_slot, row_pos = self.row_slot[:T], self.row_pos[:T]
         res, xn, qkv, attn, y, act = self.res[:T], self.xn[:T], self.qkv[:T], self.attn[:T], self.y[:T], self.act[:T]
         if hidden is None:

@@ -211,6 +211,73 @@ def linear(x, W, stack: LoraStack = None, slots=None, u=None, flags: int = 0, ou
     return out
 
 
+# ---------------------------------------------------------------- chained decode projections
+@dataclass
+class ChainStep:
+    """One phase of :func:`decode_chain`: optional residual add + RMSNorm writing ``x``, optional LoRA shrink
+    of ``x`` into ``u``, then ``y = x W^T`` (+ expand).  ``W`` must be a :class:`PackedWeight`, ``stack`` a
+    :class:`LoraStack` with a packed B."""
+    x: torch.Tensor
+    W: "PackedWeight"
+    y: torch.Tensor
+    flags: int = 0
+    res: torch.Tensor = None      # fp32 [T,in]: res += delta; x = RMSNorm(res) * norm_w
+    delta: torch.Tensor = None
+    norm_w: torch.Tensor = None
+    eps: float = 0.0
+    stack: "LoraStack" = None
+    u: torch.Tensor = None
+
+
+def chain_supported(T: int, steps) -> bool:
+    """Can these phases run as one ``mlora_decode_chain`` launch?  (decode-size batch, packed operands, tensor-core
+    expand, norm inputs up to 8192 wide)"""
+    if not (0 < T <= 32 and 1 <= len(steps) <= _lib.CHAIN_MAX_PHASES):
+        return False
+    for st in steps:
+        if not isinstance(st.W, PackedWeight) or st.x.stride(0) % 8 or st.W.shape[1] % 8:
+            return False
+        if st.res is not None and (st.W.shape[1] > 8192 or st.x.stride(0) != st.W.shape[1]):
+            return False
+        if st.stack is not None:
+            k = st.stack
+            pitch = 2 * k.r_max if st.flags & SILU_MUL else k.r_max
+            if not k.b_packed or pitch not in (16, 32, 64, 128) or k.n_mod > 4:
+                return False
+            if not st.flags & SILU_MUL and k.n_mod > 1 and any(o % 128 for o in k.mod_offsets[1:-1]):
+                return False
+    return True
+
+
+def decode_chain(steps, slots, ranks, scales, n_adapters: int, work):
+    """Up to six dependent projections (with the row operations between them) in one persistent launch;
+    see ``mlora_decode_chain`` in include/mlora.h.  ``work``: zero-initialised scratch as for :func:`linear`."""
+    n = len(steps)
+    arr = (_lib.ChainPhase * n)()
+    T = steps[0].x.shape[0]
+    for i, st in enumerate(steps):
+        _need_cuda(st.x, st.y)
+        ph = arr[i]
+        ph.d_x, ph.ldx, ph.d_Wp = st.x.data_ptr(), st.x.stride(0), st.W.data_ptr()
+        ph.d_y, ph.ldy = st.y.data_ptr(), st.y.stride(0)
+        ph.in_, ph.out, ph.flags, ph.eps = st.W.shape[1], st.W.shape[0], st.flags, st.eps
+        ph.d_res = st.res.data_ptr() if st.res is not None else None
+        ph.d_delta = st.delta.data_ptr() if st.delta is not None else None
+        ph.d_norm_w = st.norm_w.data_ptr() if st.norm_w is not None else None
+        if st.stack is not None:
+            k = st.stack
+            ph.d_A_all, ph.d_u, ph.d_Bp = k.A_all.data_ptr(), st.u.data_ptr(), k.B_all.data_ptr()
+            ph.r_max, ph.n_mod = k.r_max, k.n_mod
+            if k.n_mod > 1 and k.mod_offsets is not None:
+                for m, o in enumerate(k.mod_offsets):
+                    ph.mod_offsets[m] = o
+        else:
+            ph.d_A_all = ph.d_u = ph.d_Bp = None
+            ph.r_max, ph.n_mod = 0, 1
+    check(_lib.lib().mlora_decode_chain(arr, n, T, _ptr(slots), _ptr(ranks), _ptr(scales), n_adapters, _ptr(work),
+                                        work.numel(), _stream()), "mlora_decode_chain")
+
+
 # ---------------------------------------------------------------- row ops
 def residual_rmsnorm(delta, res, w, eps: float, out=None):
     _need_cuda(res, w)
