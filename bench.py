@@ -172,6 +172,143 @@ def run_13b_shape(args):
           "status": eng.status_word()})
 
 
+def run_13b_tp(args, rank, world, local_rank):
+    """The tensor-parallel configuration: Llama-2-13B shape, 128 requests, prompt lengths U[128,1024], 128 adapters
+    with ranks cycling 8/16/32/64 on q/k/v/o, paged KV (block 16), tensor parallel size = number of ranks
+    (column-parallel q/k/v/gate/up, row-parallel o/down + one NCCL all-reduce each, vocabulary-parallel lm_head).
+    One JSON line (its own, not the benchmark's): tokens/s over K CUDA-graph decode steps, per-rank algorithmic
+    bytes and HBM fraction, and the CUDA-event time of the step's all-reduces replayed alone."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    synth, model_mod, kv_mod, ops, sharding = (load(m) for m in ("synth", "model", "kv_cache", "ops", "sharding"))
+    load("build").build()
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    coll = sharding.DistCollective() if world > 1 else None
+    cfg = synth.llama_config("llama2-13b")
+    L = args.layers or cfg["num_hidden_layers"]
+    cfg = dict(cfg, num_hidden_layers=L)
+    n_req = n_ad = 128
+    K, W = max(4, min(args.steps, 64)), max(3, args.warmup)
+    ranks = [8, 16, 32, 64]
+    w = synth.base_weights(cfg, dtype=torch.bfloat16, device=dev)
+    ads = synth.lora_adapters(cfg, n_ad, ranks, dtype=torch.bfloat16, device=dev)
+    pm = model_mod.PackedLlama(cfg, w, ads, [2.0] * n_ad, device=dev, tp_rank=rank, tp_size=world)
+    del w, ads
+    torch.cuda.empty_cache()
+    lens = [int(x) for x in synth.prompt_lengths(n_req, 128, 1024)]
+    total_steps = 2 * (K + W) + 8
+    max_len = max(lens) + total_steps + 1
+    kv = kv_mod.PagedKVCache(pm.L, pm.Hkv, pm.D, n_req, sum(lens) + n_req * (total_steps + 1), 1024, PAGE, dev,
+                             max_seq_len=max_len)
+    eng = model_mod.Engine(pm, kv, max_rows=4096, collective=coll)
+    sids = list(range(n_req))
+    for sid in sids:
+        kv.add_sequence(sid)
+    rng = np.random.default_rng(synth.SEED_TOKENS)
+    prompts = [rng.integers(0, cfg["vocab_size"], n).tolist() for n in lens]
+    slots = [int(i) for i in np.random.default_rng(synth.SEED_IDS).permutation(n_ad)]  # every request its own adapter
+    t0 = time.perf_counter()
+    _, first_tok = eng.prefill(sids, prompts, slots)
+    torch.cuda.synchronize()
+    prefill_s = time.perf_counter() - t0
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    graph = eng.capture_decode(sids, slots, reserve_tokens=total_steps)
+    eng.tokens[:n_req].copy_(first_tok)
+    for _ in range(W):
+        graph.replay()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(K):
+        graph.replay()
+    e1.record()
+    barrier()
+    ms_step = max_over_ranks(e0.elapsed_time(e1)) / K
+    clocks = sampler.stop() if rank == 0 else None
+    status = eng.status_word()
+
+    # the exchange steps of one decode step alone: 2 all-reduces of [128, 5120] bf16 per layer + the token all-gather
+    ms_coll = 0.0
+    if world > 1:
+        y = eng.y[:n_req]
+        pair = torch.zeros(n_req, 2, device=dev)
+
+        def exchanges():
+            for _ in range(2 * pm.L):
+                coll.all_reduce_sum(y)
+            coll.all_gather(pair)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            exchanges()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            exchanges()
+        for _ in range(3):
+            g.replay()
+        barrier()
+        e0.record()
+        for _ in range(10):
+            g.replay()
+        e1.record()
+        barrier()
+        ms_coll = max_over_ranks(e0.elapsed_time(e1)) / 10
+
+    peak, src = measured_peak()
+    H, I, V = 5120, 13824, 32000
+    ctx_mean = float(np.mean(lens)) + W + (K - 1) / 2.0
+    wbytes = (L * 2 * (4 * H * H + 3 * H * I) + 2 * V * H) / world + (2 * L + 1) * 2 * H
+    # adapter bytes a step reads, by rank of the adapter (A and B of q/k/v/o; the sharded halves split by `world`)
+    r_each = [ranks[i % 4] for i in range(n_ad)]
+    abytes = sum(L * 2 * r * ((3 * H + 3 * H / world) + (H / world + H)) for r in r_each)
+    kvbytes = n_req * (ctx_mean + 1) * 2 * (H / world) * 2 * L
+    per_rank = wbytes + abytes + kvbytes
+    if rank == 0:
+        emit({"workload": "llama2-13b shape, tensor parallel", "metric": "multi-LoRA decode tokens/s (Llama-13B shape, "
+              "128 req/128 adapters, tensor parallel)", "value": n_req / ms_step * 1e3, "unit": "tokens/s",
+              "n_gpus": world, "tp_size": world, "layers": L, "steps": K, "warmup": W, "ms_per_step": ms_step,
+              "scaling": "strong", "dtype": "bf16", "data": "synthetic",
+              "config": {"requests": n_req, "adapters": n_ad, "adapter_ranks": ranks, "prompt_lens": "U[128,1024] seed 4",
+                         "mean_ctx": ctx_mean, "parallelism": f"tp{world} (Megatron column/row + NCCL all-reduce)"},
+              "per_rank": {"algorithmic_bytes": per_rank, "achieved_gbs": per_rank / (ms_step * 1e6),
+                           "hbm_frac": per_rank / (ms_step * 1e6) / peak, "peak_gbs": peak, "peak_source": src},
+              "collectives": {"all_reduces_per_step": 2 * L, "bytes_each": n_req * H * 2,
+                              "ms_alone_per_step": ms_coll, "share_of_step": ms_coll / ms_step if ms_step else None,
+                              "impl": "NCCL via torch.distributed, captured in the step's CUDA graph"},
+              "clocks": clocks, "prefill_seconds_untimed": prefill_s, "tc_status_word": status})
+    if world > 1:
+        # The step's CUDA graph holds NCCL kernels: tearing the process group down while such graphs exist was seen
+        # to block forever, so the ranks meet once more and then leave without the orderly teardown.
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
+
+
 def run_reference(args, rank, world):
     if rank != 0:
         return
@@ -364,6 +501,12 @@ def run_ours(args, rank, world, local_rank):
     value = tokens_total / (ms_total / 1e3)
     e2e_value = tokens_total / (ms_e2e / 1e3)
 
+    # ---- the operator micro-benchmark (T = 1, 8, 32, 128), outside every timed region ---------------------------
+    op_rows = None
+    if rank == 0 and world == 1 and not args.no_operator:
+        torch.cuda.synchronize()
+        op_rows = operator_rows(ops, synth, dev, torch)
+
     line = None
     if rank == 0:
         line = {
@@ -373,8 +516,8 @@ def run_ours(args, rank, world, local_rank):
                                                                   ctx_start=PROMPT_LEN + W, ctx_end=ctx_end),
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B,
                     "ms_per_step": ms_e2e / K,
-                    "call": "Engine decode step: pinned int32 token ids -> device, CUDA-graph step (bucketing "
-                            "state, 32 layers, lm_head, on-device argmax), int32 next tokens -> pinned host"},
+                    "call": "Engine decode step: pinned int32 token ids -> device, CUDA-graph step (device-side position "
+                            "bookkeeping, 32 layers, lm_head, on-device argmax), int32 next tokens -> pinned host"},
             "gpu_launches": launches_per_step * K, "launches_per_step": launches_per_step,
             "roofline": roof["linear"], "roofline_attention": roof["attention"],
             "step_hbm": {"algorithmic_bytes": step_bytes, "achieved_gbs": step_bytes / (ms_step * 1e6),
@@ -384,6 +527,7 @@ def run_ours(args, rank, world, local_rank):
             "lora_overhead": {"base_only_ms_per_step": ms_base, "with_lora_ms_per_step": ms_step,
                               "overhead_frac": ms_step / ms_base - 1.0},
             "clocks": clocks, "prefill_seconds_untimed": prefill_s, "tc_status_word": status,
+            "operator_microbench": op_rows,
         }
         if world == 1 and not args.no_cpu:
             # CPU leg (outside every timed region): the oracle as the timed baseline, and as the checker of the
@@ -404,10 +548,19 @@ def run_ours(args, rank, world, local_rank):
         emit(line)
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one captured launch / its algorithmic bytes
-NCU_TRAFFIC_RATIO = {"linear": (107.35 + 4.36) / 108.0, "attention": (302.82 + 3.75) / 303.3}
-NCU_TRAFFIC_NOTE = {"linear": "profiles/linear_tc_kernel_qkv_T32.md (q/k/v launch: 111.7 MB of DRAM traffic for 108.0 MB algorithmic)",
-                    "attention": "profiles/paged_attn_kernel_ctx576.md"}
+def ncu_traffic():
+    """DRAM read + write bytes of one ncu-captured launch of each hot kernel next to that launch's algorithmic
+    bytes, from profiles/ncu_traffic.txt (lines: kernel  dram_read_MB  dram_write_MB  algorithmic_MB  summary)."""
+    out = {}
+    path = os.path.join(ROOT, "profiles", "ncu_traffic.txt")
+    if os.path.exists(path):
+        with open(path) as f:
+            for ln in f:
+                parts = ln.split()
+                if len(parts) >= 5 and not ln.startswith("#"):
+                    rd, wr, alg = (float(x) for x in parts[1:4])
+                    out[parts[0]] = ((rd + wr) / alg, f"profiles/{parts[4]} ({rd + wr:.1f} MB of DRAM traffic for {alg:.1f} MB algorithmic)")
+    return out
 
 
 def kernel_rooflines(eng, pm, kv, B, slots, ops, torch, ctx, n_uniq, peak, reps=5):
@@ -437,23 +590,24 @@ def kernel_rooflines(eng, pm, kv, B, slots, ops, torch, ctx, n_uniq, peak, reps=
                                          (lw.w_gu, "gu", x, act, ops.SILU_MUL), (lw.w_down, "down", act, y, 0)):
                 st = lw.lora.get(key)
                 if st is not None:
-                    ops.linear(src, W, st, sl, u=u_for(st), flags=fl, out=dst)
+                    ops.linear(src, W, st, sl, u=u_for(st), flags=fl, out=dst, work=eng.ws_linear)
                 else:  # as the engine issues it: same kernel variant as the LoRA projections around it
-                    ops.linear(src, W, flags=fl | ops.SHARE_LORA_KERNEL, out=dst)
+                    ops.linear(src, W, flags=fl | ops.SHARE_LORA_KERNEL, out=dst, work=eng.ws_linear)
                 n += 1
                 total += lin_bytes(W, st, silu=bool(fl & ops.SILU_MUL))
-        ops.linear(x, pm.lm_head, flags=ops.OUT_F32 | ops.SHARE_LORA_KERNEL, out=eng.logits[:T])
+        ops.linear(x, pm.lm_head, flags=ops.OUT_F32 | ops.SHARE_LORA_KERNEL, out=eng.logits[:T], work=eng.ws_linear)
         return n + 1, total + lin_bytes(pm.lm_head, None, out_f32=True)
 
     def attentions():
         for l in range(pm.L):
             ops.paged_attention(qkv, kv.k_pages(l), kv.v_pages(l), kv.block_table, eng.row_slot[:T], eng.row_pos[:T],
-                                pm.Hq, pm.Hkv, pm.D, kv.page_size, pm.theta, True, out=attn)
+                                pm.Hq, pm.Hkv, pm.D, kv.page_size, pm.theta, True, out=attn, work=eng.ws_attn)
         return pm.L, pm.L * (T * (ctx + 1) * 2 * pm.Hkv * pm.D * 2 + T * (pm.Hq + 2 * pm.Hkv) * pm.D * 2
                              + T * pm.Hq * pm.D * 2)
 
     eng.row_pos[:T].fill_(ctx)
     out = {}
+    traffic = ncu_traffic()
     for name, fn, kernel in (("linear", linears, "linear_tc_kernel"), ("attention", attentions, "paged_attn_kernel")):
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
@@ -481,12 +635,12 @@ def kernel_rooflines(eng, pm, kv, B, slots, ops, torch, ctx, n_uniq, peak, reps=
                      # DRAM read+write bytes per launch: ncu capture of one launch of this kernel at the benchmark's
                      # shapes (profiles/), as a ratio to that launch's algorithmic bytes, applied to the step's
                      # average launch (traffic grows in proportion: the weights / KV pages dominate both)
-                     "traffic": NCU_TRAFFIC_RATIO[name] * total / n,
-                     "traffic_source": NCU_TRAFFIC_NOTE[name]}
+                     "traffic": traffic[name][0] * total / n if name in traffic else None,
+                     "traffic_source": traffic[name][1] if name in traffic else None}
     return out
 
 
-def run_operator_case(ops, synth, dev, torch):
+def operator_rows(ops, synth, dev, torch):
     """The operator micro-benchmark: y = x W^T + 2 (x A[id]) B[id], W [4096,4096], 16 rank-16 adapters,
     T in {1, 8, 32, 128} (shapes of tvm/lora_only/single_rank.py).  CUDA-event time of the shrink +
     projection pair (one mlora_lora_linear call) in a graph over 20 weight copies (671 MB, beyond L2); one JSON line."""
@@ -528,7 +682,13 @@ def run_operator_case(ops, synth, dev, torch):
         rows.append({"T": T, "us_with_lora": res["lora"], "us_base_only": res["base"],
                      "lora_overhead_frac": res["lora"] / res["base"] - 1.0, "algorithmic_bytes": by,
                      "achieved_gbs": by / (res["lora"] * 1e3), "frac_of_peak": by / (res["lora"] * 1e3) / peak})
-    emit({"kernel_case": "operator", "peak_gbs": peak, "peak_source": src, "rows": rows})
+    return {"case": "y = x W^T + 2 (x A[id]) B[id], W [4096,4096] bf16, 16 rank-16 adapters, ids uniform; shrink + "
+                    "projection as one mlora_lora_linear call, CUDA-event timed in a graph over 20 weight copies",
+            "peak_gbs": peak, "peak_source": src, "rows": rows}
+
+
+def run_operator_case(ops, synth, dev, torch):
+    emit(dict(operator_rows(ops, synth, dev, torch), kernel_case="operator"))
 
 
 def run_kernel_case(which):
@@ -587,21 +747,25 @@ def run_kernel_case(which):
         for i, r in enumerate(ranks):
             A[i, r:] = 0
             B[i, :, r:] = 0
-        st = ops.LoraStack(A, B, torch.tensor(ranks, dtype=torch.int32, device=dev), torch.full((n_ad,), 0.5, device=dev),
-                           rp, 1, (0, H)).pack_b()
+        mk = lambda: ops.LoraStack(A, B.clone(), torch.tensor(ranks, dtype=torch.int32, device=dev),
+                                   torch.full((n_ad,), 0.5, device=dev), rp, 1, (0, H))
+        st = mk().pack_b()                       # padded to the rank pitch (pre-tiled)
+        st_split = mk().split_b(ranks).pack_b()  # + the rank-compact copy the per-row expand prefers
         slots = torch.randperm(n_ad, device=dev, generator=g)[:T].to(torch.int32)
         out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
         u = torch.empty(T, rp, dtype=torch.float32, device=dev)
         res = {}
-        for name in ("base", "shrink", "per_row", "tensor_core_stages"):
+        for name in ("base", "shrink", "per_row_padded", "tensor_core_stages", "per_row_split"):
             def body():
                 for W in Ws:
                     if name == "base":
                         ops.linear(x, W, out=out)
                     elif name == "shrink":
                         ops.lora_shrink(x, st, slots, out=u)
+                    elif name == "per_row_split":
+                        ops.linear(x, W, st_split, slots, u=u, out=out, flags=ops.LORA_PER_ROW)
                     else:
-                        ops.linear(x, W, st, slots, u=u, out=out, flags=ops.LORA_PER_ROW if name == "per_row" else 0)
+                        ops.linear(x, W, st, slots, u=u, out=out, flags=ops.LORA_PER_ROW if name == "per_row_padded" else 0)
             body()
             torch.cuda.synchronize()
             gr = torch.cuda.CUDAGraph()
@@ -616,7 +780,7 @@ def run_kernel_case(which):
             torch.cuda.synchronize()
             res[name] = 1e3 * e0.elapsed_time(e1) / (3 * len(Ws))
         emit({"kernel_case": which, "us": res, "bytes_W": 2 * H * H, "bytes_B_by_rank": sum(2 * H * r for r in ranks),
-              "bytes_B_padded": n_ad * 2 * H * rp, "status": int(ops.workspace(4, dev, "linear")[:4].view(torch.int32)),
+              "bytes_B_padded": n_ad * 2 * H * rp, "status": ops.status_word(ops.workspace(4, dev, "linear")),
               "launches": ops.launch_count()})
         return
     elif which == "prefill":
@@ -651,7 +815,7 @@ def run_kernel_case(which):
         emit({"kernel_case": which, "T": T, "ms_base": res["base"], "ms_with_lora": res["lora"],
                           "tflops_base": fl / res["base"] / 1e9, "tflops_with_lora": (fl + 2.0 * T * 48 * (4096 + 4096)) / res["lora"] / 1e9,
                           "peak_tflops": tpk, "frac_base": fl / res["base"] / 1e9 / tpk,
-                          "status": int(ops.workspace(4, dev, "linear")[:4].view(torch.int32)), "launches": ops.launch_count()})
+                          "status": ops.status_word(ops.workspace(4, dev, "linear")), "launches": ops.launch_count()})
         return
     else:
         # one layer's attention at context 576: 32 rows x 32 heads, 302 MB of KV
@@ -691,13 +855,16 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="debug: truncate the model (the number is then not a bench value)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-operator", action="store_true", help="skip the operator micro-benchmark rows")
     ap.add_argument("--skip-prefill", action="store_true",
                     help="profiling aid: fill the KV cache with seeded random values instead of running prefill "
                          "(the number is then not a bench value)")
     ap.add_argument("--kernel-case", default="", choices=["", "linear", "attention", "operator", "prefill", "expand"],
                     help="profiling aid: launch one kernel a few times on a small case (> L2, < 1 GB) and exit")
-    ap.add_argument("--workload", default="", choices=["", "13b-shape"],
-                    help="side measurement (own JSON line, not the benchmark's): the 13B shape and adapter mix on one GPU")
+    ap.add_argument("--workload", default="", choices=["", "13b-shape", "13b-tp"],
+                    help="side measurements (own JSON line, not the benchmark's): 13b-shape = the 13B shape and adapter "
+                         "mix on one GPU; 13b-tp = the tensor-parallel configuration, tp size = number of ranks "
+                         "(launch with torch.distributed.run)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -710,6 +877,8 @@ def main():
     os.dup2(2, 1)
     if args.workload == "13b-shape":
         run_13b_shape(args)
+    elif args.workload == "13b-tp":
+        run_13b_tp(args, rank, world, local_rank)
     elif args.kernel_case:
         run_kernel_case(args.kernel_case)
     elif args.impl == "reference":

@@ -41,6 +41,13 @@ extern "C" {
                                feature) that streams each row's B_all[slot] up to the adapter's own rank, instead of
                                one masked tensor-core stage per distinct adapter.  Not with MLORA_SILU_MUL (ignored
                                there).  bf16 outputs are rounded twice (projection, then sum) */
+#define MLORA_B_SPLIT 128   /* with MLORA_LORA_PER_ROW: d_B_all is the rank-compact "split" layout -- every adapter stored
+                               as rank/8 slices [out, 8] bf16 laid one after the other (the split-to-the-minimum-rank
+                               strategy of tvm/lora_only/case_study/multiple_ranks.py:98-151 as a data layout: slices of
+                               one adapter are summed) -- and d_ranks holds 2*n_adapters ints: the ranks (multiples of
+                               8), then the index of each adapter's first slice.  The expand then reads exactly
+                               rank * out * 2 bytes per row, in whole 16-byte units per output feature, whatever the
+                               widest rank of the stack is */
 #define MLORA_SHARE_LORA_KERNEL 32 /* hint for a call WITHOUT LoRA operands that sits between calls with them
                                (gate/up/down when only q/k/v/o carry adapters): run the kernel variant the LoRA
                                calls use, so one code footprint stays hot in the instruction caches for the whole

@@ -5,8 +5,11 @@
 // a tile that is zero except for one row.  Here the work is laid out by (row, output feature) instead: one thread
 // per output feature reads that feature's B row of the token's adapter -- consecutive threads read consecutive
 // B rows, i.e. the kernel streams B_all[slot] -- up to the adapter's own rank only, and adds the product to the
-// projection's output in place.  Both B layouts are read: row-major [N, out, r_max] and the pre-tiled one of
-// mlora_pack_lora_b (128-row tiles per 64-wide rank slice, 16-byte chunks XOR-swizzled inside a row).
+// projection's output in place.  Three B layouts are read: row-major [N, out, r_max], the pre-tiled one of
+// mlora_pack_lora_b (128-row tiles per 64-wide rank slice, 16-byte chunks XOR-swizzled inside a row), and the
+// rank-compact split layout (MLORA_B_SPLIT: rank/8 slices [out, 8] per adapter), whose 16-byte unit per (slice,
+// output feature) makes consecutive threads read consecutive memory with no padding in between: DRAM traffic =
+// sum over rows of rank * out * 2 bytes, where the padded layouts drag the rest of each 128-byte row along.
 #include "linear.cuh"
 
 namespace mlora {
@@ -37,7 +40,26 @@ __global__ void __launch_bounds__(kExpThreads) lora_expand_rows_kernel(LinearArg
   const float* um = su + module_of(a, o) * a.r_max;
   const int n_chunks = (rank + 7) / 8;
   float acc = 0.f;
-  if (!packed) {
+  if (packed == 2) {
+    // split layout: slice j of this adapter is the [out, 8] block number ranks[n_adapters + slot] + j
+    const int first = a.ranks[a.n_adapters + slot];
+    const uint4* base = reinterpret_cast<const uint4*>(a.B_all) + (size_t)first * a.out + o;
+    for (int c0 = 0; c0 < n_chunks; c0 += 8) {  // up to 8 x 128-bit loads in flight
+      uint4 v[8];
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+        if (c0 + c < n_chunks) v[c] = ld_stream(base + (size_t)(c0 + c) * a.out);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        if (c0 + c < n_chunks) {
+          float bf[8];
+          unpack8(v[c], bf);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc = fmaf(um[(c0 + c) * 8 + e], bf[e], acc);
+        }
+      }
+    }
+  } else if (!packed) {
     const bf16* b = a.B_all + ((size_t)slot * a.out + o) * a.r_max;
     for (int c0 = 0; c0 < n_chunks; c0 += 8) {  // up to 8 x 128-bit loads in flight
       uint4 v[8];
@@ -87,13 +109,15 @@ __global__ void __launch_bounds__(kExpThreads) lora_expand_rows_kernel(LinearArg
 }  // namespace
 
 bool lora_expand_rows_supported(const LinearArgs& a) {
+  if ((a.flags & MLORA_B_SPLIT) && ((a.flags & MLORA_B_PACKED) || a.full_rank)) return false;
   return a.u != nullptr && !(a.flags & MLORA_SILU_MUL) && a.r_max % 8 == 0 && a.r_max * a.n_mod <= kExpMaxRtot &&
          (!(a.flags & MLORA_B_PACKED) || a.r_max == 16 || a.r_max == 32 || a.r_max == 64 || a.r_max == 128) && a.T <= 65535;
 }
 
 int launch_lora_expand_rows(const LinearArgs& a, cudaStream_t st) {
   dim3 grid((a.out + kExpThreads - 1) / kExpThreads, a.T);
-  launch_pdl_if(pdl_enabled(), lora_expand_rows_kernel, grid, dim3(kExpThreads), 0, st, a, (a.flags & MLORA_B_PACKED) ? 1 : 0);
+  launch_pdl_if(pdl_enabled(), lora_expand_rows_kernel, grid, dim3(kExpThreads), 0, st, a,
+                (a.flags & MLORA_B_SPLIT) ? 2 : (a.flags & MLORA_B_PACKED) ? 1 : 0);
   count_launch();
   MLORA_CHECK_LAUNCH("lora_expand_rows_kernel");
   return MLORA_OK;

@@ -76,7 +76,7 @@ static int linear_impl(const void* d_x, int64_t ldx, const void* d_W, void* d_y,
     LinearArgs b = a;
     b.u = nullptr;
     b.B_all = nullptr;
-    b.flags &= ~(MLORA_B_PACKED | MLORA_LORA_PER_ROW);
+    b.flags &= ~(MLORA_B_PACKED | MLORA_B_SPLIT | MLORA_LORA_PER_ROW);
     int rc;
     if (flags & MLORA_W_PACKED) {
       MLORA_REQUIRE(!(flags & MLORA_FORCE_SIMT) && d_work && linear_tc_supported(b),
@@ -90,6 +90,8 @@ static int linear_impl(const void* d_x, int64_t ldx, const void* d_W, void* d_y,
     if (rc != MLORA_OK) return rc;
     return launch_lora_expand_rows(a, st);
   }
+  MLORA_REQUIRE(!(flags & MLORA_B_SPLIT), "linear: the split B layout is read by the per-row expand only "
+                "(MLORA_LORA_PER_ROW, not MLORA_SILU_MUL, not MLORA_B_PACKED)");
   if (flags & MLORA_B_PACKED)
     MLORA_REQUIRE(d_u && !(flags & MLORA_FORCE_SIMT) && d_work, "linear: a packed B_all needs the tensor-core kernel");
   if (flags & (MLORA_W_PACKED | MLORA_B_PACKED)) {

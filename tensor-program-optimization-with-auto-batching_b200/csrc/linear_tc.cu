@@ -1012,11 +1012,6 @@ Plan make_plan(int T, int in, int out) {
     int gt = (int)grid;
     for (int d = 1; d <= 48 && d <= (int)grid; ++d)
       if (grid % d == 0) gt = d;  // largest divisor of the grid up to 48 (148 SMs -> 37)
-    static const int forced = [] {
-      const char* e = getenv("MLORA_WAVE_GT");  // experiments: token tiles per wave
-      return e ? atoi(e) : 0;
-    }();
-    if (forced > 0) gt = forced;
     pl.wave_gt = gt < pl.tok_tiles ? gt : pl.tok_tiles;
     pl.wave_full = pl.tok_tiles / pl.wave_gt;
     const int gt_last = pl.tok_tiles - pl.wave_full * pl.wave_gt;

@@ -220,11 +220,7 @@ __global__ void __launch_bounds__(kShrinkThreads, 1) lora_shrink_tc_kernel(const
 
 bool lora_shrink_tc_supported(const void* x, int64_t ldx, const void* A_all, const float* u, int T, int in, int r_tot) {
   // worth it from a few token tiles on; below that the warp-per-(row, rank) kernel is latency bound anyway
-  static const bool off = [] {
-    const char* e = getenv("MLORA_SHRINK_SIMT");  // "1": CUDA-core kernel at every size (comparison runs)
-    return e && e[0] == '1';
-  }();
-  return !off && T >= 256 && r_tot % 8 == 0 && r_tot <= 256 && in % 8 == 0 && ldx % 8 == 0 && aligned16(x) && aligned16(A_all) &&
+  return T >= 256 && r_tot % 8 == 0 && r_tot <= 256 && in % 8 == 0 && ldx % 8 == 0 && aligned16(x) && aligned16(A_all) &&
          aligned16(u);
 }
 

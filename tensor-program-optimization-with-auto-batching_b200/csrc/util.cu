@@ -23,17 +23,14 @@ int fail(int code, const char* fmt, ...) {
 // Programmatic dependent launch policy.  Which kernels are launched programmatically dependent (may become
 // resident, and run whatever does not depend on earlier kernels, while the kernel before them still runs) is a
 // bit mask: bit 0 projection (its weight producer streams ahead), 1 LoRA shrink, 2 attention, 3 RMSNorm, 4 the
-// rest.  Measured on the benchmark's decode step: projection only (1) 5.60 ms, projection + RMSNorm (9) 5.53 ms --
-// the default --, + shrink (3 / 11) 5.57, + attention (5 / 13) 5.79-5.84 (its early-resident CTAs take registers
-// and issue slots from the kernel before them), everything (31) slowest, none (0) 5.9.
-// MLORA_PDL_MASK=<mask> overrides; MLORA_PDL=0 / 1 / 2 / 3 are shorthands for masks 0 / 31 / 1 / 3.
+// rest.  Measured on the benchmark's decode step (ms per step): none (0) 5.9, projection only (1) 4.98-5.60,
+// projection + RMSNorm (9) 5.00-5.53 -- the default --, + shrink (11) 5.01-5.57, + attention (13, 15, 31) 5.25-5.8
+// (its early-resident CTAs take registers and issue slots from the kernel before them).
+// The one documented switch: MLORA_PDL_MASK=<mask>.
 static int pdl_mask() {
   static const int mask = [] {
     const char* e = getenv("MLORA_PDL_MASK");
-    if (e) return atoi(e);
-    e = getenv("MLORA_PDL");
-    if (!e) return 9;
-    return strcmp(e, "0") == 0 ? 0 : strcmp(e, "1") == 0 ? 31 : strcmp(e, "3") == 0 ? 3 : 1;
+    return e ? atoi(e) : 9;
   }();
   return mask;
 }

@@ -42,6 +42,7 @@ class MultiLoraLinear(nn.Module):
         self.merged = False
         self.active_adapters = []
         self._packed = None  # (key, LoraStack, name -> slot, packed base weight)
+        self._ctx = None     # shared AdapterContext (set by MultiLoraModel): per-call adapter names + slot-tensor cache
         if adapter_name is not None and r > 0:
             self.update_layer(adapter_name, r, lora_alpha)
 
@@ -114,23 +115,42 @@ class MultiLoraLinear(nn.Module):
         return self._packed
 
     # -- forward ---------------------------------------------------------------------------------------------
+    def _slot_tensor(self, slots_per_batch_row, per_row, device):
+        """int32 [rows] on the device: built once per (adapter list, tokens per row) and shared by every layer of
+        the model through the context -- one small host-to-device copy per generate step, not one per layer."""
+        key = (tuple(slots_per_batch_row), per_row, str(device))
+        cache = self._ctx.slot_cache if self._ctx is not None else None
+        if cache is not None and key in cache:
+            return cache[key]
+        t = torch.tensor(slots_per_batch_row, dtype=torch.int32).repeat_interleave(per_row).pin_memory() \
+            .to(device, non_blocking=True)
+        if cache is not None:
+            if len(cache) > 64:
+                cache.clear()
+            cache[key] = t
+        return t
+
     def _run(self, x, slots_per_batch_row):
         """x [B,S,in] (or [T,in]); one slot per leading row, shared by that row's S tokens."""
         _, stack, _, Wp = self._pack()
         lead = x.shape[:-1]
-        x2 = x.reshape(-1, self.in_features).to(torch.bfloat16).contiguous()
+        x2 = x.reshape(-1, self.in_features)
+        if x2.dtype != torch.bfloat16 or not x2.is_contiguous():
+            x2 = x2.to(torch.bfloat16).contiguous()
         slots = None
         if slots_per_batch_row is not None and stack is not None:
-            per_row = x2.shape[0] // len(slots_per_batch_row)
-            slots = torch.tensor(slots_per_batch_row, dtype=torch.int32).repeat_interleave(per_row).to(x2.device)
+            slots = self._slot_tensor(slots_per_batch_row, x2.shape[0] // len(slots_per_batch_row), x2.device)
         y = ops.linear(x2, Wp, stack if slots is not None else None, slots)
         if self.base_layer.bias is not None:
             y = y + self.base_layer.bias.to(y.dtype)
-        return y.reshape(*lead, self.out_features).to(x.dtype)
+        y = y.reshape(*lead, self.out_features)
+        return y if y.dtype == x.dtype else y.to(x.dtype)
 
     def forward(self, x: torch.Tensor, *args: Any, **kwargs: Any) -> torch.Tensor:
         self._check_forward_args(x, *args, **kwargs)
         adapter_names = kwargs.pop("adapter_names", None)
+        if adapter_names is None and self._ctx is not None:
+            adapter_names = self._ctx.adapter_names  # handed over by MultiLoraModel (peft does this with forward hooks)
         if not x.is_cuda:
             raise RuntimeError("MultiLoraLinear runs on a CUDA device only (there is no CPU path)")
         if self.disable_adapters:
@@ -180,3 +200,119 @@ def wrap_model(model: nn.Module, target_modules=("q_proj", "v_proj")):
                 setattr(parent, name, layer)
                 wrapped.append(layer)
     return wrapped
+
+
+class AdapterContext:
+    """What peft passes to every LoRA layer of a model during one ``generate`` / ``forward`` call: the per-row
+    adapter names (``adapter_names=`` of ``model.generate``, ``gen_lora.py:116``).  Also holds the device slot
+    tensors built from them, shared by all layers."""
+
+    def __init__(self):
+        self.adapter_names = None
+        self.slot_cache = {}
+
+
+class MultiLoraModel:
+    """A HuggingFace causal LM whose target ``nn.Linear`` modules are :class:`MultiLoraLinear` layers, with the
+    adapters of ``get_hf_model`` (``huggingface/generation/gen_lora.py:21-57``) injected and loaded, driven like
+    the reference drives its peft model: ``model.generate(**tokens, adapter_names=[...], max_new_tokens=n,
+    do_sample=False)`` (``gen_lora.py:116``)."""
+
+    def __init__(self, model, layers):
+        self.model, self.layers, self.ctx = model, layers, AdapterContext()
+        for layer in layers:
+            layer._ctx = self.ctx
+
+    def _call(self, fn, adapter_names, *args, **kwargs):
+        if adapter_names is not None:
+            adapter_names = list(adapter_names)
+        self.ctx.adapter_names = adapter_names
+        try:
+            with torch.no_grad():
+                return fn(*args, **kwargs)
+        finally:
+            self.ctx.adapter_names = None
+
+    def generate(self, *args, adapter_names=None, **kwargs):
+        return self._call(self.model.generate, adapter_names, *args, **kwargs)
+
+    def __call__(self, *args, adapter_names=None, **kwargs):
+        return self._call(self.model, adapter_names, *args, **kwargs)
+
+    def disable_adapter(self):
+        """Context manager: the base model alone (peft's ``with model.disable_adapter():``)."""
+        import contextlib
+
+        @contextlib.contextmanager
+        def ctx():
+            old = [layer.disable_adapters for layer in self.layers]
+            for layer in self.layers:
+                layer.disable_adapters = True
+            try:
+                yield self
+            finally:
+                for layer, o in zip(self.layers, old):
+                    layer.disable_adapters = o
+        return ctx()
+
+    # hot add / remove of one adapter (files in the format of adapters.py)
+    def add_adapter(self, name, tensors, r, lora_alpha):
+        for layer in self.layers:
+            layer.update_layer(name, r, lora_alpha)
+        _load_into(self.model, name, tensors)
+        self.ctx.slot_cache.clear()
+
+    def remove_adapter(self, name):
+        for layer in self.layers:
+            if name in layer.lora_A:
+                del layer.lora_A[name], layer.lora_B[name], layer.lora_dropout[name]
+                layer.scaling.pop(name), layer.r.pop(name), layer.use_dora.pop(name)
+                if name in layer.active_adapters:
+                    layer.active_adapters.remove(name)
+                layer.invalidate()
+        self.ctx.slot_cache.clear()
+
+
+def _load_into(model, adapter, tensors):
+    """The reference's key map (``gen_lora.py:50``): file key ``layers.{L}.self_attn.q_proj.lora_A.weight`` is peft's
+    parameter ``base_model.model.model.layers.{L}.self_attn.q_proj.lora_A.{adapter}.weight``; here the same path
+    under the unwrapped HF model: ``model.layers.{L}.self_attn.q_proj`` -> ``lora_A[adapter].weight``."""
+    root = model.get_submodule("model") if hasattr(model, "model") else model
+    loaded = 0
+    for k, v in tensors.items():
+        if not k.endswith(".weight"):
+            continue
+        path, which = k[: -len(".weight")].rsplit(".", 1)  # "layers.3.self_attn.q_proj", "lora_A"
+        try:
+            mod = root.get_submodule(path)
+        except AttributeError:
+            continue
+        if not isinstance(mod, MultiLoraLinear) or adapter not in getattr(mod, which):
+            continue
+        p = getattr(mod, which)[adapter].weight
+        if tuple(p.shape) != tuple(v.shape):
+            raise ValueError(f"{k}: file holds {tuple(v.shape)}, the layer expects {tuple(p.shape)}")
+        p.data = v.to(dtype=p.dtype, device=p.device)
+        mod.invalidate()
+        loaded += 1
+    if loaded == 0:
+        raise ValueError(f"no tensor of adapter '{adapter}' matched a wrapped layer")
+    return loaded
+
+
+def get_hf_model(base_model, adapter_dir, unique_adapters, r=64, lora_alpha=32, target_modules=("q_proj", "v_proj")):
+    """``get_hf_model`` of ``huggingface/generation/gen_lora.py:21-57`` on a model the caller has built: wraps the
+    target projections (``:30-44``), injects every adapter of ``unique_adapters`` (names ``adapter{i}``), loads
+    ``{adapter_dir}/r{r}_a{i}.safetensors`` into them (``:46-53``) and returns a :class:`MultiLoraModel`."""
+    from . import adapters as adapter_io
+
+    layers = wrap_model(base_model, target_modules)
+    names = sorted(unique_adapters)
+    for name in names:
+        for layer in layers:
+            layer.update_layer(name, r, lora_alpha)
+    for name in names:
+        path = adapter_io.adapter_path(adapter_dir, r, int(name.replace("adapter", "")))
+        _load_into(base_model, name, adapter_io.load_adapter(path))
+    base_model.eval()
+    return MultiLoraModel(base_model, layers)

@@ -61,7 +61,7 @@ class PackedLlama:
     Adapter ``i`` occupies slot ``i`` of every stack."""
 
     def __init__(self, cfg, weights, adapters=(), scales=(), device="cuda", n_layers=None, pack=True,
-                 tp_rank=0, tp_size=1):
+                 tp_rank=0, tp_size=1, adapter_capacity=None, max_rank=None, adapter_targets=None):
         """pack=True stores every projection matrix and adapter B stack in the pre-tiled layouts of
         mlora_pack_weight / mlora_pack_lora_b (one bulk copy per pipeline stage).
 
@@ -71,7 +71,10 @@ class PackedLlama:
         all-reduce), lm_head is vocabulary-parallel.  Adapters follow their projection: on a
         column-parallel projection A is replicated and B sliced by rows; on a row-parallel one A is
         sliced by columns and B replicated, so each rank's LoRA partial rides in its GEMM partial and
-        the one all-reduce sums both."""
+        the one all-reduce sums both.
+
+        ``adapter_capacity`` / ``max_rank`` / ``adapter_targets``: room for adapters added later with
+        :meth:`add_adapter` (slots, widest rank, projection names when no adapter is given at construction)."""
         self.cfg = dict(cfg)
         self.pack = pack
         self.tp_rank, self.tp_size = int(tp_rank), int(tp_size)
@@ -97,16 +100,23 @@ class PackedLlama:
         self.norm = bf(weights["model.norm.weight"])
         lm = weights["lm_head.weight"][self.vocab_offset:self.vocab_offset + self.V]
         self.lm_head = ops.PackedWeight(bf(lm)) if pack else bf(lm)
-        self.n_adapters = len(adapters)
+        # adapter slots: the adapters given now fill slots 0..n-1; ``adapter_capacity`` reserves further (empty) slots
+        # that add_adapter() fills later without moving any buffer (captured graphs stay valid)
+        n_slots = max(len(adapters), int(adapter_capacity or 0))
+        self.n_adapters = n_slots
+        self._free_slots = list(range(n_slots - 1, len(adapters) - 1, -1))
+        self.adapter_targets = tuple(adapter_targets) if adapter_targets else None
         ranks = []
-        for ad in adapters:
-            ka = next(k for k in ad if k.endswith("lora_A.weight"))
-            ranks.append(ad[ka].shape[0])
-        self.ranks_host = ranks
-        self.r_max = (16 if max(ranks) <= 16 else 32 if max(ranks) <= 32 else -(-max(ranks) // 64) * 64) if ranks else 0
-        if adapters:
-            self.ranks = torch.tensor(ranks, dtype=torch.int32, device=self.device)
-            self.scales = torch.tensor(list(scales), dtype=torch.float32, device=self.device)
+        for ad in adapters:  # an adapter's rank = the largest over its projections
+            ranks.append(max(v.shape[0] for k, v in ad.items() if k.endswith("lora_A.weight")))
+        top = max(ranks + [int(max_rank or 0)]) if (ranks or max_rank) else 0
+        self.ranks_host = ranks + [0] * (n_slots - len(ranks))
+        self.r_max = (16 if top <= 16 else 32 if top <= 32 else -(-top // 64) * 64) if n_slots else 0
+        if self.r_max > 64:
+            raise ValueError(f"adapter rank {top} exceeds 64, the widest rank pitch the projection kernels take")
+        if n_slots:
+            self.ranks = torch.tensor(self.ranks_host, dtype=torch.int32, device=self.device)
+            self.scales = torch.tensor(list(scales) + [0.0] * (n_slots - len(ranks)), dtype=torch.float32, device=self.device)
         self.layers = []
         for l in range(self.L):
             p = f"model.layers.{l}."
@@ -119,64 +129,119 @@ class PackedLlama:
                 w_o=pk(w("self_attn.o_proj")[:, self._q_rows]),
                 w_gu=pk(interleave_gate_up(w("mlp.gate_proj")[self._i_rows], w("mlp.up_proj")[self._i_rows])),
                 w_down=pk(w("mlp.down_proj")[:, self._i_rows]))
-            if adapters:
+            if n_slots:
                 self._pack_lora(l, lw, adapters)
             self.layers.append(lw)
 
-    def _pack_lora(self, l, lw, adapters):
-        N, r_max, dev = len(adapters), self.r_max, self.device
+    # -- adapter stacks ---------------------------------------------------------------------------------------
+    def _stack_specs(self):
         qd, kvd = self.Hq * self.D, self.Hkv * self.D
+        return {"qkv": ("self_attn", ("q_proj", "k_proj", "v_proj"), (qd, kvd, kvd), self.H, False),
+                "o": ("self_attn", ("o_proj",), (self.H,), qd, False),
+                "gu": ("mlp", ("gate_proj", "up_proj"), (self.I, self.I), self.H, True),
+                "down": ("mlp", ("down_proj",), (self.H,), self.I, False)}
 
+    def _adapter_slices(self, l, ad, blk, proj):
+        """(A [r,in], B [out,r]) of one projection of one adapter, cut to this rank's tensor-parallel share."""
+        ka = f"layers.{l}.{blk}.{proj}.lora_A.weight"
+        if ka not in ad:
+            return None
+        A, B = ad[ka], ad[ka.replace("lora_A", "lora_B")]
         rows_of = {"q_proj": self._q_rows, "k_proj": self._kv_rows, "v_proj": self._kv_rows,
                    "gate_proj": self._i_rows, "up_proj": self._i_rows}
         cols_of = {"o_proj": self._q_rows, "down_proj": self._i_rows}
+        if proj in rows_of:      # column-parallel: B follows the output rows of this rank
+            B = B[rows_of[proj]]
+        else:                    # row-parallel: A follows the input columns of this rank
+            A = A[:, cols_of[proj]]
+        return A, B
 
-        def get(ad, blk, proj):
-            ka = f"layers.{l}.{blk}.{proj}.lora_A.weight"
-            if ka not in ad:
-                return None
-            A, B = ad[ka], ad[ka.replace("lora_A", "lora_B")]
-            if proj in rows_of:      # column-parallel: B follows the output rows of this rank
-                B = B[rows_of[proj]]
-            else:                    # row-parallel: A follows the input columns of this rank
-                A = A[:, cols_of[proj]]
-            return A, B
+    def _one_adapter(self, l, key, ad):
+        """A_one [n_mod*r_max, in] and B_one [out_total, pitch] (zero padded, bf16, on the device) of adapter ``ad``
+        for stack ``key`` of layer ``l``."""
+        blk, projs, outs, in_f, interleave = self._stack_specs()[key]
+        r_max, dev = self.r_max, self.device
+        A_one = torch.zeros(len(projs) * r_max, in_f, dtype=torch.bfloat16, device=dev)
+        parts = [torch.zeros(o, r_max, dtype=torch.bfloat16, device=dev) for o in outs]
+        for m, proj in enumerate(projs):
+            ab = self._adapter_slices(l, ad, blk, proj)
+            if ab is None:
+                continue
+            A, B = ab
+            r = A.shape[0]
+            if r > r_max:
+                raise ValueError(f"adapter rank {r} exceeds the stack's rank pitch {r_max}")
+            A_one[m * r_max:m * r_max + r] = A.to(device=dev, dtype=torch.bfloat16)
+            parts[m][:, :r] = B.to(device=dev, dtype=torch.bfloat16)
+        if interleave:
+            # gate rows carry [B_gate | 0], up rows [0 | B_up]: one dot product against [u_gate | u_up]
+            z = torch.zeros_like(parts[0])
+            B_one = interleave_gate_up(torch.cat([parts[0], z], 1), torch.cat([z, parts[1]], 1))
+        else:
+            B_one = torch.cat(parts, 0)
+        return A_one, B_one.contiguous()
 
-        def build(blk, projs, outs, in_f, interleave=False):
-            if not any(get(ad, blk, p) is not None for ad in adapters for p in projs):
-                return None
-            n_mod = len(projs)
-            A_all = torch.zeros(N, n_mod * r_max, in_f, dtype=torch.bfloat16, device=dev)
-            B_parts = [torch.zeros(N, o, r_max, dtype=torch.bfloat16, device=dev) for o in outs]
+    def _pack_lora(self, l, lw, adapters):
+        N, r_max, dev = self.n_adapters, self.r_max, self.device
+        for key, (blk, projs, outs, in_f, interleave) in self._stack_specs().items():
+            named = any(f"layers.{l}.{blk}.{p}.lora_A.weight" in ad for ad in adapters for p in projs)
+            wanted = self.adapter_targets is not None and any(p in self.adapter_targets for p in projs)
+            if not (named or wanted):
+                continue
+            pitch = 2 * r_max if interleave else r_max
+            A_all = torch.zeros(N, len(projs) * r_max, in_f, dtype=torch.bfloat16, device=dev)
+            B_all = torch.zeros(N, sum(outs), pitch, dtype=torch.bfloat16, device=dev)
             for s, ad in enumerate(adapters):
-                for m, proj in enumerate(projs):
-                    ab = get(ad, blk, proj)
-                    if ab is None:
-                        continue
-                    A, B = ab
-                    r = A.shape[0]
-                    A_all[s, m * r_max:m * r_max + r] = A.to(device=dev, dtype=torch.bfloat16)
-                    B_parts[m][s, :, :r] = B.to(device=dev, dtype=torch.bfloat16)
-            if interleave:
-                # gate rows carry [B_gate | 0], up rows [0 | B_up]: one dot product against [u_gate | u_up]
-                z = torch.zeros_like(B_parts[0])
-                g2, u2 = torch.cat([B_parts[0], z], 2), torch.cat([z, B_parts[1]], 2)
-                B_all = torch.stack([interleave_gate_up(g2[s], u2[s]) for s in range(N)])
-            else:
-                B_all = torch.cat(B_parts, 1)
+                A_all[s], B_all[s] = self._one_adapter(l, key, ad)
             offs = tuple(int(x) for x in np.cumsum([0] + list(outs)))
-            st = LoraStack(A_all, B_all.contiguous(), self.ranks, self.scales, r_max, n_mod, offs)
-            st.bytes_per_adapter = 2 * (A_all[0].numel() + sum(o for o in outs) * r_max)
+            st = LoraStack(A_all, B_all, self.ranks, self.scales, r_max, len(projs), offs)
+            st.bytes_per_adapter = 2 * (A_all[0].numel() + sum(outs) * r_max)
+            # mixed ranks: a second, rank-compact copy of B for the per-row expand (batches where every row brings
+            # its own adapter); not for stacks with spare slots, whose rows must stay writable in place
+            mixed = any(r != r_max for r in self.ranks_host)
+            if mixed and not interleave and not self._free_slots and N == len(adapters):
+                st.split_b(self.ranks_host)
             if self.pack and all(o % 128 == 0 for o in offs[1:-1]):
                 st.pack_b()
-            return st
+            lw.lora[key] = st
 
-        for key, st in (("qkv", build("self_attn", ("q_proj", "k_proj", "v_proj"), (qd, kvd, kvd), self.H)),
-                        ("o", build("self_attn", ("o_proj",), (self.H,), qd)),
-                        ("gu", build("mlp", ("gate_proj", "up_proj"), (self.I, self.I), self.H, True)),
-                        ("down", build("mlp", ("down_proj",), (self.H,), self.I))):
-            if st is not None:
-                lw.lora[key] = st
+    def add_adapter(self, adapter: dict, scale: float) -> int:
+        """Loads one more adapter into a free slot (reserved with ``adapter_capacity``) while the model is serving:
+        only that slot's rows of the stacks, its rank and its scale are written, so buffers -- and CUDA graphs
+        captured over them -- stay as they are.  Returns the slot.  (The loader half of the reference's adapter
+        files, ``init_peft_weights/lora_weights.py`` / ``compile_tvm.py:296-314``, made incremental.)"""
+        if not self._free_slots:
+            raise RuntimeError("no free adapter slot: construct PackedLlama with a larger adapter_capacity")
+        rank = max(v.shape[0] for k, v in adapter.items() if k.endswith("lora_A.weight"))
+        if rank > self.r_max:
+            raise ValueError(f"adapter rank {rank} exceeds the rank pitch {self.r_max} the stacks were built with")
+        slot = self._free_slots.pop()
+        for l, lw in enumerate(self.layers):
+            for key, st in lw.lora.items():
+                A_one, B_one = self._one_adapter(l, key, adapter)
+                st.A_all[slot].copy_(A_one)
+                st.write_b_slot(slot, B_one)
+                st._all_full_rank = None
+                st.B_split = st.rank_tbl = None
+        self.ranks[slot] = rank
+        self.scales[slot] = float(scale)
+        self.ranks_host[slot] = rank
+        return slot
+
+    def remove_adapter(self, slot: int) -> None:
+        """Empties a slot (zero rank, zero scale, zero rows: the kernels multiply padding rather than look ranks up).
+        Requests must have stopped naming the slot."""
+        if slot in self._free_slots or not 0 <= slot < self.n_adapters:
+            raise ValueError(f"adapter slot {slot} is not in use")
+        for lw in self.layers:
+            for st in lw.lora.values():
+                st.A_all[slot].zero_()
+                st.write_b_slot(slot, None)
+                st._all_full_rank = None
+        self.ranks[slot] = 0
+        self.scales[slot] = 0.0
+        self.ranks_host[slot] = 0
+        self._free_slots.append(slot)
 
     def weight_bytes(self):
         """Bytes of base weights one decode step streams (all layers + final norm + lm_head)."""

@@ -13,7 +13,7 @@ import torch
 from . import _lib
 from ._lib import check
 
-OUT_F32, SILU_MUL, FORCE_SIMT, W_PACKED, B_PACKED, SHARE_LORA_KERNEL, LORA_PER_ROW = 1, 2, 4, 8, 16, 32, 64
+OUT_F32, SILU_MUL, FORCE_SIMT, W_PACKED, B_PACKED, SHARE_LORA_KERNEL, LORA_PER_ROW, B_SPLIT = 1, 2, 4, 8, 16, 32, 64, 128
 
 
 def _ptr(t):
@@ -114,6 +114,29 @@ class LoraStack:
     mod_offsets: tuple = None
     b_packed: bool = False   # B_all holds the tiled layout of mlora_pack_lora_b (uint8 buffer)
     n_out: int = 0           # output features (needed once B_all is packed)
+    B_split: torch.Tensor = None   # rank-compact copy for the per-row expand: [slices, out, 8] bf16 (see split_b)
+    rank_tbl: torch.Tensor = None  # int32 [2N]: ranks (rounded up to 8), then each adapter's first slice
+
+    def split_b(self, ranks_host):
+        """Builds the rank-compact "split" layout from the row-major B_all (call BEFORE pack_b): adapter s becomes
+        ceil(rank[s] / 8) slices [out, 8], stored one after the other; a table gives each adapter's first slice.
+        The per-row expand (``LORA_PER_ROW``) then reads rank * out * 2 bytes per row and nothing else."""
+        if self.b_packed:
+            raise ValueError("split_b needs the row-major B_all (call it before pack_b)")
+        N, out, pitch = self.B_all.shape
+        n_sl = [-(-int(r) // 8) for r in ranks_host]
+        first = [0]
+        for n in n_sl:
+            first.append(first[-1] + n)
+        dev = self.B_all.device
+        if first[-1] == 0:
+            return self
+        idx_slot = torch.tensor([s for s, n in enumerate(n_sl) for _ in range(n)], device=dev)
+        idx_sl = torch.tensor([j for n in n_sl for j in range(n)], device=dev)
+        B5 = self.B_all.view(N, out, pitch // 8, 8)
+        self.B_split = B5[idx_slot, :, idx_sl, :].contiguous()            # [slices, out, 8]
+        self.rank_tbl = torch.tensor([8 * n for n in n_sl] + first[:-1], dtype=torch.int32, device=dev)
+        return self
 
     def pack_b(self, interleaved: bool = False):
         """Replace B_all by its pre-tiled form (tensor-core expand only; modules must be tile aligned)."""
@@ -125,6 +148,28 @@ class LoraStack:
         check(_lib.lib().mlora_pack_lora_b(_ptr(self.B_all), N, out, pitch, _ptr(buf), _stream()), "mlora_pack_lora_b")
         self.B_all, self.b_packed, self.n_out = buf, True, out
         return self
+
+
+def _write_b_slot(self, slot: int, B_one):
+    """Replace one adapter's rows of B_all (``B_one`` [out, pitch] bf16, or None = zeros), packed or not."""
+    if not self.b_packed:
+        if B_one is None:
+            self.B_all[slot].zero_()
+        else:
+            self.B_all[slot].copy_(B_one)
+        return
+    N = self.A_all.shape[0]
+    per = self.B_all.numel() // N  # bytes of one slot: tiles are laid out slot-major
+    region = self.B_all[slot * per:(slot + 1) * per]
+    if B_one is None:
+        region.zero_()
+        return
+    out, pitch = B_one.shape
+    assert _lib.lib().mlora_packed_lora_b_bytes(1, out, pitch) == per
+    check(_lib.lib().mlora_pack_lora_b(_ptr(B_one.contiguous()), 1, out, pitch, _ptr(region), _stream()), "mlora_pack_lora_b")
+
+
+LoraStack.write_b_slot = _write_b_slot
 
 
 def lora_shrink(x, stack: LoraStack, slots, out=None):
@@ -173,8 +218,11 @@ def linear(x, W, stack: LoraStack = None, slots=None, u=None, flags: int = 0, ou
         raise ValueError("mlora.linear needs bf16 x and W")
     if isinstance(W, PackedWeight):
         flags |= W_PACKED
-    if stack is not None and stack.b_packed:
+    split = stack is not None and bool(flags & LORA_PER_ROW) and stack.B_split is not None and not flags & SILU_MUL
+    if stack is not None and stack.b_packed and not split:
         flags |= B_PACKED
+    if split:
+        flags |= B_SPLIT
     T, K = x.shape
     N = W.shape[0]
     cols = N // 2 if flags & SILU_MUL else N
@@ -203,8 +251,10 @@ def linear(x, W, stack: LoraStack = None, slots=None, u=None, flags: int = 0, ou
         return out
     check(_lib.lib().mlora_linear(
         _ptr(x), x.stride(0), _ptr(W), _ptr(out), out.stride(0), T, K, N,
-        _ptr(u) if stack is not None else None, _ptr(stack.B_all) if stack is not None else None,
-        _ptr(stack.ranks) if stack is not None else None, _ptr(stack.scales) if stack is not None else None,
+        _ptr(u) if stack is not None else None,
+        (_ptr(stack.B_split) if split else _ptr(stack.B_all)) if stack is not None else None,
+        (_ptr(stack.rank_tbl) if split else _ptr(stack.ranks)) if stack is not None else None,
+        _ptr(stack.scales) if stack is not None else None,
         _ptr(slots) if stack is not None else None, stack.A_all.shape[0] if stack is not None else 0,
         stack.r_max if stack is not None else 0,
         stack.n_mod if stack is not None else 1, mod, flags, _ptr(ws), wb, _stream()), "mlora_linear")

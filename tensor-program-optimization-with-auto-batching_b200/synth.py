@@ -113,6 +113,35 @@ def adapter_ids_zipf(n_requests: int, n_adapters: int, s: float = 1.1) -> np.nda
     return np.random.default_rng(SEED_IDS).choice(n_adapters, size=n_requests, p=p).astype(np.int32)
 
 
+def request_mix(request_type: str, batch_size: int, seed: int = SEED_IDS) -> np.ndarray:
+    """The reference's three request mixes (``huggingface/generation/gen_lora.py:77-85``): ``uniform`` = sorted
+    draws from ``[0, ceil(sqrt(B)))`` (same-adapter rows contiguous), ``distinct`` = every request its own adapter,
+    ``identical`` = one adapter for all.  Seeded (the reference draws from numpy's global generator)."""
+    if request_type == "uniform":
+        hi = int(np.ceil(np.sqrt(batch_size)))
+        return np.sort(np.random.default_rng(seed).integers(0, hi, batch_size)).astype(np.int32)
+    if request_type == "distinct":
+        return np.arange(batch_size, dtype=np.int32)
+    if request_type == "identical":
+        return np.zeros(batch_size, dtype=np.int32)
+    raise ValueError(f"unknown request_type {request_type}")
+
+
+def request_mix_by_rank(request_type: str, batch_size: int, num_seqs_per_adapter, lora_ranks, seed: int = SEED_IDS):
+    """The auto-batcher driver's batch (``tvm/llama_auto_batcher/main.py:24-35``): one group of requests per adapter
+    rank, weight ids inside a group drawn per ``request_type``, and ``batch_size - sum(groups)`` requests WITHOUT
+    adapter padded in front.  Returns ``(ranks, wids)``, each ``[batch_size]`` with -1 for the padding rows."""
+    if sum(num_seqs_per_adapter) > batch_size:
+        raise ValueError("more adapter requests than the batch holds")
+    ranks = [r for n, r in zip(num_seqs_per_adapter, lora_ranks) for _ in range(n)]
+    if request_type == "identical":
+        wids = [0] * sum(num_seqs_per_adapter)
+    else:
+        wids = [int(w) for g, n in enumerate(num_seqs_per_adapter) for w in request_mix(request_type, n, seed + g)]
+    pad = [-1] * (batch_size - sum(num_seqs_per_adapter))
+    return np.asarray(pad + ranks, dtype=np.int32), np.asarray(pad + wids, dtype=np.int32)
+
+
 def prompts(n_requests: int, length: int, vocab: int) -> np.ndarray:
     return np.random.default_rng(SEED_TOKENS).integers(0, vocab, (n_requests, length)).astype(np.int32)
 

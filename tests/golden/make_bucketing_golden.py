@@ -12,7 +12,9 @@ import sys
 
 import numpy as np
 
-ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) != 2:
+    sys.exit(f"usage: python {sys.argv[0]} <path-to-reference-checkout>")
+ref = sys.argv[1]
 sys.path.insert(0, os.path.join(ref, "tvm", "llama_auto_batcher"))
 from llama_seq_info import LlamaSeqInfo  # noqa: E402
 from exec_graph import ExecGraph  # noqa: E402

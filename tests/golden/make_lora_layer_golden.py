@@ -17,7 +17,9 @@ import numpy as np
 import torch
 from torch import nn
 
-ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) != 2:
+    sys.exit(f"usage: python {sys.argv[0]} <path-to-reference-checkout>")
+ref = sys.argv[1]
 
 
 class _StandInLinear(nn.Module):

@@ -146,3 +146,67 @@ def test_vm_function_table_runs_the_reference_executor_protocol(synth, cuda):
     # a batch of one type only uses decode_a{t}(hidden, kv, wids)
     name, plist = info.get_decode_method([3, 1])
     assert name == "decode_a0" and plist == [[0, 1]]
+
+
+def test_hf_model_with_injected_adapter_files_generates_like_the_cpu_hf_path(synth, cuda, tmp_path):
+    """``get_hf_model`` + ``generate(adapter_names=...)`` of huggingface/generation/gen_lora.py:21-57,114-116 on a
+    transformers ``LlamaForCausalLM`` (bf16, on the GPU) whose q/k/v/o projections are ``MultiLoraLinear`` layers
+    loaded from adapter files in the reference's format, against the CPU HF path (fp32 model + the restated
+    GatherBMMLinear) on the same files."""
+    from oracle import hf_path
+
+    ll, adapter_io = load("lora_linear"), load("adapters")
+    cfg = synth.llama_config("tiny")
+    w = {k: v.bfloat16() for k, v in synth.base_weights(cfg).items()}
+    r, alpha, n_ad = 8, 16, 4
+    adapter_io.write_adapter_files(str(tmp_path), cfg, [r], n_ad, targets=synth.ATTN_PROJ, scaling_factor=0.05)
+    ads = [{k: v.bfloat16() for k, v in adapter_io.load_adapter(adapter_io.adapter_path(str(tmp_path), r, a)).items()}
+           for a in range(n_ad)]
+    ids = [2, 0, 3, 0]
+    names = [f"adapter{i}" for i in ids]
+    prompts = torch.from_numpy(synth.prompts(4, 48, cfg["vocab_size"])).long()
+    gen = 8
+
+    cpu = hf_path.build_hf_model(cfg, w, ads, [alpha / r] * n_ad)
+    want_tok = hf_path.generate(cpu, prompts, ids, gen)
+    want_logits = hf_path.forward_logits(cpu, torch.cat([prompts, want_tok[:, :-1]], 1), ids)
+
+    base = hf_path.build_hf_model(cfg, w, dtype=torch.bfloat16).to(cuda)
+    model = ll.get_hf_model(base, str(tmp_path), {f"adapter{i}" for i in range(n_ad)}, r=r, lora_alpha=alpha,
+                            target_modules=synth.ATTN_PROJ)
+    assert len(model.layers) == 4 * cfg["num_hidden_layers"]
+    launches0 = load("ops").launch_count()
+    out = model.generate(input_ids=prompts.to(cuda), attention_mask=torch.ones_like(prompts).to(cuda),
+                         adapter_names=names, max_new_tokens=gen, min_new_tokens=gen, do_sample=False, pad_token_id=0)
+    got_tok = out[:, prompts.shape[1]:].cpu()
+    assert load("ops").launch_count() > launches0          # the projections ran in the library
+    assert len(model.ctx.slot_cache) == 2                   # one slot tensor for the prompt pass, one for all decode steps
+    # teacher-forced logits (transformers' own bf16 ops sit between the projections: a wider bar than the engine's)
+    got_logits = model(input_ids=torch.cat([prompts, want_tok[:, :-1]], 1).to(cuda), adapter_names=names).logits.float().cpu()
+    S = prompts.shape[1]
+    torch.testing.assert_close(got_logits[:, S - 1:], want_logits[:, S - 1:], atol=6e-2, rtol=5e-2)
+    agree = (got_logits[:, S - 1:].argmax(-1) == want_tok).float().mean()
+    assert agree >= 0.95, agree
+    # free-running tokens: wherever a row first departs, the CPU model's margin between the two tokens is a near-tie
+    for b in range(4):
+        d = (got_tok[b] != want_tok[b]).nonzero()
+        if len(d):
+            st = int(d[0])
+            lg = want_logits[b, S - 1 + st]
+            assert float(lg[want_tok[b, st]] - lg[got_tok[b, st]]) <= 0.12
+    # adapters matter, and switching them off reproduces the base model
+    with model.disable_adapter():
+        base_logits = model(input_ids=prompts.to(cuda)).logits.float().cpu()
+    want_base = hf_path.forward_logits(cpu, prompts, None)
+    torch.testing.assert_close(base_logits[:, -1], want_base[:, -1], atol=6e-2, rtol=5e-2)
+    assert float((base_logits[:, -1] - got_logits[:, S - 1]).abs().max()) > 0.05
+
+    # hot add / remove of one adapter: the other rows' results do not move, the new adapter takes effect
+    ref_rows = model(input_ids=prompts.to(cuda), adapter_names=names).logits[:, -1].float().cpu()
+    extra = {k: 3.0 * v for k, v in adapter_io.load_adapter(adapter_io.adapter_path(str(tmp_path), r, 1)).items()}
+    model.add_adapter("adapter9", extra, r, alpha)
+    with_new = model(input_ids=prompts.to(cuda), adapter_names=["adapter9"] + names[1:]).logits[:, -1].float().cpu()
+    assert torch.equal(with_new[1:], ref_rows[1:]) and not torch.equal(with_new[0], ref_rows[0])
+    model.remove_adapter("adapter9")
+    again = model(input_ids=prompts.to(cuda), adapter_names=names).logits[:, -1].float().cpu()
+    assert torch.equal(again, ref_rows)

@@ -246,3 +246,58 @@ def test_benchmark_shape_two_layer_truncation_through_graph_replays(cuda):
     assert r["logits_rel"] <= 1.3, r
     assert r["greedy_agree"] >= 0.95, r
     assert r["ids_bit_exact"], r
+
+
+def test_adapters_added_and_removed_while_serving(synth, cuda):
+    """Hot add / remove of adapters: a model built with spare adapter slots takes a new adapter between two decode
+    steps (only that slot's rows are written: the graph captured before keeps replaying over the same buffers),
+    drops one, and reuses the freed slot; every step against the CPU oracle."""
+    cfg, w, ads = _tiny(synth, n_adapters=3, ranks=[8, 16, 8], targets=synth.ATTN_PROJ + synth.MLP_PROJ)
+    scales = [2.0, 1.0, 0.5]
+    model_mod, kv_mod = load("model"), load("kv_cache")
+    pm = model_mod.PackedLlama(cfg, w, ads[:2], scales[:2], device=cuda, adapter_capacity=4, max_rank=16)
+    assert pm.n_adapters == 4 and pm.r_max == 16
+    kv = kv_mod.PagedKVCache(pm.L, pm.Hkv, pm.D, 4, 4 * 64, 64, 16, cuda, max_seq_len=64)
+    eng = model_mod.Engine(pm, kv, 64)
+    P = synth.prompts(4, 30, cfg["vocab_size"])
+    oracle = ollama.OracleLlama(cfg, w, ads, scales)
+    sids = [0, 1, 2, 3]
+    for s in sids:
+        kv.add_sequence(s)
+    ids = [0, 1, -1, 0]
+    want = torch.cat([oracle.prefill(b, list(P[b]), ids[b]) for b in range(4)])
+    lg, tok = eng.prefill(sids, [list(p) for p in P], ids)
+    _check_logits(lg, want)
+    feed = want.argmax(-1).tolist()
+
+    def step(ids, via_graph=None):
+        nonlocal feed
+        want = oracle.decode(sids, feed, ids)
+        if via_graph is not None:
+            eng._stage(eng.slots, ids, torch.int32)
+            eng.tokens[:4].copy_(torch.tensor(feed, dtype=torch.int32))
+            via_graph.replay()
+            lg = eng.logits[:4]
+        else:
+            lg, _ = eng.decode(sids, feed, ids)
+        _check_logits(lg, want)
+        feed = want.argmax(-1).tolist()
+        return lg.float().cpu().clone()
+
+    graph = eng.capture_decode(sids, ids, reserve_tokens=8, feed_back=False)
+    step(ids, graph)
+    slot = pm.add_adapter(ads[2], scales[2])
+    assert slot == 2 and pm.ranks.cpu().tolist() == [8, 16, 8, 0]
+    step([0, 1, 2, 0], graph)               # request 2 moves onto the adapter that has just arrived
+    step([2, 2, 2, 2])                      # eager path, everyone on it
+    pm.remove_adapter(1)
+    assert pm.ranks.cpu().tolist() == [8, 0, 8, 0]
+    step([0, -1, 2, 0], graph)
+    with pytest.raises(ValueError):
+        pm.remove_adapter(1)
+    assert pm.add_adapter(ads[1], scales[1]) == 1   # the freed slot is reused
+    step([0, 1, 2, 1], graph)
+    assert pm.add_adapter(ads[0], 0.25) == 3
+    with pytest.raises(RuntimeError):
+        pm.add_adapter(ads[0], 1.0)                 # capacity exhausted
+    assert eng.status_word() == 0

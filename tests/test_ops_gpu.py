@@ -637,6 +637,15 @@ def test_every_row_its_own_adapter(ops, cuda, T, n_ad, r, K, N):
         torch.testing.assert_close(y, want, atol=ATOL, rtol=RTOL)
     y32 = ops.linear(x.to(cuda), W.to(cuda), st_rm, slots.to(cuda), flags=ops.LORA_PER_ROW | ops.OUT_F32).cpu()
     torch.testing.assert_close(y32, want, atol=ATOL, rtol=RTOL)
+    # the rank-compact split layout (every adapter stored as rank/8 slices [out, 8]): same sums in the same order
+    st_sp = ops.LoraStack(A.to(cuda), B.to(cuda), _i32(ranks, cuda), torch.full((n_ad,), 0.5, device=cuda), r, 1, (0, N))
+    st_sp.split_b(ranks)
+    assert st_sp.B_split.shape == (sum(rk // 8 for rk in ranks), N, 8)          # rank-proportional storage
+    assert st_sp.rank_tbl.cpu().tolist()[:n_ad] == ranks
+    y32s = ops.linear(x.to(cuda), W.to(cuda), st_sp, slots.to(cuda), flags=ops.LORA_PER_ROW | ops.OUT_F32).cpu()
+    assert torch.equal(y32s, y32)
+    ys = ops.linear(x.to(cuda), ops.PackedWeight(W.to(cuda)), st_sp.pack_b(), slots.to(cuda), flags=ops.LORA_PER_ROW).float().cpu()
+    torch.testing.assert_close(ys, want, atol=ATOL, rtol=RTOL)
 
 
 def test_per_row_expand_with_fused_modules(ops, cuda):
@@ -661,3 +670,15 @@ def test_per_row_expand_with_fused_modules(ops, cuda):
         y2 = ops.linear(x.to(cuda), ops.PackedWeight(W.to(cuda)), st.pack_b(), slots.to(cuda), flags=ops.LORA_PER_ROW).float().cpu()
         torch.testing.assert_close(y, want, atol=ATOL, rtol=RTOL)
         torch.testing.assert_close(y2, want, atol=ATOL, rtol=RTOL)
+        # split layout with mixed ranks over the three modules (rank below the pitch for every third adapter)
+        rk = [r if i % 3 else 8 for i in range(n_ad)]
+        A2, B2 = A.clone(), B.clone()
+        for i, q in enumerate(rk):
+            for m in range(3):
+                A2[i, m * r + q:(m + 1) * r] = 0
+            B2[i, :, q:] = 0
+        st2 = _stack(ops, A2, B2, rk, [1.5] * n_ad, cuda, 3, offs)
+        ya = ops.linear(x.to(cuda), W.to(cuda), st2, slots.to(cuda), flags=ops.LORA_PER_ROW | ops.OUT_F32).cpu()
+        st2.split_b(rk)
+        yb = ops.linear(x.to(cuda), W.to(cuda), st2, slots.to(cuda), flags=ops.LORA_PER_ROW | ops.OUT_F32).cpu()
+        assert torch.equal(ya, yb)
