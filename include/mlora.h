@@ -310,6 +310,31 @@ int mlora_paged_attention_static(const void* d_qkv, int64_t ld, void* d_k_pages,
 int mlora_kv_begin_decode(const int32_t* d_row_slot, int32_t* d_seq_lens, int32_t* d_row_pos,
                           int32_t B, void* stream);
 
+/* ---- the batched greedy loop with sequences that finish, without the host in between --------------
+ * The reference's executor reads the logits back after every token, takes the argmax on the host, drops
+ * finished sequences (end-of-sequence token or the sequence's own max_gen_len) and rebuilds the index lists of
+ * the live batch (tvm/llama_auto_batcher/llama_exec_graph.py:94-100, 102-141).  These two calls keep that state
+ * on the device.  The sequences of a fused decode node are held in the order of mlora_bucket_sort (rows without
+ * adapter first, then by adapter); per sequence b: d_live[b], d_seq_slot[b] (KV cache slot), d_adapter_slot[b],
+ * d_last_tok[b], d_gen_count[b], d_max_gen[b], d_out_tokens[b, 0..ld_out).
+ *
+ * mlora_decode_step_begin: stable compaction of the live sequences into rows 0..n_live-1 of a step of n_rows rows
+ * (the adapter order survives); for each: d_row_src = b, d_row_slot, d_row_pos = seq_lens[slot]++ (what
+ * kv_state_begin_forward(kv, seq_ids, [1]*B) does), d_row_adapter, d_row_tok.  Rows n_live..n_rows-1 become
+ * padding: no adapter, position -1 (mlora_paged_attention stores and reads nothing for them), token 0.
+ * *d_n_live = n_live.  n_rows must be >= the number of live sequences.
+ *
+ * mlora_decode_step_end: for every live row i: the new token d_next_tok[i] is appended to d_out_tokens[b,
+ * gen_count[b]++] and becomes d_last_tok[b]; the sequence stops (d_live[b] = 0, *d_n_live decremented) when the
+ * token equals eos_id (pass -1 for none) or gen_count reaches d_max_gen[b] (or ld_out). */
+int mlora_decode_step_begin(const int32_t* d_live, const int32_t* d_seq_slot, const int32_t* d_adapter_slot,
+                            const int32_t* d_last_tok, int32_t n_seq, int32_t n_rows, int32_t* d_seq_lens,
+                            int32_t* d_row_src, int32_t* d_row_slot, int32_t* d_row_pos, int32_t* d_row_adapter,
+                            int32_t* d_row_tok, int32_t* d_n_live, void* stream);
+int mlora_decode_step_end(const int32_t* d_row_src, const int32_t* d_next_tok, int32_t n_rows, int32_t* d_live,
+                          int32_t* d_last_tok, int32_t* d_gen_count, const int32_t* d_max_gen,
+                          int32_t* d_out_tokens, int64_t ld_out, int32_t eos_id, int32_t* d_n_live, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

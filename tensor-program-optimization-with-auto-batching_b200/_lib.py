@@ -53,6 +53,8 @@ PROTOTYPES = {
     "mlora_paged_attention_static": (C.c_int, [_vp, _i64, _vp, _vp, _vp, _i32, _vp, _vp, _i32, _i32, _i32, _i32, _i32,
                                                _f32, _i32, _vp, _i64, _i32, _vp]),
     "mlora_kv_begin_decode": (C.c_int, [_vp, _vp, _vp, _i32, _vp]),
+    "mlora_decode_step_begin": (C.c_int, [_vp, _vp, _vp, _vp, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "mlora_decode_step_end": (C.c_int, [_vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _vp, _vp]),
 }
 
 

@@ -200,8 +200,31 @@ class LlamaExecGraph(ExecGraph):
         eos = getattr(self.tokenizer, "eos_token_id", None)
         return [s for s in live if outputs[s][-1] != eos and len(outputs[s]) < self.seq_info.get_max_gen_len(s)]
 
+    # ``device_loop`` (default): the batch state of a decode node lives on the device (model.DecodeSession): the
+    # batch is ordered once with the device bucket sort, every step is a CUDA-graph replay, finished sequences leave
+    # inside the step, and the host reads 4 bytes per ``sync_every`` steps plus all tokens once at the end.
+    # ``device_loop = False`` runs the reference's host loop below, step for step (kept as the checked slow path).
+    device_loop = True
+    sync_every = 1
+
+    def _decode_on_device(self, op):
+        from .model import DecodeSession
+        live, positions = self.seq_info.order_seqs(op.seqids)
+        slots = [self.vm.slot_of(self.seq_info.get_adapter_info(s)) for s in live]
+        first = [int(op.input_vars[positions[i]].var) for i in range(len(live))]
+        max_gen = [self.seq_info.get_max_gen_len(s) for s in live]
+        sess = DecodeSession(self.vm.engine_for(self.kv_cache), live, slots, first, max_gen,
+                             getattr(self.tokenizer, "eos_token_id", None), use_lora=any(s >= 0 for s in slots))
+        outs = sess.run(self.sync_every)
+        self.decode_steps += sess.steps
+        self.decode_d2h_bytes = getattr(self, "decode_d2h_bytes", 0) + sess.d2h_bytes
+        for i in range(len(live)):
+            op.output_vars[positions[i]].var = torch.tensor(outs[i])
+
     def _decode(self, op):
         assert len(op.input_vars) == len(op.output_vars) == len(op.seqids), "decode node: inputs, outputs and seqids differ"
+        if self.device_loop and isinstance(self.vm, mvm.B200VM):
+            return self._decode_on_device(op)
         gf = mvm.get_global_func
         live, positions = self.seq_info.order_seqs(op.seqids)
         outputs = {sid: [op.input_vars[positions[i]].var] for i, sid in enumerate(live)}

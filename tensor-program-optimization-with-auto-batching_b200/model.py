@@ -598,3 +598,98 @@ class DecodeGraph:
         self._headroom -= 1
         self.graph.replay()
         self.engine.kv.note_device_decode(self.seq_ids)
+
+
+class DecodeSession:
+    """The batched greedy loop of one fused decode node (``tvm/llama_auto_batcher/llama_exec_graph.py:102-141``)
+    with the batch state on the device: sequences finish on their end-of-sequence token or their own
+    ``max_gen_len`` and leave the batch without the host rebuilding anything.  Every step is a CUDA-graph replay
+    of ``decode_step_begin -> forward -> decode_step_end`` captured for a bucket of rows (powers of two up to the
+    node's size); the host only learns the live count (4 bytes, every ``sync_every`` steps) to pick the bucket and
+    to stop, and reads all generated tokens once at the end.
+
+    ``seq_ids`` must already be in bucketing order (``LlamaSeqInfo.order_seqs``): rows of one adapter adjacent."""
+
+    def __init__(self, engine: Engine, seq_ids, adapter_slots, first_tokens, max_gen, eos_id=None, use_lora=True):
+        self.eng, self.seq_ids, self.use_lora = engine, list(seq_ids), use_lora
+        kv, dev, n = engine.kv, engine.m.device, len(seq_ids)
+        self.n = n
+        self.max_len = int(max(max_gen)) + 1  # (a sequence always takes part in the node's first step)
+        i32 = lambda v: torch.as_tensor(np.asarray(v, dtype=np.int32)).pin_memory().to(dev, non_blocking=True)
+        self.live = torch.ones(n, dtype=torch.int32, device=dev)
+        self.seq_slot = i32([kv.slot(s) for s in seq_ids])
+        self.adapter_slot = i32(adapter_slots)
+        self.last_tok = i32(first_tokens)
+        self.max_gen = i32(max_gen)
+        self.gen_count = torch.ones(n, dtype=torch.int32, device=dev)  # the prefill's token is the first one
+        self.out_tokens = torch.zeros(n, self.max_len, dtype=torch.int32, device=dev)
+        self.out_tokens[:, 0] = self.last_tok
+        self.row_src = torch.full((max(n, 1),), -1, dtype=torch.int32, device=dev)
+        self.n_live = torch.zeros(1, dtype=torch.int32, device=dev)
+        self._n_live_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self.eos_id = -1 if eos_id is None else int(eos_id)
+        self.n_distinct = len({int(a) for a in adapter_slots if a >= 0})
+        for sid, g in zip(seq_ids, max_gen):
+            kv.reserve(sid, kv.length(sid) + int(g) + 1)
+        self._graphs = {}
+        self.steps = 0
+        self.d2h_bytes = 0
+
+    def _step(self, rows):
+        e = self.eng
+        ops.decode_step_begin(self.live, self.seq_slot, self.adapter_slot, self.last_tok, rows, e.kv.seq_lens,
+                              self.row_src, e.row_slot, e.row_pos, e.slots, e.tokens, self.n_live)
+        e.n_distinct = self.n_distinct
+        e.forward(rows, True, self.use_lora)
+        ops.decode_step_end(self.row_src, e.next_tok, rows, self.live, self.last_tok, self.gen_count, self.max_gen,
+                            self.out_tokens, self.eos_id, self.n_live)
+
+    def _graph(self, rows):
+        g = self._graphs.get(rows)
+        if g is not None:
+            return g
+        e = self.eng
+        state = (self.live, self.last_tok, self.gen_count, self.out_tokens, e.kv.seq_lens, self.n_live)
+        saved = [t.clone() for t in state]
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self._step(rows)  # warm-up outside capture; its effects are undone below
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self._step(rows)
+        for t, s in zip(state, saved):
+            t.copy_(s)
+        torch.cuda.synchronize()
+        self._graphs[rows] = g
+        return g
+
+    @staticmethod
+    def bucket(n_live, n):
+        """Rows of the step that serves ``n_live`` live sequences: the next power of two, capped at the node's size."""
+        b = 1
+        while b < n_live:
+            b *= 2
+        return min(b, n)
+
+    def run(self, sync_every=1):
+        """Runs until every sequence has finished.  Returns the token lists (first token included) in the order of
+        ``seq_ids``."""
+        bound = self.n  # upper bound of the live count (sequences only ever leave)
+        while bound > 0:
+            g = self._graph(self.bucket(bound, self.n))
+            for _ in range(max(1, sync_every)):
+                g.replay()
+                self.steps += 1
+            self._n_live_host.copy_(self.n_live, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            self.d2h_bytes += 4
+            bound = int(self._n_live_host[0])
+        counts = self.gen_count.cpu().tolist()
+        toks = self.out_tokens.cpu().tolist()
+        self.d2h_bytes += 4 * (self.n + self.out_tokens.numel())
+        for sid, c in zip(self.seq_ids, counts):
+            self.eng.kv.note_device_decode([sid], c - 1)
+        return [t[:c] for t, c in zip(toks, counts)]

@@ -400,5 +400,19 @@ def kv_begin_decode(row_slot, seq_lens, row_pos):
                                            _stream()), "mlora_kv_begin_decode")
 
 
+def decode_step_begin(live, seq_slot, adapter_slot, last_tok, n_rows, seq_lens, row_src, row_slot, row_pos, row_adapter,
+                      row_tok, n_live):
+    check(_lib.lib().mlora_decode_step_begin(_ptr(live), _ptr(seq_slot), _ptr(adapter_slot), _ptr(last_tok), live.numel(),
+                                             n_rows, _ptr(seq_lens), _ptr(row_src), _ptr(row_slot), _ptr(row_pos),
+                                             _ptr(row_adapter), _ptr(row_tok), _ptr(n_live), _stream()),
+          "mlora_decode_step_begin")
+
+
+def decode_step_end(row_src, next_tok, n_rows, live, last_tok, gen_count, max_gen, out_tokens, eos_id, n_live):
+    check(_lib.lib().mlora_decode_step_end(_ptr(row_src), _ptr(next_tok), n_rows, _ptr(live), _ptr(last_tok), _ptr(gen_count),
+                                           _ptr(max_gen), _ptr(out_tokens), out_tokens.stride(0), eos_id, _ptr(n_live),
+                                           _stream()), "mlora_decode_step_end")
+
+
 def launch_count() -> int:
     return int(_lib.lib().mlora_launch_count())

@@ -6,9 +6,13 @@ generation-length table, ``order_seqs`` (stable sort of a batch: no-adapter
 rows first, then adapter type id, then weight id, ``:61-75``) and
 ``get_decode_method`` (per-type position / weight-id lists and the name of the
 decode function to call, ``:77-104``).  The integer work runs in
-``mlora_bucket_sort`` on the GPU; the ``*_device`` variants keep the results
-there (what the fused decode step consumes), the reference-named methods copy
-them back and return the reference's Python lists.
+``mlora_bucket_sort`` on the GPU.  The reference-named methods copy the results
+back and return the reference's Python lists (a synchronising call: the
+executor's device-resident decode loop makes it once per fused decode node, to
+put the batch in adapter order; after that the per-step regrouping the
+reference does on the host is the stable compaction inside
+``mlora_decode_step_begin``).  The ``*_device`` variants leave the results on
+the device for callers that gather by ``perm`` there.
 """
 from __future__ import annotations
 

@@ -116,6 +116,18 @@ class B200VM:
             return mixed
         raise KeyError(name)
 
+    # ---- what the device-resident decode loop needs from the table ---------------------------------------
+    def engine_for(self, kv):
+        """The engine created with this cache by ``create_paged_kv_cache``."""
+        return self._engines[id(kv)]
+
+    def slot_of(self, adapter_info):
+        """Packed-stack slot of ``{"tid", "wid"}`` (None -> -1, no adapter)."""
+        if adapter_info is None:
+            return -1
+        self._check_type(adapter_info["tid"])
+        return self.type_slot_base[adapter_info["tid"]] + int(adapter_info["wid"])
+
     def _check_type(self, t):
         if t >= len(self.type_slot_base):
             raise KeyError(f"adapter type {t} is not loaded")

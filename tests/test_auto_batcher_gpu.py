@@ -44,9 +44,12 @@ def test_graph_fusion_matches_reference_levels():
 
 
 @pytest.mark.gpu
-def test_user_script_flow_matches_oracle(synth, cuda, tmp_path, capsys):
+@pytest.mark.parametrize("loop", ["device", "device_sync4", "host"])
+def test_user_script_flow_matches_oracle(synth, cuda, tmp_path, capsys, loop):
     """The flow of the reference's user_example.py: sequences with no adapter, two types, per-sequence
-    generation lengths; outputs come back per sequence in request order."""
+    generation lengths; outputs come back per sequence in request order.  Run three ways: with the batch state on
+    the device (graph replays, sequences finishing inside the step), the same with the live count read back only
+    every fourth step, and with the reference's host loop; all must give the same tokens."""
     ab, adapters = load("auto_batcher"), load("adapters")
     cfg = synth.llama_config("tiny")
     w = {k: v.bfloat16() for k, v in synth.base_weights(cfg).items()}
@@ -73,10 +76,16 @@ def test_user_script_flow_matches_oracle(synth, cuda, tmp_path, capsys):
         results.append(res)
     B.compile()
     assert B.graph.get_max_batch_sizes() == {"decode": 6}
+    B.graph.device_loop = loop != "host"
+    B.graph.sync_every = 4 if loop == "device_sync4" else 1
     B.execute()
     printed = capsys.readouterr().out
     assert printed.count("Answer for Sequence") == 6
-    assert B.graph.decode_steps == 6  # the longest sequence (7 tokens incl. the prefill token) needs 6 steps
+    # the longest sequence (7 tokens incl. the prefill token) needs 6 steps (8 when the host looks every 4th step)
+    assert B.graph.decode_steps == (8 if loop == "device_sync4" else 6)
+    if loop == "device":
+        # per step the host read back 4 bytes (the live count), and every token once at the end
+        assert B.graph.decode_d2h_bytes == 4 * 6 + 4 * (6 + 6 * 8)
 
     # oracle: same adapters (files -> bf16 like the packed model), slots: type 0 (r16) -> 0..2, type 1 (r8) -> 3,4
     ads = [adapters.load_adapter(adapters.adapter_path(os.path.join(cache, "lora_adapters"), 16, a)) for a in range(3)]

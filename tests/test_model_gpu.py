@@ -301,3 +301,55 @@ def test_adapters_added_and_removed_while_serving(synth, cuda):
     with pytest.raises(RuntimeError):
         pm.add_adapter(ads[0], 1.0)                 # capacity exhausted
     assert eng.status_word() == 0
+
+
+def test_device_resident_decode_loop_with_finishing_sequences(synth, cuda):
+    """``DecodeSession``: twelve sequences with ragged generation limits and an end-of-sequence token leave the batch
+    inside the captured step (stable compaction keeps the adapter order; padding rows write nothing), the host reads
+    the live count only.  Checked against the same loop driven from the host one eager step at a time
+    (llama_exec_graph.py:102-141: decode the live rows, append, drop finished), token for token."""
+    model_mod = load("model")
+    cfg, w, ads = _tiny(synth, n_adapters=4)
+    scales = [2.0] * 4
+    n = 12
+    ids = [-1, -1, 0, 0, 0, 1, 1, 2, 2, 2, 3, 3]           # bucketing order: no adapter first, then by adapter
+    max_gen = [2, 9, 3, 5, 9, 4, 7, 2, 6, 9, 3, 8]
+    P = synth.prompts(n, 20, cfg["vocab_size"])
+    sids = list(range(n))
+
+    def fresh():
+        pm, kv, eng = _engine(cfg, w, ads, scales, n, 40, cuda)
+        for s in sids:
+            kv.add_sequence(s)
+        _, tok = eng.prefill(sids, [list(p) for p in P], ids)
+        return pm, kv, eng, tok.cpu().tolist()
+
+    def host_loop(eos):
+        pm, kv, eng, first = fresh()
+        out = {s: [first[s]] for s in sids}
+        live, steps = list(sids), 0
+        while live:
+            _, tok = eng.decode(live, [out[s][-1] for s in live], [ids[s] for s in live])
+            for s, t in zip(live, tok.cpu().tolist()):
+                out[s].append(t)
+            steps += 1
+            live = [s for s in live if out[s][-1] != eos and len(out[s]) < max_gen[s]]
+        return [out[s] for s in sids], steps, kv
+
+    free_run, _, _ = host_loop(None)
+    eos = free_run[4][3]                                     # a token sequence 4 emits on its third step
+    want, want_steps, kv_h = host_loop(eos)
+    assert len(want[4]) == 4 and any(len(o) < m for o, m in zip(want, max_gen))  # the eos cut something short
+
+    for sync_every in (1, 3):
+        pm, kv, eng, first = fresh()
+        sess = model_mod.DecodeSession(eng, sids, ids, first, max_gen, eos_id=eos)
+        got = sess.run(sync_every)
+        assert got == want
+        assert sess.steps >= want_steps and (sync_every > 1 or sess.steps == want_steps)
+        assert sorted(sess._graphs) == sorted({model_mod.DecodeSession.bucket(b, n) for b in range(1, n + 1)} & set(sess._graphs))
+        assert len(sess._graphs) >= 3                        # the batch shrank through several graph buckets
+        # the cache holds exactly the tokens each sequence consumed: same lengths as after the host loop
+        assert [kv.length(s) for s in sids] == [kv_h.length(s) for s in sids]
+        assert kv.seq_lens[:n].cpu().tolist() == [kv.length(s) for s in sids]
+        assert eng.status_word() == 0
