@@ -189,8 +189,10 @@ def run_13b_tp(args, rank, world, local_rank):
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    coll = sharding.DistCollective() if world > 1 else None
     cfg = synth.llama_config("llama2-13b")
+    coll = None
+    if world > 1:  # the exchange step: NCCL, or the library's own kernel over peer memory
+        coll = sharding.PeerCollective(128, cfg["hidden_size"]) if args.tp_collective == "peer" else sharding.DistCollective()
     L = args.layers or cfg["num_hidden_layers"]
     cfg = dict(cfg, num_hidden_layers=L)
     n_req = n_ad = 128
@@ -248,34 +250,42 @@ def run_13b_tp(args, rank, world, local_rank):
     clocks = sampler.stop() if rank == 0 else None
     status = eng.status_word()
 
-    # the exchange steps of one decode step alone: 2 all-reduces of [128, 5120] bf16 per layer + the token all-gather
-    ms_coll = 0.0
+    # the exchange steps of one decode step alone, each with the residual add + RMSNorm it feeds (2 per layer), in both
+    # forms: NCCL all-reduce + norm kernel, and the fused peer-memory kernel
+    ms_coll = {}
     if world > 1:
-        y = eng.y[:n_req]
-        pair = torch.zeros(n_req, 2, device=dev)
+        y, xn, lnw = eng.y[:n_req], eng.xn[:n_req], pm.layers[0].ln2
+        res_tmp = torch.zeros(n_req, pm.H, device=dev)
+        forms = {"nccl": sharding.DistCollective()}
+        if args.tp_collective == "peer":
+            forms["peer"] = coll
 
-        def exchanges():
+        def exchanges(c):
+            fused = getattr(c, "allreduce_rmsnorm", None)
             for _ in range(2 * pm.L):
-                coll.all_reduce_sum(y)
-            coll.all_gather(pair)
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            exchanges()
-        torch.cuda.current_stream().wait_stream(side)
-        torch.cuda.synchronize()
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            exchanges()
-        for _ in range(3):
-            g.replay()
-        barrier()
-        e0.record()
-        for _ in range(10):
-            g.replay()
-        e1.record()
-        barrier()
-        ms_coll = max_over_ranks(e0.elapsed_time(e1)) / 10
+                if fused is None or not fused(y, res_tmp, lnw, pm.eps, xn):
+                    c.all_reduce_sum(y)
+                    ops.residual_rmsnorm(y, res_tmp, lnw, pm.eps, out=xn)
+        for name, c in forms.items():
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                exchanges(c)
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                exchanges(c)
+            for _ in range(3):
+                g.replay()
+            barrier()
+            e0.record()
+            for _ in range(10):
+                g.replay()
+            e1.record()
+            barrier()
+            ms_coll[name] = max_over_ranks(e0.elapsed_time(e1)) / 10
+            del g
 
     peak, src = measured_peak()
     H, I, V = 5120, 13824, 32000
@@ -295,9 +305,12 @@ def run_13b_tp(args, rank, world, local_rank):
                          "mean_ctx": ctx_mean, "parallelism": f"tp{world} (Megatron column/row + NCCL all-reduce)"},
               "per_rank": {"algorithmic_bytes": per_rank, "achieved_gbs": per_rank / (ms_step * 1e6),
                            "hbm_frac": per_rank / (ms_step * 1e6) / peak, "peak_gbs": peak, "peak_source": src},
-              "collectives": {"all_reduces_per_step": 2 * L, "bytes_each": n_req * H * 2,
-                              "ms_alone_per_step": ms_coll, "share_of_step": ms_coll / ms_step if ms_step else None,
-                              "impl": "NCCL via torch.distributed, captured in the step's CUDA graph"},
+              "collectives": {"exchanges_per_step": 2 * L, "bytes_each": n_req * H * 2,
+                              "impl_in_step": "fused peer-memory kernel (mlora_tp_allreduce_rmsnorm)" if args.tp_collective == "peer"
+                              else "NCCL all-reduce via torch.distributed + norm kernel",
+                              "ms_alone_per_step_with_their_norms": ms_coll,
+                              "share_of_step": (ms_coll.get(args.tp_collective, 0.0) / ms_step) if ms_step else None,
+                              "peer_status": coll.status() if args.tp_collective == "peer" and world > 1 else None},
               "clocks": clocks, "prefill_seconds_untimed": prefill_s, "tc_status_word": status})
     if world > 1:
         # The step's CUDA graph holds NCCL kernels: tearing the process group down while such graphs exist was seen
@@ -856,6 +869,9 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="debug: truncate the model (the number is then not a bench value)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-operator", action="store_true", help="skip the operator micro-benchmark rows")
+    ap.add_argument("--tp-collective", default="nccl", choices=["nccl", "peer"],
+                    help="13b-tp workload: the exchange after row-parallel projections -- NCCL all-reduce + norm kernel, or "
+                         "the library's fused peer-memory kernel")
     ap.add_argument("--skip-prefill", action="store_true",
                     help="profiling aid: fill the KV cache with seeded random values instead of running prefill "
                          "(the number is then not a bench value)")

@@ -310,6 +310,33 @@ int mlora_paged_attention_static(const void* d_qkv, int64_t ld, void* d_k_pages,
 int mlora_kv_begin_decode(const int32_t* d_row_slot, int32_t* d_seq_lens, int32_t* d_row_pos,
                           int32_t B, void* stream);
 
+/* ---- tensor parallelism: the exchange after a row-parallel projection, over peer memory ---------------
+ * (The reference is single-device; this is the Megatron-style split of the same decoder layer,
+ * tvm/llama_auto_batcher/llama_for_causal_lm.py:71-84: o and down produce partial sums on every rank.)
+ * One process per GPU.  mlora_tp_create allocates this rank's arena (device memory, once, at set-up);
+ * mlora_tp_export writes its 64-byte CUDA IPC handle, which the ranks exchange by any means;
+ * mlora_tp_connect maps a peer's arena.  Then, on every rank, in the same order:
+ *   mlora_tp_allreduce_rmsnorm:  s = sum over ranks of d_partial (bf16 [T,H], summed in rank order in fp32,
+ *     rounded to bf16);  d_res != NULL: res += s, d_out = RMSNorm(res) * w (what all-reduce followed by
+ *     mlora_residual_rmsnorm gives);  d_res == NULL: d_out = s (a plain all-reduce; d_out may be d_partial).
+ * ONE kernel per rank: it stores its rows into the peers' arenas over NVLink, sets a per-row flag there, waits
+ * (bounded) for the peers' rows to land in its own arena, and reduces locally.  T <= 512 and <= T_max, H <= 8192.
+ * The calls of the ranks must pair up one to one; a rank whose peer's rows do not arrive within the spin limit
+ * (mlora_tp_set_spin_limit polls of ~100 ns; default 2^22) sets bit g (rank g missing) in its status word
+ * (mlora_tp_status), produces garbage for that exchange and returns -- it does not hang.  After such a failure
+ * all ranks call mlora_tp_reset between two host-side barriers.  Peers must stay alive (and must not destroy
+ * their arena) while any rank may still launch an exchange. */
+size_t mlora_tp_arena_bytes(int32_t T_max, int32_t H);
+int mlora_tp_create(int32_t rank, int32_t world, int32_t T_max, int32_t H, void** ctx_out);
+int mlora_tp_export(void* ctx, void* handle_out64);
+int mlora_tp_connect(void* ctx, int32_t peer_rank, const void* handle64);
+int mlora_tp_set_spin_limit(void* ctx, uint32_t polls);
+int mlora_tp_status(void* ctx, int32_t* status_out);
+int mlora_tp_reset(void* ctx);
+int mlora_tp_destroy(void* ctx);
+int mlora_tp_allreduce_rmsnorm(void* ctx, const void* d_partial, float* d_res, const void* d_w, float eps,
+                               void* d_out, int32_t T, int32_t H, void* stream);
+
 /* ---- the batched greedy loop with sequences that finish, without the host in between --------------
  * The reference's executor reads the logits back after every token, takes the argmax on the host, drops
  * finished sequences (end-of-sequence token or the sequence's own max_gen_len) and rebuilds the index lists of

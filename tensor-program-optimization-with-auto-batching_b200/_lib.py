@@ -53,6 +53,15 @@ PROTOTYPES = {
     "mlora_paged_attention_static": (C.c_int, [_vp, _i64, _vp, _vp, _vp, _i32, _vp, _vp, _i32, _i32, _i32, _i32, _i32,
                                                _f32, _i32, _vp, _i64, _i32, _vp]),
     "mlora_kv_begin_decode": (C.c_int, [_vp, _vp, _vp, _i32, _vp]),
+    "mlora_tp_arena_bytes": (_sz, [_i32, _i32]),
+    "mlora_tp_create": (C.c_int, [_i32, _i32, _i32, _i32, C.POINTER(_vp)]),
+    "mlora_tp_export": (C.c_int, [_vp, _vp]),
+    "mlora_tp_connect": (C.c_int, [_vp, _i32, _vp]),
+    "mlora_tp_set_spin_limit": (C.c_int, [_vp, C.c_uint32]),
+    "mlora_tp_status": (C.c_int, [_vp, C.POINTER(_i32)]),
+    "mlora_tp_reset": (C.c_int, [_vp]),
+    "mlora_tp_destroy": (C.c_int, [_vp]),
+    "mlora_tp_allreduce_rmsnorm": (C.c_int, [_vp, _vp, _vp, _vp, _f32, _vp, _i32, _i32, _vp]),
     "mlora_decode_step_begin": (C.c_int, [_vp, _vp, _vp, _vp, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "mlora_decode_step_end": (C.c_int, [_vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _vp, _vp]),
 }

@@ -341,6 +341,17 @@ class Engine:
         cap = ((64 if bn == 128 else 16) * 1024) // (bn * stack.r_max * 2)
         return flags | LORA_PER_ROW if self.n_distinct > max(cap, 1) else flags
 
+    def _reduce_norm(self, delta, res, w, out, reduce=True):
+        """res += delta (summed over the tensor-parallel ranks when ``delta`` is a row-parallel partial), out =
+        RMSNorm(res) * w: one fused exchange kernel when the collective has one, else all-reduce + norm kernel."""
+        m = self.m
+        if m.tp_size > 1 and reduce and delta is not None:
+            fused = getattr(self.coll, "allreduce_rmsnorm", None)
+            if fused is not None and fused(delta, res, w, m.eps, out):
+                return
+            self.coll.all_reduce_sum(delta)
+        ops.residual_rmsnorm(delta, res, w, m.eps, out=out)
+
     def _proj(self, x, W, stack, slots, out, flags=0):
         T = x.shape[0]
         if stack is not None and slots is not None:
@@ -434,7 +445,7 @@ class Engine:
         for l, lw in enumerate(m.layers):
             st = lw.lora.get("qkv")
             if (st is not None and slots is not None and T < 256 and m.H <= 8192 and self.fuse_norm_shrink
-                    and self._full_rank(st)):  # (the fused kernel reads every rank row of the pitch)
+                    and m.tp_size == 1 and self._full_rank(st)):  # (the fused kernel reads every rank row of the pitch)
                 # one launch: residual add + RMSNorm + the shrink that reads the normalised rows
                 r_tot = st.r_max * st.n_mod
                 u = self.u.view(-1)[: T * r_tot].view(T, r_tot)
@@ -442,7 +453,7 @@ class Engine:
                 res, res_other = res_other, res
                 ops.linear(xn, lw.w_qkv, st, slots, u=u, flags=self._lora_flags(T, st, 0), out=qkv, work=self.ws_linear)
             else:
-                ops.residual_rmsnorm(delta, res, lw.ln1, m.eps, out=xn)
+                self._reduce_norm(delta, res, lw.ln1, xn, reduce=l > 0)
                 self._proj(xn, lw.w_qkv, st, slots, qkv)
             kp, vp = kv.k_pages(l), kv.v_pages(l)
             if not fused_append:
@@ -451,15 +462,12 @@ class Engine:
             ops.paged_attention(qkv, kp, vp, kv.block_table, row_slot, row_pos, m.Hq, m.Hkv, m.D, kv.page_size,
                                 m.theta, fused_append, out=attn, work=self.ws_attn)
             self._proj(attn, lw.w_o, lw.lora.get("o"), slots, y)
-            if m.tp_size > 1:
-                self.coll.all_reduce_sum(y)  # row-parallel partials (base + LoRA) -> full o_proj output
-            ops.residual_rmsnorm(y, res, lw.ln2, m.eps, out=xn)
+            # row-parallel partials (base + LoRA) -> full o_proj output, added to the residual, normalised
+            self._reduce_norm(y, res, lw.ln2, xn)
             self._proj(xn, lw.w_gu, lw.lora.get("gu"), slots, act, flags=SILU_MUL)
             self._proj(act, lw.w_down, lw.lora.get("down"), slots, y)
-            if m.tp_size > 1:
-                self.coll.all_reduce_sum(y)
-            delta = y
-        ops.residual_rmsnorm(delta, res, m.norm, m.eps, out=xn)
+            delta = y  # (under tensor parallelism still a partial sum: reduced together with the next norm)
+        self._reduce_norm(delta, res, m.norm, xn)
         if lm_rows is not None:
             xl = ops.embed(lm_rows[:n_lm], xn, out_bf16=self.xn_last[:n_lm])  # row gather
         else:

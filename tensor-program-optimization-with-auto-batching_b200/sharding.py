@@ -92,6 +92,81 @@ class DistCollective:
         return out
 
 
+class PeerCollective:
+    """The exchange step in the library's own kernel (``mlora_tp_allreduce_rmsnorm``): every rank stores its partial
+    rows into the peers' memory over NVLink and reduces what lands in its own, fused with the residual add + RMSNorm
+    that follows -- one launch where the NCCL form takes an all-reduce and a norm kernel.  One process per GPU; the
+    arenas are exchanged as CUDA IPC handles through the process group at construction.  Row counts beyond the
+    kernel's limit (prefill passes) and the small token all-gather go through ``DistCollective``."""
+
+    MAX_ROWS = 512
+
+    def __init__(self, max_rows, hidden, group=None):
+        import ctypes as C
+
+        import torch
+        import torch.distributed as dist
+
+        from . import _lib
+        self._lib, self._check, self._C, self._torch = _lib.lib(), _lib.check, C, torch
+        self.dist, self.group = dist, group
+        self.size, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.max_rows, self.hidden = min(int(max_rows), self.MAX_ROWS), int(hidden)
+        self.fallback = DistCollective(group)
+        ctx = C.c_void_p()
+        self._check(self._lib.mlora_tp_create(self.rank, self.size, self.max_rows, self.hidden, C.byref(ctx)), "mlora_tp_create")
+        self.ctx = ctx
+        mine = (C.c_ubyte * 64)()
+        self._check(self._lib.mlora_tp_export(ctx, mine), "mlora_tp_export")
+        handles = [None] * self.size
+        dist.all_gather_object(handles, bytes(mine), group=group)
+        for g, h in enumerate(handles):
+            if g != self.rank:
+                self._check(self._lib.mlora_tp_connect(ctx, g, (C.c_ubyte * 64).from_buffer_copy(h)), "mlora_tp_connect")
+        dist.barrier(group=group)
+
+    def _fits(self, t):
+        return t.dim() == 2 and t.shape[0] <= self.max_rows and t.shape[1] == self.hidden and t.dtype == self._torch.bfloat16 \
+            and t.is_contiguous()
+
+    def _stream(self):
+        return self._C.c_void_p(self._torch.cuda.current_stream().cuda_stream)
+
+    def all_reduce_sum(self, t):
+        if not self._fits(t):
+            return self.fallback.all_reduce_sum(t)
+        p = self._C.c_void_p(t.data_ptr())
+        self._check(self._lib.mlora_tp_allreduce_rmsnorm(self.ctx, p, None, None, 0.0, p, t.shape[0], t.shape[1], self._stream()),
+                    "mlora_tp_allreduce_rmsnorm")
+
+    def allreduce_rmsnorm(self, partial, res, w, eps, out):
+        """res += sum over ranks of ``partial``; out = RMSNorm(res) * w.  False when the shape does not fit the kernel
+        (the caller then takes all_reduce_sum + the norm kernel)."""
+        if not self._fits(partial):
+            return False
+        vp = lambda t: self._C.c_void_p(t.data_ptr())
+        self._check(self._lib.mlora_tp_allreduce_rmsnorm(self.ctx, vp(partial), vp(res), vp(w), float(eps), vp(out), partial.shape[0],
+                                                         partial.shape[1], self._stream()), "mlora_tp_allreduce_rmsnorm")
+        return True
+
+    def all_gather(self, t):
+        return self.fallback.all_gather(t)
+
+    def status(self):
+        v = self._C.c_int32(0)
+        self._check(self._lib.mlora_tp_status(self.ctx, self._C.byref(v)), "mlora_tp_status")
+        return int(v.value)
+
+    def set_spin_limit(self, polls):
+        self._check(self._lib.mlora_tp_set_spin_limit(self.ctx, int(polls)), "mlora_tp_set_spin_limit")
+
+    def reset(self):
+        """After a failed exchange: every rank, between two barriers."""
+        self.dist.barrier(group=self.group)
+        self._check(self._lib.mlora_tp_reset(self.ctx), "mlora_tp_reset")
+        self.dist.barrier(group=self.group)
+
+
 class ThreadCollective:
     """The same interface for G ranks that run as threads of ONE process on ONE GPU (tests on a single
     device: kernels that wait on one another must not run as separate processes there).  Host-side
