@@ -104,3 +104,95 @@ def test_user_script_flow_matches_oracle(synth, cuda, tmp_path, capsys, loop):
             k = next(j for j in range(gen) if got[j] != want[j])
             lg = want_logits[k][0]
             assert float(lg[want[k]] - lg[got[k]]) <= 4e-2, (i, k)
+
+
+@pytest.mark.gpu
+def test_user_defined_adapter_class_runs_through_the_auto_batcher(synth, cuda, tmp_path):
+    """A user-defined adapter other than the default ``Lora`` (compile_tvm.py:29-113: define_parameters,
+    weight_computation, weight_application, post_computation): three declared parameters, a per-output magnitude
+    folded into the second factor by ``weight_computation``.  Its files (a third tensor next to lora_A / lora_B)
+    go through ``compile`` -- validation, probing, one-off weight computation, packing -- and the GPU decodes with
+    it; the oracle gets the folded factors computed here by hand."""
+    import dataclasses
+
+    ab, adapters, ac = load("auto_batcher"), load("adapters"), load("adapter_contract")
+    Tensor, nn, op = ac.Tensor, ac.nn, ac.op
+
+    @dataclasses.dataclass(frozen=True)
+    class MagConfig:
+        r: int
+        alpha: float
+
+    class MagnitudeLora(nn.Module):
+        def __init__(self, in_features: int, out_features: int, config: MagConfig):
+            super().__init__()
+            self.c = config.alpha / config.r
+
+        def define_parameters(self, in_features: int, out_features: int, config: MagConfig) -> tuple[Tensor, Tensor, Tensor]:
+            return (nn.Parameter((in_features, config.r)), nn.Parameter((config.r, out_features)),
+                    nn.Parameter((1, out_features)))
+
+        def weight_computation(self, a: Tensor, b: Tensor, m: Tensor) -> tuple[Tensor, Tensor]:
+            return a, op.multiply(b, m)
+
+        def weight_application(self, x: Tensor, a: Tensor, bm: Tensor) -> Tensor:
+            return op.matmul(op.matmul(x, a), bm)
+
+        def post_computation(self, y: Tensor) -> Tensor:
+            return y * self.c
+
+    ac.register_adapter(MagConfig, MagnitudeLora)
+    cfg = synth.llama_config("tiny")
+    w = {k: v.bfloat16() for k, v in synth.base_weights(cfg).items()}
+    cache = str(tmp_path)
+    directory = os.path.join(cache, "lora_adapters")
+    adapters.write_adapter_files(directory, cfg, ranks=[8], n_adapters=2, scaling_factor=0.05)
+    g = torch.Generator().manual_seed(9)
+    folded = []
+    for a in range(2):  # add the magnitude tensors to the files; fold them by hand for the oracle
+        path = adapters.adapter_path(directory, 8, a)
+        t = adapters.load_adapter(path)
+        low = {}
+        for k in [k for k in t if k.endswith("lora_B.weight")]:
+            m = torch.rand(1, t[k].shape[0], generator=g) + 0.5
+            t[k.replace("lora_B", "p2")] = m
+            low[k] = (t[k] * m.t()).bfloat16()
+            low[k.replace("lora_B", "lora_A")] = t[k.replace("lora_B", "lora_A")].bfloat16()
+        adapters.save_adapter(path, t)
+        folded.append(low)
+
+    P = synth.prompts(3, 17, cfg["vocab_size"])
+    plan = [(0, 5), (1, 5), (None, 4)]
+    B = ab.LlamaAutoBatcherClass()
+    B.set_device(cuda)
+    B.set_model_config(cfg)
+    B.set_weights(w)
+    B.set_cache_dir(cache)
+    B.set_tokenizer(ListTokenizer())
+    B.set_exec_config(ab.LlamaExecConfig(max_prompt_len=32, max_gen_len=8, page_size=16))
+    results = []
+    for i, (wid, gen) in enumerate(plan):
+        var = B.create_var(P[i].tolist())
+        if wid is not None:
+            B.set_adapter(MagConfig(r=8, alpha=4.0), wid=wid)
+        results.append(B.generate(var, max_gen_len=gen))
+    B.compile()
+    B.execute()
+    oracle = ollama.OracleLlama(cfg, w, folded, [0.5, 0.5])
+    plain = ollama.OracleLlama(cfg, w, [adapters.load_adapter(adapters.adapter_path(directory, 8, a)) for a in range(2)], [0.5, 0.5])
+    for i, (wid, gen) in enumerate(plan):
+        got = results[i].var
+        assert len(got) == gen
+        for o in (oracle, plain):
+            o.k_cache.clear()
+            o.v_cache.clear()
+        want_tok, want_logits = oracle.greedy([P[i].tolist()], [-1 if wid is None else wid], gen)
+        want = want_tok[0].tolist()
+        if got != want:
+            k = next(j for j in range(gen) if got[j] != want[j])
+            lg = want_logits[k][0]
+            assert float(lg[want[k]] - lg[got[k]]) <= 4e-2, (i, k)
+    # the magnitude matters: without the fold the first adapter's prefill logits differ visibly
+    a0 = oracle.prefill(100, P[0].tolist(), 0)
+    b0 = plain.prefill(100, P[0].tolist(), 0)
+    assert float((a0 - b0).abs().max()) > 1e-3
