@@ -172,6 +172,77 @@ def run_13b_shape(args):
           "status": eng.status_word()})
 
 
+def run_prefill_heavy(args):
+    """Side measurement (its own JSON line): the prefill-heavy configuration on one GPU -- Llama-2-7B shape, 64
+    requests x 512-token prompts, 64 rank-64 adapters on all seven projections, adapter ids Zipf(1.1) (skewed segment
+    sizes for the grouped shrink), then 16 greedy decode tokens.  Prefill is timed with CUDA events over the engine's
+    own passes (8 passes of 4096 rows); flops are the algorithmic ones of the workload."""
+    import numpy as np
+    import torch
+
+    ops, synth, model_mod, kv_mod = load("ops"), load("synth"), load("model"), load("kv_cache")
+    load("build").build()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    cfg = synth.llama_config("llama2-7b")
+    L = args.layers or cfg["num_hidden_layers"]
+    cfg = dict(cfg, num_hidden_layers=L)
+    n_req = n_ad = 64
+    rank, prompt_len, gen = 64, 512, 16
+    w = synth.base_weights(cfg, dtype=torch.bfloat16, device=dev)
+    ads = synth.lora_adapters(cfg, n_ad, rank, targets=synth.ATTN_PROJ + synth.MLP_PROJ, dtype=torch.bfloat16, device=dev)
+    pm = model_mod.PackedLlama(cfg, w, ads, [0.5] * n_ad, device=dev)
+    del w, ads
+    torch.cuda.empty_cache()
+    ids = [int(i) for i in synth.adapter_ids_zipf(n_req, n_ad)]
+    prompts = [p.tolist() for p in synth.prompts(n_req, prompt_len, cfg["vocab_size"])]
+    max_len = prompt_len + gen + 4
+    sids = list(range(n_req))
+    times = []
+    for rep in range(2):  # first pass warms up (lazy kernel loading); the second is the measured one
+        kv = kv_mod.PagedKVCache(pm.L, pm.Hkv, pm.D, n_req, n_req * max_len, prompt_len, PAGE, dev, max_seq_len=max_len)
+        eng = model_mod.Engine(pm, kv, max_rows=4096)
+        for sid in sids:
+            kv.add_sequence(sid)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        _, first_tok = eng.prefill(sids, prompts, ids)
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+        if rep == 0:
+            del eng, kv
+            torch.cuda.empty_cache()
+    ms_prefill = times[-1]
+    graph = eng.capture_decode(sids, ids, reserve_tokens=gen + 2)
+    eng.tokens[:n_req].copy_(first_tok)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    graph.replay()
+    e0.record()
+    for _ in range(gen - 1):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    ms_decode = e0.elapsed_time(e1) / (gen - 1)
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    tokens = n_req * prompt_len
+    base = 2.0 * (4 * H * H + 3 * H * I) * tokens * L
+    lora = 2.0 * rank * (4 * (H + H) + 2 * (H + I) + (I + H)) * tokens * L
+    attn = 4.0 * H * L * n_req * prompt_len * (prompt_len + 1) / 2
+    head = 2.0 * V * H * n_req
+    peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
+    tpk = float(peaks.get("bf16_tflops_sustained", 1400.0))
+    fl = base + lora + attn + head
+    emit({"workload": "llama2-7b shape, prefill-heavy", "layers": L, "requests": n_req, "prompt_len": prompt_len,
+          "adapters": n_ad, "adapter_rank": rank, "adapter_targets": "q/k/v/o/gate/up/down", "adapter_ids": "Zipf(1.1) seed 3",
+          "distinct_adapters_in_batch": len(set(ids)), "prefill_ms": ms_prefill, "prefill_tokens_per_s": tokens / ms_prefill * 1e3,
+          "prefill_tflops": fl / ms_prefill / 1e9, "flops": {"base": base, "lora": lora, "attention": attn, "lm_head": head},
+          "peak_tflops_sustained": tpk, "frac_of_tensor_peak": fl / ms_prefill / 1e9 / tpk,
+          "decode_ms_per_step": ms_decode, "decode_tokens_per_s": n_req / ms_decode * 1e3, "decode_tokens": gen,
+          "tc_status_word": eng.status_word(), "dtype": "bf16", "data": "synthetic"})
+
+
 def run_13b_tp(args, rank, world, local_rank):
     """The tensor-parallel configuration: Llama-2-13B shape, 128 requests, prompt lengths U[128,1024], 128 adapters
     with ranks cycling 8/16/32/64 on q/k/v/o, paged KV (block 16), tensor parallel size = number of ranks
@@ -747,6 +818,66 @@ def run_kernel_case(which):
         emit({"kernel_case": which, "us_per_launch": us, "algorithmic_bytes": by, "achieved_gbs": by / us / 1e3,
                           "frac_of_peak": by / us / 1e3 / peak, "peak_source": src, "launches": ops.launch_count()})
         return
+    elif which == "chain":
+        # one layer segment of the benchmark's model as ONE persistent launch (mlora_decode_chain): o -> norm -> gate|up
+        # -> down -> norm + q/k/v shrink -> q/k/v, 32 rows, 16 rank-16 adapters on q/k/v/o; two weight sets = 810 MB
+        model_mod = load("model")
+        H, I, r = 4096, 11008, RANK
+        g = torch.Generator(device=dev).manual_seed(0)
+        mat = lambda o, i: (torch.randn(o, i, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+
+        def stack(in_f, outs):
+            n_mod = len(outs)
+            A = ((torch.rand(N_ADAPTERS, n_mod * r, in_f, device=dev, generator=g) * 2 - 1) / in_f ** 0.5).to(torch.bfloat16)
+            B = (torch.randn(N_ADAPTERS, sum(outs), r, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+            offs = [0]
+            for o in outs:
+                offs.append(offs[-1] + o)
+            return ops.LoraStack(A, B, torch.full((N_ADAPTERS,), r, dtype=torch.int32, device=dev),
+                                 torch.full((N_ADAPTERS,), ALPHA / RANK, device=dev), r, n_mod, tuple(offs)).pack_b()
+        sets = []
+        for _ in range(2):
+            sets.append(dict(w_o=ops.PackedWeight(mat(H, H)), w_gu=ops.PackedWeight(model_mod.interleave_gate_up(mat(I, H), mat(I, H))),
+                             w_down=ops.PackedWeight(mat(H, I)), w_qkv=ops.PackedWeight(mat(3 * H, H)),
+                             st_o=stack(H, [H]), st_qkv=stack(H, [H, H, H])))
+        ln = (1 + 0.1 * torch.randn(H, device=dev, generator=g)).to(torch.bfloat16)
+        attn = torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16)
+        res = torch.randn(T, H, device=dev, generator=g)
+        y, xn, act, qkv = (torch.zeros(T, n, dtype=torch.bfloat16, device=dev) for n in (H, H, I, 3 * H))
+        u = torch.zeros(T, 3 * r, dtype=torch.float32, device=dev)
+        slots = torch.from_numpy(synth.adapter_ids_uniform(T, N_ADAPTERS)).to(dev)
+        lib = load("_lib").lib()
+        work = ops.new_workspace(max(lib.mlora_linear_workspace(T, k, n) for k, n in ((H, H), (H, 2 * I), (I, H), (H, 3 * H))), dev)
+
+        def segment(c):
+            S = ops.ChainStep
+            ops.decode_chain([S(x=attn, W=c["w_o"], y=y, stack=c["st_o"], u=u.view(-1)[: T * r].view(T, r)),
+                              S(x=xn, W=c["w_gu"], y=act, flags=ops.SILU_MUL, res=res, delta=y, norm_w=ln, eps=1e-5),
+                              S(x=act, W=c["w_down"], y=y),
+                              S(x=xn, W=c["w_qkv"], y=qkv, res=res, delta=y, norm_w=ln, eps=1e-5, stack=c["st_qkv"], u=u)],
+                             slots, c["st_o"].ranks, c["st_o"].scales, N_ADAPTERS, work)
+        for i in range(4):
+            segment(sets[i % 2])
+        torch.cuda.synchronize()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            for c in sets:
+                segment(c)
+        for _ in range(3):
+            gr.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(10):
+            gr.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        us = 1e3 * e0.elapsed_time(e1) / 20
+        n_uniq = len(set(slots.tolist()))
+        by = 2 * (4 * H * H + 3 * H * I) + n_uniq * 2 * r * (H + H + H + 3 * H) + 2 * T * (H + H + I + H) + 2 * T * (H + I + H + 3 * H) + 2 * 8 * T * H
+        peak, src = measured_peak()
+        emit({"kernel_case": which, "us_per_launch": us, "algorithmic_bytes": by, "achieved_gbs": by / us / 1e3,
+              "frac_of_peak": by / us / 1e3 / peak, "peak_source": src, "status": ops.status_word(work), "launches": ops.launch_count()})
+        return
     elif which == "expand":
         # a 13B-shaped projection (5120 x 5120) over 128 rows that each bring their own adapter (128 adapters, ranks
         # cycling 8/16/32/64 in a pitch-64 stack): base projection + per-row expand, CUDA-event timed in a graph
@@ -875,12 +1006,13 @@ def main():
     ap.add_argument("--skip-prefill", action="store_true",
                     help="profiling aid: fill the KV cache with seeded random values instead of running prefill "
                          "(the number is then not a bench value)")
-    ap.add_argument("--kernel-case", default="", choices=["", "linear", "attention", "operator", "prefill", "expand"],
+    ap.add_argument("--kernel-case", default="", choices=["", "linear", "attention", "operator", "prefill", "expand", "chain"],
                     help="profiling aid: launch one kernel a few times on a small case (> L2, < 1 GB) and exit")
-    ap.add_argument("--workload", default="", choices=["", "13b-shape", "13b-tp"],
+    ap.add_argument("--workload", default="", choices=["", "13b-shape", "13b-tp", "prefill-heavy"],
                     help="side measurements (own JSON line, not the benchmark's): 13b-shape = the 13B shape and adapter "
                          "mix on one GPU; 13b-tp = the tensor-parallel configuration, tp size = number of ranks "
-                         "(launch with torch.distributed.run)")
+                         "(launch with torch.distributed.run); prefill-heavy = 64 x 512-token prompts, 64 rank-64 adapters on "
+                         "seven projections, Zipf ids, 16 decode tokens")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -895,6 +1027,8 @@ def main():
         run_13b_shape(args)
     elif args.workload == "13b-tp":
         run_13b_tp(args, rank, world, local_rank)
+    elif args.workload == "prefill-heavy":
+        run_prefill_heavy(args)
     elif args.kernel_case:
         run_kernel_case(args.kernel_case)
     elif args.impl == "reference":

@@ -90,7 +90,7 @@ template <int BN>
 struct Cfg {
   static constexpr int kWBytes = BM * BK * 2;
   static constexpr int kXBytes = BN * BK * 2;
-  static constexpr int kXStages = 16;  // token tiles come from L2, but behind the weight requests: a deep ring
+  static constexpr int kXStages = 8;  // token tiles come from L2: a shallow ring leaves the shared memory to the weight stream
   static constexpr int kCacheBytes = 16 * 1024;  // LoRA B operands (scaled, masked shrink outputs) of the token tile
   static constexpr int kOutBytes = 32 * BM * 4;  // staging of one 32-token output chunk
   static constexpr int kAuxBytes = 1024 + 5 * BN * 4 + kCacheBytes + kOutBytes;

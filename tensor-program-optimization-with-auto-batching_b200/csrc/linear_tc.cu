@@ -855,10 +855,24 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
 #pragma unroll
           for (int i = 0; i < C::kChunk; ++i) pre[i] = 0.f;
           if (pre_have) {
-            for (int cc = c_first + 1; cc <= c_last; ++cc) {  // CTA order: deterministic
+            // CTA order: deterministic.  Two contributors' partials are requested together: each is a round trip to
+            // L2 (or DRAM, behind the weight stream), and tiles of narrow projections have four or five of them.
+            for (int cc = c_first + 1; cc <= c_last; cc += 2) {
               const float* ps = p.partials + ((size_t)cc * 2) * (size_t)(BN * BM);
+              const bool two = cc + 1 <= c_last;
+              float a0[C::kChunk], a1[C::kChunk];
 #pragma unroll
-              for (int i = 0; i < C::kChunk; ++i) pre[i] += __ldcg(ps + (size_t)i * BM + etid);
+              for (int i = 0; i < C::kChunk; ++i) a0[i] = __ldcg(ps + (size_t)i * BM + etid);
+              if (two) {
+#pragma unroll
+                for (int i = 0; i < C::kChunk; ++i) a1[i] = __ldcg(ps + (size_t)2 * (BN * BM) + (size_t)i * BM + etid);
+              }
+#pragma unroll
+              for (int i = 0; i < C::kChunk; ++i) pre[i] += a0[i];
+              if (two) {
+#pragma unroll
+                for (int i = 0; i < C::kChunk; ++i) pre[i] += a1[i];
+              }
             }
           }
           epi_bar_sync();  // s_last is reused by the next split segment
@@ -908,9 +922,10 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&acc_empty[buf]);
-          __threadfence();
+          // the CTA-wide barrier orders every thread's partial stores before thread 0's release, which publishes
+          // them (cumulatively) to the finisher's acquire: one fence instead of one per thread
           epi_bar_sync();
-          if (etid == 0) atomicAdd(&p.tickets[c_first], 1);
+          if (etid == 0) asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(p.tickets + c_first) : "memory");
         } else if constexpr (BN <= 32) {
           float v[32];
           if (BN >= 32) tmem_ld32(t_addr, v); else tmem_ld16(t_addr, v);

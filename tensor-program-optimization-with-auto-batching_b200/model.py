@@ -306,6 +306,8 @@ class Engine:
         # decode-size passes can run everything between two attention calls as one persistent launch
         # (mlora_decode_chain); measured slower than the separate launches on the benchmark's step, so off unless asked for
         self.use_chain = os.environ.get("MLORA_CHAIN", "0") == "1"
+        # "2": only gate|up -> down (two projections with nothing between them) as one launch
+        self.chain_mlp = os.environ.get("MLORA_CHAIN", "0") == "2"
 
     # ------------------------------------------------------------------------------------------
     def status_word(self) -> int:
@@ -351,6 +353,30 @@ class Engine:
                 return
             self.coll.all_reduce_sum(delta)
         ops.residual_rmsnorm(delta, res, w, m.eps, out=out)
+
+    def _mlp_chained(self, T, lw, slots, xn, act, y):
+        """gate|up (SiLU) -> down as ONE persistent launch (mlora_decode_chain with two phases); False when the shapes
+        do not fit it or the switch is off."""
+        m = self.m
+        if not (self.chain_mlp and m.pack and 0 < T <= 32):
+            return False
+        steps = []
+        for x, W, out, key, fl in ((xn, lw.w_gu, act, "gu", SILU_MUL), (act, lw.w_down, y, "down", 0)):
+            st = ops.ChainStep(x=x, W=W, y=out, flags=fl)
+            stack = lw.lora.get(key)
+            if stack is not None and slots is not None:
+                if self._lora_flags(T, stack, fl) & LORA_PER_ROW:
+                    return False
+                r_tot = stack.r_max * stack.n_mod
+                st.stack, st.u = stack, self.u.view(-1)[: T * r_tot].view(T, r_tot)
+            steps.append(st)
+        if steps[0].stack is not None and steps[1].stack is not None:
+            return False  # (the two shrink outputs would share one buffer inside one launch)
+        if not ops.chain_supported(T, steps):
+            return False
+        ops.decode_chain(steps, slots, m.ranks if m.n_adapters else None, m.scales if m.n_adapters else None, m.n_adapters,
+                         self.ws_linear)
+        return True
 
     def _proj(self, x, W, stack, slots, out, flags=0):
         T = x.shape[0]
@@ -464,8 +490,9 @@ class Engine:
             self._proj(attn, lw.w_o, lw.lora.get("o"), slots, y)
             # row-parallel partials (base + LoRA) -> full o_proj output, added to the residual, normalised
             self._reduce_norm(y, res, lw.ln2, xn)
-            self._proj(xn, lw.w_gu, lw.lora.get("gu"), slots, act, flags=SILU_MUL)
-            self._proj(act, lw.w_down, lw.lora.get("down"), slots, y)
+            if not self._mlp_chained(T, lw, slots, xn, act, y):
+                self._proj(xn, lw.w_gu, lw.lora.get("gu"), slots, act, flags=SILU_MUL)
+                self._proj(act, lw.w_down, lw.lora.get("down"), slots, y)
             delta = y  # (under tensor parallelism still a partial sum: reduced together with the next norm)
         self._reduce_norm(delta, res, m.norm, xn)
         if lm_rows is not None:
