@@ -136,7 +136,7 @@ def run_13b_shape(args):
     torch.cuda.empty_cache()
     max_len = prompt_len + 2 * (steps + warm) + 8
     kv = kv_mod.PagedKVCache(pm.L, pm.Hkv, pm.D, n_req, n_req * max_len, prompt_len, PAGE, dev, max_seq_len=max_len)
-    eng = model_mod.Engine(pm, kv, max_rows=4096)
+    eng = model_mod.Engine(pm, kv, max_rows=8192)
     sids = list(range(n_req))
     for sid in sids:
         kv.add_sequence(sid)
@@ -176,7 +176,7 @@ def run_prefill_heavy(args):
     """Side measurement (its own JSON line): the prefill-heavy configuration on one GPU -- Llama-2-7B shape, 64
     requests x 512-token prompts, 64 rank-64 adapters on all seven projections, adapter ids Zipf(1.1) (skewed segment
     sizes for the grouped shrink), then 16 greedy decode tokens.  Prefill is timed with CUDA events over the engine's
-    own passes (8 passes of 4096 rows); flops are the algorithmic ones of the workload."""
+    own passes (4 passes of 8192 rows); flops are the algorithmic ones of the workload."""
     import numpy as np
     import torch
 
@@ -201,7 +201,7 @@ def run_prefill_heavy(args):
     times = []
     for rep in range(2):  # first pass warms up (lazy kernel loading); the second is the measured one
         kv = kv_mod.PagedKVCache(pm.L, pm.Hkv, pm.D, n_req, n_req * max_len, prompt_len, PAGE, dev, max_seq_len=max_len)
-        eng = model_mod.Engine(pm, kv, max_rows=4096)
+        eng = model_mod.Engine(pm, kv, max_rows=8192)
         for sid in sids:
             kv.add_sequence(sid)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -401,7 +401,9 @@ def run_reference(args, rank, world):
     tps, cores, sample, r = cpu_reference_step(cfg, synth, args.steps, args.warmup)
     line = {
         "impl": "reference", "metric": METRIC, "value": tps, "unit": "tokens/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * r["full_step_s"],
+        # a full-model CPU step takes seconds: at most 3 steps of each truncation are timed, whatever was asked for
+        "steps": max(1, min(args.steps, 3)), "warmup": max(1, min(args.warmup, 1)), "steps_requested": args.steps,
+        "ms_per_step": 1e3 * r["full_step_s"], "extrapolated": True,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_config(args.gpus),
         "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
@@ -411,7 +413,15 @@ def run_reference(args, rank, world):
     emit(line)
 
 
-def workload_config(n_gpus):
+def workload_config(n_gpus, strong=False):
+    if strong:
+        return {
+            "workload": "llama2-7b-shape multi-LoRA decode, strong-scaling side line: the SAME 32 requests x 16 rank-16 "
+                        "adapters (alpha 32) on q/k/v/o spread over the GPUs by adapter, 512-token prompts, paged KV block 16",
+            "requests_per_gpu": N_REQ / n_gpus, "adapters_per_gpu": N_ADAPTERS / n_gpus, "global_batch": N_REQ,
+            "prompt_len": PROMPT_LEN, "parallelism": f"adapter-sharded replicas x{n_gpus} (no collective), fixed total batch",
+            "l2": "inputs exceed L2 (13.2 GB of weights streamed per step on every GPU)",
+        }
     return {
         "workload": "llama2-7b-shape multi-LoRA decode: 32 layers, hidden 4096, 32x128 heads, inter 11008, "
                     "vocab 32000; per GPU 32 requests x 16 rank-16 adapters (alpha 32) on q/k/v/o, 512-token "
@@ -456,15 +466,20 @@ def run_ours(args, rank, world, local_rank):
 
     # ---- the global batch and its shard ---------------------------------------------------------------
     # rank r owns adapters [16r, 16r+16); its 32 requests draw their adapter uniformly from those
-    ids_global = np.concatenate([
-        N_ADAPTERS * r + np.random.default_rng(synth.SEED_IDS + r).integers(0, N_ADAPTERS, N_REQ) for r in range(world)
-    ]).astype(np.int32)
-    owner, per_rank = sharding.shard_requests(ids_global, world, N_ADAPTERS * world, "block")
+    strong = args.scaling == "strong"
+    if strong:  # the SAME 32 requests over 16 adapters, spread over the ranks by adapter (side line, not the benchmark's)
+        ids_global = np.random.default_rng(synth.SEED_IDS).integers(0, N_ADAPTERS, N_REQ).astype(np.int32)
+        owner, per_rank = sharding.shard_requests(ids_global, world, N_ADAPTERS, "balanced")
+    else:
+        ids_global = np.concatenate([
+            N_ADAPTERS * r + np.random.default_rng(synth.SEED_IDS + r).integers(0, N_ADAPTERS, N_REQ) for r in range(world)
+        ]).astype(np.int32)
+        owner, per_rank = sharding.shard_requests(ids_global, world, N_ADAPTERS * world, "block")
     mine = per_rank[rank]
     held, slot_of = sharding.local_adapter_slots(ids_global, owner, rank)
     slots = [slot_of[int(ids_global[i])] for i in mine]
     B = len(mine)
-    prompts_all = synth.prompts(N_REQ * world, PROMPT_LEN, cfg["vocab_size"])
+    prompts_all = synth.prompts(N_REQ * (1 if strong else world), PROMPT_LEN, cfg["vocab_size"])
     prompts = [prompts_all[i].tolist() for i in mine]
 
     # ---- model ------------------------------------------------------------------------------------------
@@ -595,8 +610,8 @@ def run_ours(args, rank, world, local_rank):
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
-            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "bf16", "data": "synthetic", "config": dict(workload_config(world), layers=L,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic", "config": dict(workload_config(world, strong), layers=L,
                                                                   ctx_start=PROMPT_LEN + W, ctx_end=ctx_end),
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B,
                     "ms_per_step": ms_e2e / K,
@@ -1000,6 +1015,9 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="debug: truncate the model (the number is then not a bench value)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-operator", action="store_true", help="skip the operator micro-benchmark rows")
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="weak (the benchmark): 32 requests and 16 adapters PER GPU; strong (side line): the same 32 requests "
+                         "spread over the GPUs by adapter")
     ap.add_argument("--tp-collective", default="nccl", choices=["nccl", "peer"],
                     help="13b-tp workload: the exchange after row-parallel projections -- NCCL all-reduce + norm kernel, or "
                          "the library's fused peer-memory kernel")

@@ -276,6 +276,41 @@ int mlora_paged_attention(const void* d_qkv, int64_t ld, void* d_k_pages, void* 
                           int32_t fused_append, void* d_out, int64_t ld_out, int32_t n_splits,
                           void* d_work, size_t work_bytes, void* stream);
 
+/* mlora_prefill_attention: causal attention for prompt rows on the tensor cores, after mlora_kv_append_rope has
+ * rotated q in place and stored the rows' k / v -- the ragged prefill path of attention_with_fused_qkv
+ * (tvm/llama_auto_batcher/llama_for_causal_lm.py:55-64; prefill call llama_exec_graph.py:75-85).  The rows are given as
+ * tiles: d_tiles [n_tiles][4] int32 = (cache slot, index of the tile's first row in d_qkv / d_out, rows <= 128,
+ * position of that first row in its sequence); the rows of a tile are consecutive rows of ONE sequence at consecutive
+ * positions.  Same result as mlora_paged_attention(fused_append = 0) on those rows (different summation order).
+ * head_dim 128 and page size 16 only; n_pages_total = pages in d_k_pages / d_v_pages; T = rows of d_qkv.
+ * d_status (optional, device int32): set to 1 if a bounded wait expired (the affected rows are then zeros). */
+int mlora_prefill_attention(const void* d_qkv, int64_t ld, const void* d_k_pages, const void* d_v_pages,
+                            int32_t n_pages_total, const int32_t* d_block_table, int32_t max_pages,
+                            const int32_t* d_tiles, int32_t n_tiles, int32_t Hq, int32_t Hkv, int32_t D,
+                            int32_t page_size, int32_t T, void* d_out, int64_t ld_out, int32_t* d_status, void* stream);
+
+/* Split count the library picks for n_splits <= 0 (1 = every (row, head) is one CTA, no merge kernel). */
+uint32_t mlora_paged_attention_splits(int32_t T, int32_t Hq, int32_t max_pages);
+
+/* mlora_paged_attention_shrink: attention as above AND, in the same launch, the LoRA shrink of the projection that
+ * reads its output -- o_proj's half of "q += ft_proj(h, wids)" (tvm/llama_auto_batcher/compile_tvm.py:126-134 applied
+ * to the output projection; huggingface/custom_peft/lora_gatherbmm_linear_layer.py:16-19):
+ *   d_u[t, j] = sum_c A_all[slot[t], j, c] * out[t, c]      (out as rounded to bf16; rows without adapter give 0)
+ * Every (row, head) CTA adds its head's share to per-head partial sums; the last head of a row to finish adds them in
+ * head order.  d_A_all [N, r_max, Hq*D] bf16 (rows at or beyond an adapter's rank zero), d_u [T, r_max] float32.
+ * Only where the library runs one CTA per (row, head) (mlora_paged_attention_splits(...) == 1); otherwise the call
+ * is refused and the caller runs mlora_paged_attention + mlora_lora_shrink.  d_shrink_work:
+ * mlora_paged_attention_shrink_workspace(T, Hq, r_max) bytes, zero-filled once before first use (arrival counters,
+ * they reset themselves), not shared with concurrent calls.  Sums in a different order than mlora_lora_shrink. */
+size_t mlora_paged_attention_shrink_workspace(int32_t T, int32_t Hq, int32_t r_max);
+int mlora_paged_attention_shrink(const void* d_qkv, int64_t ld, void* d_k_pages, void* d_v_pages,
+                                 const int32_t* d_block_table, int32_t max_pages, const int32_t* d_row_slot,
+                                 const int32_t* d_row_pos, int32_t T, int32_t Hq, int32_t Hkv, int32_t D,
+                                 int32_t page_size, float rope_theta, int32_t fused_append, void* d_out,
+                                 int64_t ld_out, const void* d_A_all, const int32_t* d_ranks, const int32_t* d_slots,
+                                 int32_t n_adapters, int32_t r_max, float* d_u, void* d_shrink_work,
+                                 size_t shrink_work_bytes, void* stream);
+
 /* mlora_paged_attention_static: the same operation for callers that must not allocate.
  * (No counterpart in the reference project; added for embedders of this library.)
  * Some hosts of this code hand out all device memory themselves at start-up -- a serving runtime

@@ -49,6 +49,12 @@ PROTOTYPES = {
     "mlora_paged_attention_workspace": (_sz, [_i32, _i32, _i32, _i32]),
     "mlora_paged_attention": (C.c_int, [_vp, _i64, _vp, _vp, _vp, _i32, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _f32,
                                         _i32, _vp, _i64, _i32, _vp, _sz, _vp]),
+    "mlora_prefill_attention": (C.c_int, [_vp, _i64, _vp, _vp, _i32, _vp, _i32, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp,
+                                          _i64, _vp, _vp]),
+    "mlora_paged_attention_splits": (C.c_uint32, [_i32, _i32, _i32]),
+    "mlora_paged_attention_shrink_workspace": (_sz, [_i32, _i32, _i32]),
+    "mlora_paged_attention_shrink": (C.c_int, [_vp, _i64, _vp, _vp, _vp, _i32, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _f32,
+                                               _i32, _vp, _i64, _vp, _vp, _vp, _i32, _i32, _vp, _vp, _sz, _vp]),
     "mlora_paged_attention_static_max_bytes": (_sz, []),
     "mlora_paged_attention_static": (C.c_int, [_vp, _i64, _vp, _vp, _vp, _i32, _vp, _vp, _i32, _i32, _i32, _i32, _i32,
                                                _f32, _i32, _vp, _i64, _i32, _vp]),

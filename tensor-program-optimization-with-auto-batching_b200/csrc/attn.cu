@@ -33,6 +33,13 @@ struct AttnArgs {
   int64_t ld_out;
   int n_splits;
   float* work;
+  // optional: the LoRA shrink of the projection that reads `out` (o_proj), computed in this kernel's tail
+  const bf16* sh_A;            // [N, sh_r, Hq*D] or nullptr
+  const int32_t* sh_slots;     // [T]
+  int sh_n_adapters, sh_r;
+  float* sh_u;                 // [T, sh_r]
+  float* sh_part;              // [T, Hq, sh_r] per-head partial dot products
+  int32_t* sh_tickets;         // [T], zero between calls
 };
 
 // K/V pages are read once per step: no L1 allocation, and first in line for L2 eviction (`pol`), so that gigabytes
@@ -221,6 +228,7 @@ __global__ void __launch_bounds__(128) paged_attn_kernel(AttnArgs a) {
   __syncthreads();
 
   // ---- merge warps (+ the new token) and write -------------------------------------------------
+  float o_val = 0.f;
   if (tid < D) {
     float M = has_new ? s_new : -INFINITY;
 #pragma unroll
@@ -240,13 +248,64 @@ __global__ void __launch_bounds__(128) paged_attn_kernel(AttnArgs a) {
       }
     }
     if (a.n_splits == 1) {
-      a.out[(size_t)t * a.ld_out + h * D + tid] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+      const bf16 ob = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+      a.out[(size_t)t * a.ld_out + h * D + tid] = ob;
+      o_val = __bfloat162float(ob);  // exactly what a separate shrink kernel would read back
     } else {
       float* w = a.work + (((size_t)t * a.Hq + h) * a.n_splits + split) * (D + 2);
       w[tid] = O;
       if (tid == 0) {
         w[D] = M;
         w[D + 1] = L;
+      }
+    }
+  }
+  // ---- optional tail: u[t, j] = A[slot, j, :] . out[t, :] for the projection that reads this output ------------------
+  // Every (row, head) CTA multiplies its 128 outputs with the matching columns of the adapter's A rows (they are
+  // L2 resident: the K/V stream is marked evict-first) and leaves per-head partial sums; the last head of a row to
+  // arrive adds them up in head order.  One launch less per layer than a separate shrink kernel, and none of its
+  // round trips on the critical path between attention and projection.
+  if (a.sh_A != nullptr && a.n_splits == 1) {
+    __shared__ int s_last;
+    const int r = a.sh_r;
+    const int slot = a.sh_slots[t];
+    const bool has = slot >= 0 && slot < a.sh_n_adapters;
+    float* part = a.sh_part + ((size_t)t * a.Hq + h) * r;
+    __syncthreads();  // wacc is reused below
+    float* sred = &wacc[0][0];  // [4][16]
+    for (int j0 = 0; j0 < r; j0 += 16) {
+      if (has) {
+        const bf16* arow = a.sh_A + ((size_t)slot * r + j0) * ((size_t)a.Hq * D) + (size_t)h * D + tid;
+        float p[16];
+#pragma unroll
+        for (int jj = 0; jj < 16; ++jj)
+          p[jj] = (tid < D && j0 + jj < r) ? o_val * __bfloat162float(arow[(size_t)jj * a.Hq * D]) : 0.f;
+#pragma unroll
+        for (int jj = 0; jj < 16; ++jj) p[jj] = warp_sum(p[jj]);
+        if (lane == 0) {
+#pragma unroll
+          for (int jj = 0; jj < 16; ++jj) sred[warp * 16 + jj] = p[jj];
+        }
+      }
+      __syncthreads();
+      if (tid < 16 && j0 + tid < r)
+        part[j0 + tid] = has ? (sred[tid] + sred[16 + tid]) + (sred[32 + tid] + sred[48 + tid]) : 0.f;
+      __syncthreads();
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      const int old = atomicAdd(&a.sh_tickets[t], 1);
+      s_last = old == a.Hq - 1;
+      if (s_last) a.sh_tickets[t] = 0;  // ready for the next call
+    }
+    __syncthreads();
+    if (s_last) {
+      __threadfence();
+      for (int j = tid; j < r; j += blockDim.x) {
+        float acc = 0.f;
+        for (int hh = 0; hh < a.Hq; ++hh) acc += __ldcg(a.sh_part + ((size_t)t * a.Hq + hh) * r + j);  // head order
+        a.sh_u[(size_t)t * r + j] = acc;
       }
     }
   }
@@ -357,12 +416,21 @@ extern "C" int mlora_kv_append_rope(void* d_qkv, int64_t ld, void* d_k_pages, vo
   return MLORA_OK;
 }
 
-extern "C" int mlora_paged_attention(const void* d_qkv, int64_t ld, void* d_k_pages, void* d_v_pages,
-                                     const int32_t* d_block_table, int32_t max_pages, const int32_t* d_row_slot,
-                                     const int32_t* d_row_pos, int32_t T, int32_t Hq, int32_t Hkv, int32_t D,
-                                     int32_t page_size, float rope_theta, int32_t fused_append, void* d_out,
-                                     int64_t ld_out, int32_t n_splits, void* d_work, size_t work_bytes,
-                                     void* stream) {
+struct ShrinkTail {
+  const void* A = nullptr;
+  const int32_t* slots = nullptr;
+  int n_adapters = 0, r = 0;
+  float* u = nullptr;
+  float* part = nullptr;
+  int32_t* tickets = nullptr;
+};
+
+static int attention_impl(const void* d_qkv, int64_t ld, void* d_k_pages, void* d_v_pages,
+                          const int32_t* d_block_table, int32_t max_pages, const int32_t* d_row_slot,
+                          const int32_t* d_row_pos, int32_t T, int32_t Hq, int32_t Hkv, int32_t D,
+                          int32_t page_size, float rope_theta, int32_t fused_append, void* d_out,
+                          int64_t ld_out, int32_t n_splits, void* d_work, size_t work_bytes,
+                          void* stream, const ShrinkTail& sh) {
   int rc = check_kv_common("paged_attention", T, Hq, Hkv, D, page_size);
   if (rc) return rc;
   MLORA_REQUIRE(d_qkv && d_k_pages && d_v_pages && d_block_table && d_row_slot && d_row_pos && d_out && max_pages > 0,
@@ -382,7 +450,7 @@ extern "C" int mlora_paged_attention(const void* d_qkv, int64_t ld, void* d_k_pa
   }
   AttnArgs a{(const bf16*)d_qkv, ld, (bf16*)d_k_pages, (bf16*)d_v_pages, d_block_table, max_pages, d_row_slot,
              d_row_pos, T, Hq, Hkv, page_size, rope_theta, fused_append ? 1 : 0, (bf16*)d_out, ld_out, n_splits,
-             (float*)d_work};
+             (float*)d_work, (const bf16*)sh.A, sh.slots, sh.n_adapters, sh.r, sh.u, sh.part, sh.tickets};
   dim3 grid(Hq, T, n_splits);
   cudaStream_t st = (cudaStream_t)stream;
   if (D == 128 && page_size == 16)
@@ -400,6 +468,58 @@ extern "C" int mlora_paged_attention(const void* d_qkv, int64_t ld, void* d_k_pa
   }
   MLORA_CHECK_LAUNCH("paged_attn_kernel");
   return MLORA_OK;
+}
+
+extern "C" int mlora_paged_attention(const void* d_qkv, int64_t ld, void* d_k_pages, void* d_v_pages,
+                                     const int32_t* d_block_table, int32_t max_pages, const int32_t* d_row_slot,
+                                     const int32_t* d_row_pos, int32_t T, int32_t Hq, int32_t Hkv, int32_t D,
+                                     int32_t page_size, float rope_theta, int32_t fused_append, void* d_out,
+                                     int64_t ld_out, int32_t n_splits, void* d_work, size_t work_bytes,
+                                     void* stream) {
+  return attention_impl(d_qkv, ld, d_k_pages, d_v_pages, d_block_table, max_pages, d_row_slot, d_row_pos, T, Hq, Hkv, D,
+                        page_size, rope_theta, fused_append, d_out, ld_out, n_splits, d_work, work_bytes, stream,
+                        ShrinkTail{});
+}
+
+extern "C" uint32_t mlora_paged_attention_splits(int32_t T, int32_t Hq, int32_t max_pages) {
+  if (T <= 0 || Hq <= 0 || max_pages <= 0) return 1;
+  return (uint32_t)pick_splits(T, Hq, max_pages);
+}
+
+extern "C" size_t mlora_paged_attention_shrink_workspace(int32_t T, int32_t Hq, int32_t r_max) {
+  if (T <= 0 || Hq <= 0 || r_max <= 0) return 0;
+  return (((size_t)T * sizeof(int32_t) + 255) & ~(size_t)255) + (size_t)T * Hq * r_max * sizeof(float);
+}
+
+extern "C" int mlora_paged_attention_shrink(const void* d_qkv, int64_t ld, void* d_k_pages, void* d_v_pages,
+                                            const int32_t* d_block_table, int32_t max_pages,
+                                            const int32_t* d_row_slot, const int32_t* d_row_pos, int32_t T, int32_t Hq,
+                                            int32_t Hkv, int32_t D, int32_t page_size, float rope_theta,
+                                            int32_t fused_append, void* d_out, int64_t ld_out, const void* d_A_all,
+                                            const int32_t* d_ranks, const int32_t* d_slots, int32_t n_adapters,
+                                            int32_t r_max, float* d_u, void* d_shrink_work, size_t shrink_work_bytes,
+                                            void* stream) {
+  MLORA_REQUIRE(d_A_all && d_ranks && d_slots && d_u && d_shrink_work && n_adapters > 0 && r_max > 0 && r_max % 8 == 0,
+                "paged_attention_shrink: LoRA operands");
+  MLORA_REQUIRE(T >= 0 && Hq > 0, "paged_attention_shrink: bad sizes");
+  const size_t need = mlora_paged_attention_shrink_workspace(T, Hq, r_max);
+  if (shrink_work_bytes < need)
+    return fail(MLORA_ESIZE, "paged_attention_shrink: workspace of %zu bytes needed, %zu given", need, shrink_work_bytes);
+  if (T > 0 && pick_splits(T, Hq, max_pages) != 1) {
+    // few rows: the attention is split over the context and merged by a second kernel; the shrink then runs as its own
+    MLORA_REQUIRE(false, "paged_attention_shrink: %d rows x %d heads leave SMs idle, the split-context form is needed: "
+                         "call mlora_paged_attention and mlora_lora_shrink", T, Hq);
+  }
+  ShrinkTail sh;
+  sh.A = d_A_all;
+  sh.slots = d_slots;
+  sh.n_adapters = n_adapters;
+  sh.r = r_max;
+  sh.u = d_u;
+  sh.tickets = (int32_t*)d_shrink_work;
+  sh.part = (float*)((uint8_t*)d_shrink_work + (((size_t)T * sizeof(int32_t) + 255) & ~(size_t)255));
+  return attention_impl(d_qkv, ld, d_k_pages, d_v_pages, d_block_table, max_pages, d_row_slot, d_row_pos, T, Hq, Hkv, D,
+                        page_size, rope_theta, fused_append, d_out, ld_out, 1, nullptr, 0, stream, sh);
 }
 
 // ---- allocation-free variant -------------------------------------------------------------------------

@@ -155,7 +155,8 @@ template <int BN>
 struct Cfg {
   static constexpr int kWBytes = BM * BK * 2;    // weight stage: 16 KB
   static constexpr int kXBytes = BN * BK * 2;    // token-tile stage
-  static constexpr int kXStages = BN >= 64 ? 4 : 8;  // token tiles come from L2: a shallower ring is enough
+  // token tiles come from L2: a shallower ring is enough (256-token tiles: three 48 KB stage pairs = 1500 tensor cycles ahead)
+  static constexpr int kXStages = BN >= 256 ? 3 : BN >= 64 ? 4 : 8;
   // barriers | 7 integer lists of BN (token slots / distinct adapters per role) | staged shrink outputs
   // LoRA B operands (scaled, masked shrink outputs) of a token tile; prefill-size tiles get room for a rank-128
   // pitch (interleaved gate/up at rank 64) so the operands are built once per token tile, not once per tile
@@ -171,6 +172,8 @@ struct Cfg {
   static constexpr int kSmemBytes = kWStages * kWBytes + kXStages * kXBytes + kAuxBytes + 1024;
   static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;  // two accumulators
   static constexpr int kChunk = BN < 32 ? BN : 32;              // columns per TMEM load
+  static_assert(kWStages >= 3, "weight ring too shallow");
+  static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 };
 
 // Do the LoRA B operands of a token tile with n_seg distinct adapters fit the shared-memory cache?
@@ -588,19 +591,52 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
               break;
             }
             uint8_t* xt = x_ring + s * C::kXBytes;
-            for (int idx = lane; idx < BN * chunks; idx += 32) {
-              const int nrow = idx / chunks, c = idx - nrow * chunks;
-              uint4 val = make_uint4(0u, 0u, 0u, 0u);
-              if (x_tok[nrow] == slot) {
-                const float* ur = (stage_u ? s_u + nrow * r_tot : a.u + (size_t)(t0 + nrow) * r_tot) + u_off +
-                                  sb * p.lora_sub + c * 8;
-                float f[8];
+            if constexpr (BN >= 128) {
+              // four items per lane and step, their shrink outputs (L2 round trips) requested before the first is used
+              for (int base = lane; base < BN * chunks; base += 32 * 4) {
+                float4 lo[4], hi[4];
+                bool mine[4];
 #pragma unroll
-                for (int e = 0; e < 8; ++e) f[e] = ur[e] * sc;
-                val = pack8(f);
+                for (int b = 0; b < 4; ++b) {
+                  const int idx = base + b * 32;
+                  const int nrow = idx / chunks, c = idx - nrow * chunks;
+                  mine[b] = idx < BN * chunks && x_tok[nrow] == slot;
+                  if (mine[b]) {
+                    const float* ur = a.u + (size_t)(t0 + nrow) * r_tot + u_off + sb * p.lora_sub + c * 8;
+                    lo[b] = *reinterpret_cast<const float4*>(ur);
+                    hi[b] = *reinterpret_cast<const float4*>(ur + 4);
+                  }
+                }
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                  const int idx = base + b * 32;
+                  if (idx >= BN * chunks) continue;
+                  const int nrow = idx / chunks, c = idx - nrow * chunks;
+                  uint4 val = make_uint4(0u, 0u, 0u, 0u);
+                  if (mine[b]) {
+                    const float f[8] = {lo[b].x * sc, lo[b].y * sc, lo[b].z * sc, lo[b].w * sc,
+                                        hi[b].x * sc, hi[b].y * sc, hi[b].z * sc, hi[b].w * sc};
+                    val = pack8(f);
+                  }
+                  const int sw = rb == 128 ? (nrow & 7) : rb == 64 ? ((nrow >> 1) & 3) : ((nrow >> 2) & 1);
+                  *reinterpret_cast<uint4*>(xt + nrow * rb + ((c ^ sw) << 4)) = val;
+                }
               }
-              const int sw = rb == 128 ? (nrow & 7) : rb == 64 ? ((nrow >> 1) & 3) : ((nrow >> 2) & 1);
-              *reinterpret_cast<uint4*>(xt + nrow * rb + ((c ^ sw) << 4)) = val;
+            } else {
+              for (int idx = lane; idx < BN * chunks; idx += 32) {
+                const int nrow = idx / chunks, c = idx - nrow * chunks;
+                uint4 val = make_uint4(0u, 0u, 0u, 0u);
+                if (x_tok[nrow] == slot) {
+                  const float* ur = (stage_u ? s_u + nrow * r_tot : a.u + (size_t)(t0 + nrow) * r_tot) + u_off +
+                                    sb * p.lora_sub + c * 8;
+                  float f[8];
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) f[e] = ur[e] * sc;
+                  val = pack8(f);
+                }
+                const int sw = rb == 128 ? (nrow & 7) : rb == 64 ? ((nrow >> 1) & 3) : ((nrow >> 2) & 1);
+                *reinterpret_cast<uint4*>(xt + nrow * rb + ((c ^ sw) << 4)) = val;
+              }
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
@@ -1012,9 +1048,10 @@ struct Plan {
   int bn, row_tiles, tok_tiles, k_blocks, grid, per_cta, wave_gt, wave_full, wave_ch, wave_ch_last;
 };
 
-Plan make_plan(int T, int in, int out) {
+// min_waves: whole-tile mode needs at least this many tiles per CTA, so that the unfilled last wave costs little.
+Plan plan_for(int bn, int min_waves, int T, int in, int out) {
   Plan pl;
-  pl.bn = pick_bn(T);
+  pl.bn = bn;
   pl.row_tiles = (out + BM - 1) / BM;
   pl.tok_tiles = (T + pl.bn - 1) / pl.bn;
   pl.k_blocks = (in + BK - 1) / BK;
@@ -1022,8 +1059,8 @@ Plan make_plan(int T, int in, int out) {
   long long grid = sm_count();
   pl.wave_gt = pl.wave_full = pl.wave_ch = pl.wave_ch_last = 0;
   const long long n_tiles = (long long)pl.row_tiles * pl.tok_tiles;
-  if (pl.tok_tiles >= 4 && n_tiles >= 8 * grid) {
-    // enough whole tiles that the unfilled last wave costs little: waves of (token tiles x row tiles)
+  if (pl.tok_tiles >= 4 && n_tiles >= min_waves * grid) {
+    // waves of (token tiles x row tiles)
     int gt = (int)grid;
     for (int d = 1; d <= 48 && d <= (int)grid; ++d)
       if (grid % d == 0) gt = d;  // largest divisor of the grid up to 48 (148 SMs -> 37)
@@ -1042,6 +1079,25 @@ Plan make_plan(int T, int in, int out) {
   pl.per_cta = (int)((total + grid - 1) / grid);
   pl.grid = (int)((total + pl.per_cta - 1) / pl.per_cta);
   return pl;
+}
+
+// 256-token tiles where whole tiles fill the grid at least three times over (prompt passes of thousands of rows): a
+// 128 x 128 tile moves 64 KB through shared memory per 256 tensor-pipe cycles, twice what a shared memory delivers;
+// 128 x 256 moves 96 KB per 512.  Switch: MLORA_TILE256=0 keeps 128-token tiles.
+bool tile256_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("MLORA_TILE256");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
+Plan make_plan(int T, int in, int out) {
+  if (T >= 1024 && tile256_enabled()) {
+    Plan big = plan_for(256, 3, T, in, out);
+    if (big.wave_gt > 0) return big;
+  }
+  return plan_for(pick_bn(T), 8, T, in, out);
 }
 
 template <int BN>
@@ -1223,6 +1279,7 @@ int launch_linear_tc(const LinearArgs& a, void* work, size_t work_bytes, cudaStr
     case 16: return launch<16>(a, pl, work, st);
     case 32: return launch<32>(a, pl, work, st);
     case 64: return launch<64>(a, pl, work, st);
+    case 256: return launch<256>(a, pl, work, st);
     default: return launch<128>(a, pl, work, st);
   }
 }

@@ -300,6 +300,16 @@ class Engine:
         # engine and are never shared with (or outgrown by) other callers on the device.
         self.ws_linear = ops.new_workspace(need, dev)
         self.ws_attn = ops.new_workspace(lib.mlora_paged_attention_workspace(T, m.Hq, m.D, 16), dev)
+        # the o-projection's shrink computed in the attention launch (decode passes): its own zero-initialised scratch.
+        # Measured on the benchmark's step: 32 launches fewer but 0.035 ms slower (the tail sits on the attention
+        # kernel's critical path, the separate shrink launch overlaps the projection's weight prefetch), so off unless asked for
+        self.fuse_o_shrink = os.environ.get("MLORA_FUSE_O_SHRINK", "0") == "1"
+        self.ws_oshrink = ops.new_workspace(lib.mlora_paged_attention_shrink_workspace(min(T, 1024), m.Hq, max(m.r_max, 8)), dev)
+        # prompt passes: tiles of <= 128 consecutive rows of one sequence for the tensor-core attention
+        self.tc_prefill = os.environ.get("MLORA_TC_PREFILL", "1") != "0" and m.D == 128 and kv.page_size == 16
+        self.pf_tiles = torch.zeros((T + 127) // 128 + kv.max_batch + 1, 4, dtype=torch.int32, device=dev)
+        self.pf_status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self._n_pf_tiles = 0
         self._graphs = {}
         self.n_distinct = 0  # distinct adapters among the rows staged for the next pass (set with self.slots)
         self.fuse_norm_shrink = os.environ.get("MLORA_FUSE_NORM_SHRINK", "1") != "0"
@@ -485,9 +495,22 @@ class Engine:
             if not fused_append:
                 ops.kv_append_rope(qkv, kp, vp, kv.block_table, row_slot, row_pos, m.Hq, m.Hkv, m.D, kv.page_size,
                                    m.theta)
-            ops.paged_attention(qkv, kp, vp, kv.block_table, row_slot, row_pos, m.Hq, m.Hkv, m.D, kv.page_size,
-                                m.theta, fused_append, out=attn, work=self.ws_attn)
-            self._proj(attn, lw.w_o, lw.lora.get("o"), slots, y)
+            st_o = lw.lora.get("o")
+            if (st_o is not None and slots is not None and self.fuse_o_shrink and fused_append and T <= 1024
+                    and ops.attention_shrink_fits(T, m.Hq, kv.block_table.shape[1], st_o)):
+                # attention and the o-projection's shrink in one launch; the projection then only expands
+                u_o = self.u.view(-1)[: T * st_o.r_max].view(T, st_o.r_max)
+                ops.paged_attention_shrink(qkv, kp, vp, kv.block_table, row_slot, row_pos, m.Hq, m.Hkv, m.D, kv.page_size,
+                                           m.theta, fused_append, attn, st_o, slots, u_o, self.ws_oshrink)
+                ops.linear(attn, lw.w_o, st_o, slots, u=u_o, flags=self._lora_flags(T, st_o, 0), out=y, work=self.ws_linear)
+            else:
+                if not fused_append and self.tc_prefill and self._n_pf_tiles > 0:
+                    ops.prefill_attention(qkv, kp, vp, kv.block_table, self.pf_tiles, self._n_pf_tiles, m.Hq, m.Hkv, m.D,
+                                          kv.page_size, attn, self.pf_status)
+                else:
+                    ops.paged_attention(qkv, kp, vp, kv.block_table, row_slot, row_pos, m.Hq, m.Hkv, m.D, kv.page_size,
+                                        m.theta, fused_append, out=attn, work=self.ws_attn)
+                self._proj(attn, lw.w_o, st_o, slots, y)
             # row-parallel partials (base + LoRA) -> full o_proj output, added to the residual, normalised
             self._reduce_norm(y, res, lw.ln2, xn)
             if not self._mlp_chained(T, lw, slots, xn, act, y):
@@ -550,6 +573,16 @@ class Engine:
             self.n_distinct = len({int(s) for s in slots if s >= 0})
             self.row_slot[:T].copy_(row_slot)
             self.row_pos[:T].copy_(row_pos)
+            # tiles of the tensor-core prompt attention: <= 128 consecutive rows of one sequence each
+            tiles, a0 = [], 0
+            for i, s0, n in chunk:
+                for off in range(0, n, 128):
+                    tiles.append((kv.slot(seq_ids[i]), a0 + off, min(128, n - off), s0 + off))
+                a0 += n
+            self._n_pf_tiles = 0
+            if self.tc_prefill and len(tiles) <= self.pf_tiles.shape[0]:
+                self._stage(self.pf_tiles.view(-1), np.asarray(tiles, dtype=np.int32).reshape(-1), torch.int32)
+                self._n_pf_tiles = len(tiles)
             ends, fin, a = [], [], 0
             for i, s, n in chunk:
                 a += n
@@ -566,7 +599,11 @@ class Engine:
                 self._stage(self.last_rows, [T - 1], torch.int32)
                 self.forward(T, False, use_lora, self.last_rows, 1)
             kv.end_forward()
+            self._n_pf_tiles = 0
         self.check_status()  # (synchronises; prefill is not the latency-critical call)
+        if int(self.pf_status.item()):
+            self.pf_status.zero_()
+            raise RuntimeError("mlora: the prompt attention kernel gave up a bounded wait; this pass's results are undefined")
         return out_logits, out_tok
 
     def decode(self, seq_ids, tokens, adapter_slots, use_lora=True):

@@ -395,6 +395,37 @@ def paged_attention(qkv, k_pages, v_pages, block_table, row_slot, row_pos, Hq, H
     return out
 
 
+def prefill_attention(qkv, k_pages, v_pages, block_table, tiles, n_tiles, Hq, Hkv, D, page_size, out, status=None):
+    """Causal attention of prompt rows on the tensor cores (``mlora_prefill_attention``); ``tiles`` int32 [n,4] on the
+    device: (cache slot, first row, rows <= 128, position of the first row)."""
+    _need_cuda(qkv, k_pages)
+    check(_lib.lib().mlora_prefill_attention(
+        _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), k_pages.shape[0], _ptr(block_table), block_table.shape[1],
+        _ptr(tiles), n_tiles, Hq, Hkv, D, page_size, qkv.shape[0], _ptr(out), out.stride(0), _ptr(status), _stream()),
+        "mlora_prefill_attention")
+    return out
+
+
+def attention_shrink_fits(T, Hq, max_pages, stack) -> bool:
+    """Can the o-projection's shrink ride in the attention launch?  (one CTA per (row, head), one module)"""
+    return stack.n_mod == 1 and _lib.lib().mlora_paged_attention_splits(T, Hq, max_pages) == 1
+
+
+def paged_attention_shrink(qkv, k_pages, v_pages, block_table, row_slot, row_pos, Hq, Hkv, D, page_size, theta,
+                           fused_append: bool, out, stack: LoraStack, slots, u, work):
+    """Attention plus, in the same launch, ``u = A[slot] . out`` for the projection that reads ``out``
+    (see ``mlora_paged_attention_shrink``).  ``work``: zero-initialised scratch of
+    ``mlora_paged_attention_shrink_workspace`` bytes owned by the caller."""
+    _need_cuda(qkv, k_pages)
+    T = qkv.shape[0]
+    check(_lib.lib().mlora_paged_attention_shrink(
+        _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
+        _ptr(row_slot), _ptr(row_pos), T, Hq, Hkv, D, page_size, theta, int(fused_append), _ptr(out), out.stride(0),
+        _ptr(stack.A_all), _ptr(stack.ranks), _ptr(slots), stack.A_all.shape[0], stack.r_max, _ptr(u), _ptr(work),
+        work.numel(), _stream()), "mlora_paged_attention_shrink")
+    return out
+
+
 def kv_begin_decode(row_slot, seq_lens, row_pos):
     check(_lib.lib().mlora_kv_begin_decode(_ptr(row_slot), _ptr(seq_lens), _ptr(row_pos), row_slot.numel(),
                                            _stream()), "mlora_kv_begin_decode")

@@ -372,6 +372,72 @@ def test_append_then_attention_prefill_rows(ops, cuda):
     torch.testing.assert_close(got.float(), kr[: S[0]].float(), atol=1e-2, rtol=1e-2)
 
 
+@pytest.mark.parametrize("Hq,Hkv", [(4, 4), (8, 2)])
+def test_prompt_attention_on_tensor_cores(ops, cuda, Hq, Hkv):
+    """Tiles of <= 128 prompt rows: ragged lengths, a 300-row prompt cut into three tiles, one row, and a chunk that
+    continues a sequence whose first 70 tokens are already in the pages.  Against the single-query kernel on the same
+    pages and against the oracle's causal attention."""
+    D, ps, theta = 128, 16, 10000.0
+    g = torch.Generator().manual_seed(11)
+    # (slot, tokens already cached, new rows)
+    seqs = [(2, 0, 300), (0, 0, 1), (3, 70, 45), (1, 0, 128), (4, 0, 17)]
+    max_pages = 24
+    n_pages = 64
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    bt = np.full((5, max_pages), -1, dtype=np.int32)
+    it = iter(perm)
+    for slot, old, n in seqs:
+        for p in range((old + n + ps - 1) // ps):
+            bt[slot, p] = next(it)
+    kp = torch.zeros(n_pages, Hkv, ps, D, dtype=torch.bfloat16, device=cuda)
+    vp = torch.zeros_like(kp)
+    W = (Hq + 2 * Hkv) * D
+    hist = {}
+    # the earlier chunk of slot 3 goes in first, through the same append kernel
+    for slot, old, n in seqs:
+        if old:
+            h = torch.randn(old, W, generator=g).bfloat16()
+            hist[slot] = h
+            ops.kv_append_rope(h.to(cuda), kp, vp, _i32(bt, cuda), _i32(np.full(old, slot, np.int32), cuda),
+                               _i32(np.arange(old, dtype=np.int32), cuda), Hq, Hkv, D, ps, theta)
+    T = sum(n for _, _, n in seqs)
+    qkv = torch.randn(T, W, generator=g).bfloat16()
+    slot_rows = np.concatenate([np.full(n, s, np.int32) for s, _, n in seqs])
+    pos_rows = np.concatenate([np.arange(o, o + n, dtype=np.int32) for _, o, n in seqs])
+    qkv_d = qkv.to(cuda)
+    ops.kv_append_rope(qkv_d, kp, vp, _i32(bt, cuda), _i32(slot_rows, cuda), _i32(pos_rows, cuda), Hq, Hkv, D, ps, theta)
+    tiles, a = [], 0
+    for s, o, n in seqs:
+        for off in range(0, n, 128):
+            tiles.append((s, a + off, min(128, n - off), o + off))
+        a += n
+    status = torch.zeros(1, dtype=torch.int32, device=cuda)
+    out = torch.full((T, Hq * D), float("nan"), dtype=torch.bfloat16, device=cuda)
+    ops.prefill_attention(qkv_d, kp, vp, _i32(bt, cuda), _i32(np.asarray(tiles, np.int32), cuda), len(tiles), Hq, Hkv, D, ps,
+                          out, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    ref = ops.paged_attention(qkv_d, kp, vp, _i32(bt, cuda), _i32(slot_rows, cuda), _i32(pos_rows, cuda), Hq, Hkv, D, ps,
+                              theta, False)
+    torch.testing.assert_close(out.float().cpu(), ref.float().cpu(), atol=ATOL, rtol=RTOL)
+    # oracle: rotate, then causal attention over history + chunk
+    a, want = 0, []
+    for s, o, n in seqs:
+        rows = qkv[a:a + n]
+        full = torch.cat([hist[s], rows]) if o else rows
+        pos = torch.arange(o + n)
+        q = oops.rope_rotate_half(full[:, : Hq * D].view(-1, Hq, D), pos, theta).bfloat16()
+        k = oops.rope_rotate_half(full[:, Hq * D:(Hq + Hkv) * D].view(-1, Hkv, D), pos, theta).bfloat16()
+        v = full[:, (Hq + Hkv) * D:].view(-1, Hkv, D)
+        want.append(oops.causal_attention(q, k, v)[o:].reshape(n, Hq * D))
+        a += n
+    torch.testing.assert_close(out.float().cpu(), torch.cat(want).float(), atol=ATOL, rtol=RTOL)
+    # sizes outside the kernel's range are refused, not mis-computed
+    with pytest.raises(Exception):
+        ops.prefill_attention(qkv_d, kp, vp, _i32(bt, cuda), _i32(np.asarray(tiles, np.int32), cuda), len(tiles), Hq, Hkv, 64,
+                              ps, out, status)
+
+
 def test_kv_begin_decode(ops, cuda):
     seq = _i32([5, 0, 9, 3], cuda)
     rows = _i32([2, 0], cuda)
@@ -521,20 +587,25 @@ def test_prefill_shrink_on_tensor_cores(ops, cuda, T, K, r, n_mod, mixing):
     torch.testing.assert_close(u.cpu(), want, atol=2e-3, rtol=1e-4)
 
 
-@pytest.mark.parametrize("T,K,N,lora", [(2048, 256, 12288, False), (2000, 320, 12288, True), (5000, 128, 6144, True)])
-def test_prefill_size_projection_in_waves(ops, cuda, T, K, N, lora):
+@pytest.mark.parametrize("T,K,N,lora,run", [(2048, 256, 12288, False, 300), (2000, 320, 12288, True, 300),
+                                             (5000, 128, 6144, True, 300), (2304, 192, 12288, True, 20),
+                                             (1500, 256, 12288, True, 300), (1100, 128, 24576, True, 7)])
+def test_prefill_size_projection_in_waves(ops, cuda, T, K, N, lora, run):
     """Enough tiles that the projection kernel deals whole tiles in L2-friendly waves instead of stream-K ranges
-    (ragged last token tile, narrower last token-tile group), with the LoRA expand and the grouped-GEMM shrink."""
+    (ragged last token tile, narrower last token-tile group), with the LoRA expand and the grouped-GEMM shrink.
+    From about 600 whole 256-token tiles on the kernel takes 256-token tiles (the first four cases and the last),
+    else 128-token ones; adapters changing every ``run`` rows put more adapters into a tile than its operand cache
+    holds (the stages then go through the token ring)."""
     g = torch.Generator().manual_seed(T)
     x = torch.randn(T, K, generator=g).bfloat16().to(cuda)
     W = (torch.randn(N, K, generator=g) * 0.05).bfloat16().to(cuda)
     want = x.float() @ W.float().t()
     st = slots = None
     if lora:
-        n_ad, r, third = 6, 16, N // 3
+        n_ad, r, third = (6 if run >= 100 else 24), 16, N // 3
         A = (torch.randn(n_ad, 3 * r, K, generator=g) * 0.05).bfloat16().to(cuda)
         B = (torch.randn(n_ad, N, r, generator=g) * 0.05).bfloat16().to(cuda)
-        slots = (torch.arange(T) // 300 % (n_ad + 1) - 1).int().to(cuda)  # runs of 300 rows, some without adapter
+        slots = (torch.arange(T) // run % (n_ad + 1) - 1).int().to(cuda)  # runs of rows, some without adapter
         st = ops.LoraStack(A, B, _i32([r] * n_ad, cuda), torch.full((n_ad,), 2.0, device=cuda), r, 3,
                            (0, third, 2 * third, N)).pack_b()
         for s in range(n_ad):
@@ -682,3 +753,43 @@ def test_per_row_expand_with_fused_modules(ops, cuda):
         st2.split_b(rk)
         yb = ops.linear(x.to(cuda), W.to(cuda), st2, slots.to(cuda), flags=ops.LORA_PER_ROW | ops.OUT_F32).cpu()
         assert torch.equal(ya, yb)
+
+
+def test_attention_with_the_output_projection_shrink_in_its_tail(ops, cuda):
+    """``mlora_paged_attention_shrink``: the same attention output, bit for bit, plus u = A[slot] . out computed by the
+    (row, head) CTAs themselves (per-head partial sums added in head order by the last head to finish); compared
+    with the separate shrink kernel on the attention output, twice in a row (the arrival counters reset themselves)."""
+    Hq, Hkv, D, ps, theta = 32, 32, 128, 16, 10000.0
+    lens = [int(n) for n in np.random.default_rng(3).integers(40, 300, 24)]
+    B = len(lens)
+    kp, vp, qkv, bt = _paged_case(7, B, Hq, Hkv, D, ps, lens, cuda)
+    slot_rows, pos = _i32(np.arange(B), cuda), _i32(lens, cuda)
+    g = torch.Generator().manual_seed(11)
+    for r, ranks in ((16, [16] * 6), (64, [8, 16, 32, 64, 64, 16])):
+        n_ad = len(ranks)
+        A = (torch.randn(n_ad, r, Hq * D, generator=g) * 0.05).bfloat16()
+        for i, rk in enumerate(ranks):
+            A[i, rk:] = 0
+        st = ops.LoraStack(A.to(cuda), torch.zeros(n_ad, 8, r, dtype=torch.bfloat16, device=cuda), _i32(ranks, cuda),
+                           torch.ones(n_ad, device=cuda), r, 1, (0, 8))
+        slots = torch.randint(-1, n_ad, (B,), generator=g).int().to(cuda)
+        assert ops.attention_shrink_fits(B, Hq, bt.shape[1], st)
+        work = ops.new_workspace(load("_lib").lib().mlora_paged_attention_shrink_workspace(B, Hq, r), cuda)
+        for rep in range(2):
+            kp1, vp1, kp2, vp2 = kp.to(cuda), vp.to(cuda), kp.to(cuda), vp.to(cuda)
+            want = ops.paged_attention(qkv.to(cuda), kp1, vp1, _i32(bt, cuda), slot_rows, pos, Hq, Hkv, D, ps, theta, True)
+            u_want = ops.lora_shrink(want, st, slots)
+            out = torch.empty_like(want)
+            u = torch.full((B, r), float("nan"), device=cuda)
+            ops.paged_attention_shrink(qkv.to(cuda), kp2, vp2, _i32(bt, cuda), slot_rows, pos, Hq, Hkv, D, ps, theta, True,
+                                       out, st, slots, u, work)
+            torch.cuda.synchronize()
+            assert torch.equal(out, want) and torch.equal(kp1, kp2) and torch.equal(vp1, vp2)
+            torch.testing.assert_close(u, u_want, atol=2e-3, rtol=2e-3)
+            assert float(u[slots < 0].abs().sum()) == 0.0
+        assert int(work[: 4 * B].view(torch.int32).abs().sum()) == 0
+    # few rows: the library would split the context; the fused form is refused with the way out in the message
+    with pytest.raises(Exception, match="split-context"):
+        ops.paged_attention_shrink(qkv[:2].to(cuda), kp.to(cuda), vp.to(cuda), _i32(bt[:2], cuda), slot_rows[:2], pos[:2], 4, 4, D,
+                                   ps, theta, True, torch.empty(2, 4 * D, dtype=torch.bfloat16, device=cuda), st, slots[:2],
+                                   torch.empty(2, 64, device=cuda), work)
