@@ -976,6 +976,40 @@ def run_kernel_case(which):
                           "peak_tflops": tpk, "frac_base": fl / res["base"] / 1e9 / tpk,
                           "status": ops.status_word(ops.workspace(4, dev, "linear")), "launches": ops.launch_count()})
         return
+    elif which == "prefill-attn":
+        # one layer's prompt attention: 16 requests x 512 rows, 32 x 128 heads, keys / values appended first
+        Hq = Hkv = 32
+        D, S, n_seq = 128, 512, 16
+        T = S * n_seq
+        n_pg = S // PAGE
+        kp = torch.zeros(n_seq * n_pg, Hkv, PAGE, D, device=dev, dtype=torch.bfloat16)
+        vp = torch.zeros_like(kp)
+        bt = torch.randperm(n_seq * n_pg, device=dev).to(torch.int32).view(n_seq, n_pg)
+        qkv = torch.randn(T, 3 * Hq * D, device=dev, dtype=torch.bfloat16)
+        slot = torch.arange(T, device=dev, dtype=torch.int32) // S
+        pos = torch.arange(T, device=dev, dtype=torch.int32) % S
+        tiles = torch.tensor([(q, q * S + o, 128, o) for q in range(n_seq) for o in range(0, S, 128)], dtype=torch.int32, device=dev)
+        out = torch.empty(T, Hq * D, dtype=torch.bfloat16, device=dev)
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        for i in range(5):
+            if i == 2:
+                ev[0].record()
+            ops.kv_append_rope(qkv, kp, vp, bt, slot, pos, Hq, Hkv, D, PAGE, 10000.0)
+        ev[1].record()
+        for i in range(5):
+            if i == 2:
+                ev[2].record()
+            ops.prefill_attention(qkv, kp, vp, bt, tiles, tiles.shape[0], Hq, Hkv, D, PAGE, out, status)
+        ev[3].record()
+        torch.cuda.synchronize()
+        us_app, us_att = ev[0].elapsed_time(ev[1]) / 3 * 1e3, ev[2].elapsed_time(ev[3]) / 3 * 1e3
+        fl = 4.0 * Hq * D * n_seq * S * (S + 1) / 2
+        by_app = T * 3 * Hq * D * 2 + T * Hq * D * 2 + 2 * T * Hkv * D * 2  # read q|k|v, write q, k and v pages
+        emit({"kernel_case": which, "rows": T, "us_append_rope": us_app, "append_rope_gbs": by_app / us_app / 1e3,
+              "us_attention": us_att, "attention_tflops_causal": fl / us_att / 1e6, "status": int(status.item()),
+              "launches": ops.launch_count()})
+        return
     else:
         # one layer's attention at context 576: 32 rows x 32 heads, 302 MB of KV
         Hq = Hkv = 32
@@ -1024,7 +1058,7 @@ def main():
     ap.add_argument("--skip-prefill", action="store_true",
                     help="profiling aid: fill the KV cache with seeded random values instead of running prefill "
                          "(the number is then not a bench value)")
-    ap.add_argument("--kernel-case", default="", choices=["", "linear", "attention", "operator", "prefill", "expand", "chain"],
+    ap.add_argument("--kernel-case", default="", choices=["", "linear", "attention", "operator", "prefill", "prefill-attn", "expand", "chain"],
                     help="profiling aid: launch one kernel a few times on a small case (> L2, < 1 GB) and exit")
     ap.add_argument("--workload", default="", choices=["", "13b-shape", "13b-tp", "prefill-heavy"],
                     help="side measurements (own JSON line, not the benchmark's): 13b-shape = the 13B shape and adapter "

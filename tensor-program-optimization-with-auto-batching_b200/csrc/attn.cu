@@ -347,21 +347,26 @@ __global__ void __launch_bounds__(256) kv_append_rope_kernel(bf16* __restrict__ 
   const int page = block_table[(size_t)slot * max_pages + pos / PS];
   bf16* row = qkv + (size_t)t * ld;
   const int half = D / 2;
-  for (int idx = threadIdx.x; idx < (Hq + Hkv) * half; idx += blockDim.x) {
-    const int head = idx / half, i = idx % half;
-    float sn, cs;
-    sincosf((float)pos * rope_inv_freq(theta, i, D), &sn, &cs);
+  // a thread keeps one pair of adjacent frequencies (its sine / cosine computed once) and walks the heads
+  const int pairs = half / 2;                       // 4-byte column pairs per half head
+  const int i = (threadIdx.x % pairs) * 2;
+  float sn0, cs0, sn1, cs1;
+  sincosf((float)pos * rope_inv_freq(theta, i, D), &sn0, &cs0);
+  sincosf((float)pos * rope_inv_freq(theta, i + 1, D), &sn1, &cs1);
+  for (int head = threadIdx.x / pairs; head < Hq + Hkv; head += blockDim.x / pairs) {
     bf16* p = row + (size_t)head * D;
-    const float x1 = __bfloat162float(p[i]), x2 = __bfloat162float(p[i + half]);
-    const bf16 r1 = __float2bfloat16_rn(x1 * cs - x2 * sn), r2 = __float2bfloat16_rn(x2 * cs + x1 * sn);
-    if (head < Hq) {
-      p[i] = r1;
-      p[i + half] = r2;
-    } else {
-      bf16* dst = k_pages + (((size_t)page * Hkv + (head - Hq)) * PS + pos % PS) * D;
-      dst[i] = r1;
-      dst[i + half] = r2;
-    }
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(p + i);
+    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(p + i + half);
+    const float x1a = __bfloat162float(a.x), x1b = __bfloat162float(a.y);
+    const float x2a = __bfloat162float(b.x), x2b = __bfloat162float(b.y);
+    __nv_bfloat162 r1, r2;
+    r1.x = __float2bfloat16_rn(x1a * cs0 - x2a * sn0);
+    r1.y = __float2bfloat16_rn(x1b * cs1 - x2b * sn1);
+    r2.x = __float2bfloat16_rn(x2a * cs0 + x1a * sn0);
+    r2.y = __float2bfloat16_rn(x2b * cs1 + x1b * sn1);
+    bf16* dst = head < Hq ? p : k_pages + (((size_t)page * Hkv + (head - Hq)) * PS + pos % PS) * D;
+    *reinterpret_cast<__nv_bfloat162*>(dst + i) = r1;
+    *reinterpret_cast<__nv_bfloat162*>(dst + i + half) = r2;
   }
   const bf16* vsrc = row + (size_t)(Hq + Hkv) * D;
   for (int idx = threadIdx.x; idx < Hkv * D / 8; idx += blockDim.x) {

@@ -10,9 +10,10 @@
 //   O_blk = P V    M = 128 queries, N = 128 head dims, K = 128 keys; V is stored [key][dim] in the pages, the B operand wants
 //                  [dim][key], so the softmax threads copy the block transposed into shared memory while K is in flight;
 //   O = O * exp2(m_old - m_new) + O_blk    in registers (128 fp32 per thread), no read-modify-write of TMEM.
-// The two MMAs of a block and the softmax between them run one after the other (no overlap yet): the point of this
-// kernel is to take prompt attention off the CUDA cores -- the single-query kernel it replaces re-reads every key for
-// every row and reduces every score with shuffles.  Every wait is bounded; a CTA that gives up writes zeros.
+// Inside a CTA the two MMAs of a block and the softmax between them run one after the other; two CTAs share an SM
+// (96 KB of shared memory and 256 TMEM columns each) and fill each other's gaps.  The point of this kernel is to take
+// prompt attention off the CUDA cores -- the single-query kernel it replaces re-reads every key for every row and
+// reduces every score with shuffles.  Every wait is bounded; a CTA that gives up writes zeros.
 #include <atomic>
 
 #include "common.cuh"
@@ -28,8 +29,25 @@ constexpr int kPfThreads = 160;    // warps 0..3: one thread per query row; warp
 constexpr int kSub = kTile * 64 * 2;  // one [128 x 64] bf16 sub-tile: 16 KB
 constexpr float kLog2e = 1.4426950408889634f;
 
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Shared-memory descriptor of an MN-major operand tile with 128-byte swizzle: rows of 128 bytes hold 64 consecutive
+// M/N elements of one k; `lbo` bytes to the next 64 M/N elements, `sbo` bytes to the next 8 k.
+__device__ __forceinline__ uint64_t make_smem_desc_mn(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)(lbo >> 4) << 16;
+  d |= (uint64_t)(sbo >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
 struct PfArgs {
-  const bf16* v_pages;
   const int32_t* block_table;
   int max_pages;
   const int32_t* tiles;  // [n_tiles][4]: cache slot, first row (index into qkv / out), rows, position of the first row
@@ -39,14 +57,15 @@ struct PfArgs {
   int32_t* status;  // optional: set to 1 when a wait expired
 };
 
-__global__ void __launch_bounds__(kPfThreads, 1) prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q,
+__global__ void __launch_bounds__(kPfThreads, 2) prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                          const __grid_constant__ CUtensorMap map_k,
+                                                                         const __grid_constant__ CUtensorMap map_v,
                                                                          PfArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* sq = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sk = sq + 2 * kSub;   // K block   [128 keys][128 d]   as two d-halves
-  uint8_t* sv = sk + 2 * kSub;   // V^T block [128 d][128 keys]   as two key-halves
-  uint8_t* sp = sv + 2 * kSub;   // P block   [128 q][128 keys]   as two key-halves
+  uint8_t* sv = sk + 2 * kSub;   // V block   [128 keys][128 d]   as two d-halves, exactly as the pages hold it
+  uint8_t* sp = sk;              // P block   [128 q][128 keys]   as two key-halves: over K, which S = Q K^T has consumed by then
   __shared__ uint64_t kbar, sbar, obar;
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
@@ -68,6 +87,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_attn_tc_kernel(const __
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     tma_prefetch_desc(&map_q);
     tma_prefetch_desc(&map_k);
+    tma_prefetch_desc(&map_v);
   }
   if (warp == 4) tmem_alloc(&tmem_slot, 256);
   tc_fence_before();
@@ -75,6 +95,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_attn_tc_kernel(const __
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
   constexpr uint32_t idesc = make_idesc(kTile, kTile);
+  constexpr uint32_t idesc_pv = idesc | (1u << 16);  // B operand MN-major
 
   // per-row state (threads 0..127)
   float o_reg[kD];
@@ -85,48 +106,44 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_attn_tc_kernel(const __
   const float scale = rsqrtf((float)kD) * kLog2e;
   bool ok = true;
 
+  // Block-table entries are read one block ahead (lane p of warp 4 keeps page p of the block's eight), so that no block
+  // starts with a dependent chain of two global round trips.
+  auto page_of = [&](int pg) { return pg < n_pages ? bt[pg] : -1; };
+  int page_next = (warp == 4 && lane < kTile / kPS) ? page_of(lane) : -1;
+
   for (int kb = 0; kb < n_blocks; ++kb) {
     const uint32_t par = kb & 1;
     const int page0 = kb * (kTile / kPS);
-    // ---- loads: K pages (and Q once) by TMA; V transposed by the row threads ---------------------------------------------
-    if (tid == 128) {
-      const int valid = min(kTile / kPS, n_pages - page0);
-      mbar_expect_tx(&kbar, (uint32_t)valid * 2 * (kPS * 128) + (kb == 0 ? 2 * kSub : 0));
-      if (kb == 0) {
-        tma_load_2d(sq, &map_q, h * kD, row0, &kbar);
-        tma_load_2d(sq + kSub, &map_q, h * kD + 64, row0, &kbar);
-      }
-      for (int p = 0; p < valid; ++p) {
-        const int page = bt[page0 + p];
-        const int r = (page * a.Hkv + kvh) * kPS;
-        tma_load_2d(sk + p * (kPS * 128), &map_k, 0, r, &kbar);
-        tma_load_2d(sk + kSub + p * (kPS * 128), &map_k, 64, r, &kbar);
-      }
-    }
-    if (tid < kTile) {
-      // this thread's key of the block: row `tid` of V, written as column `tid` of V^T (swizzled K-major B operand)
-      const int key = kb * kTile + tid;
-      const int pg = key / kPS;
-      uint4 v[16];
-      if (pg < n_pages) {
-        const int page = bt[pg];
-        const uint4* src = reinterpret_cast<const uint4*>(a.v_pages + (((size_t)page * a.Hkv + kvh) * kPS + key % kPS) * kD);
-#pragma unroll
-        for (int c = 0; c < 16; ++c) v[c] = __ldg(src + c);
-      } else {
-#pragma unroll
-        for (int c = 0; c < 16; ++c) v[c] = make_uint4(0u, 0u, 0u, 0u);  // probabilities there are 0: keep 0 * v finite
-      }
-      const int cx = (tid & 63) >> 3;
-#pragma unroll
-      for (int c = 0; c < 16; ++c) {
-        const bf16* e = reinterpret_cast<const bf16*>(&v[c]);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int d = c * 8 + i;
-          // row d at d*128 bytes; its 16-byte chunk cx sits at ((cx ^ (d & 7)) << 4)
-          *reinterpret_cast<bf16*>(sv + (tid >> 6) * kSub + d * 128 + ((cx ^ (d & 7)) << 4) + (tid & 7) * 2) = e[i];
+    const int page_cur = page_next;
+    const int valid = min(kTile / kPS, n_pages - page0);
+    if (kb + 1 < n_blocks && warp == 4 && lane < kTile / kPS) page_next = page_of(page0 + kTile / kPS + lane);
+    // ---- loads: K and V pages (and Q once) by TMA -----------------------------------------------------------------------------
+    if (warp == 4) {
+      if (lane == 0) {
+        mbar_expect_tx(&kbar, (uint32_t)valid * 4 * (kPS * 128) + (kb == 0 ? 2 * kSub : 0));
+        if (kb == 0) {
+          tma_load_2d(sq, &map_q, h * kD, row0, &kbar);
+          tma_load_2d(sq + kSub, &map_q, h * kD + 64, row0, &kbar);
         }
+      }
+      __syncwarp();
+      if (lane < valid) {  // one page per lane, both 64-column halves of K and of V (a missing table entry reads as rows before 0: zeros)
+        const int r = (page_cur * a.Hkv + kvh) * kPS;
+        tma_load_2d(sk + lane * (kPS * 128), &map_k, 0, r, &kbar);
+        tma_load_2d(sk + kSub + lane * (kPS * 128), &map_k, 64, r, &kbar);
+        tma_load_2d(sv + lane * (kPS * 128), &map_v, 0, r, &kbar);
+        tma_load_2d(sv + kSub + lane * (kPS * 128), &map_v, 64, r, &kbar);
+      }
+    } else if (n_keys - kb * kTile < kTile) {
+      // Last block, not full: the V rows of keys that do not exist (the tail of the last page, whatever the cache holds
+      // there, and the pages that were not loaded) are zeroed once the copies have landed -- their probabilities are 0,
+      // but 0 * NaN is not.  K needs nothing: those scores are masked.  (A swizzled row stays inside its own 128 bytes.)
+      if (!mbar_wait(&kbar, par, &s_abort)) s_abort = 1;
+      if (tid >= n_keys - kb * kTile) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half)
+#pragma unroll
+          for (int c = 0; c < 8; ++c) reinterpret_cast<uint4*>(sv + half * kSub + tid * 128)[c] = make_uint4(0u, 0u, 0u, 0u);
       }
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -151,20 +168,29 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_attn_tc_kernel(const __
       if (!mbar_wait(&sbar, par, &s_abort)) s_abort = 1;
       tc_fence_after();
       const uint32_t t_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
-      // pass 1: row maximum over the valid keys
+      // Only the blocks on or past the diagonal need the causal / length mask (uniform per CTA): every row of the
+      // tile sees every key of the blocks before.
+      const bool need_mask = kb * kTile + kTile - 1 > pos0;
+      // pass 1: row maximum over the valid keys (of the raw scores: the scale is positive)
       float mx = -INFINITY;
 #pragma unroll 1
       for (int c0 = 0; c0 < kTile; c0 += 32) {
         float s[32];
         tmem_ld32(t_addr + c0, s);
+        if (!need_mask) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int key = kb * kTile + c0 + i;
-          if (key <= q_pos && key < n_keys) mx = fmaxf(mx, s[i] * scale);
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, s[i]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int key = kb * kTile + c0 + i;
+            if (key <= q_pos && key < n_keys) mx = fmaxf(mx, s[i]);
+          }
         }
       }
-      const float m_new = fmaxf(m_run, mx);
-      corr = (m_run == -INFINITY) ? 0.f : exp2f(m_run - m_new);  // (m_new == -inf: nothing seen yet, l and o are 0 anyway)
+      const float m_new = fmaxf(m_run, mx * scale);
+      corr = (m_run == -INFINITY) ? 0.f : fast_exp2(m_run - m_new);  // (m_new == -inf: nothing seen yet, l and o are 0 anyway)
+      const float neg_m = m_new == -INFINITY ? 0.f : -m_new;       // (then every key of the block is masked)
       // pass 2: probabilities -> P (bf16, A-operand layout), row sum
       float lsum = 0.f;
 #pragma unroll 1
@@ -174,12 +200,20 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_attn_tc_kernel(const __
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           float p[8];
+          if (!need_mask) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int key = kb * kTile + c0 + g * 8 + i;
-            const bool valid = key <= q_pos && key < n_keys && m_new != -INFINITY;
-            p[i] = valid ? exp2f(s[g * 8 + i] * scale - m_new) : 0.f;
-            lsum += p[i];
+            for (int i = 0; i < 8; ++i) {
+              p[i] = fast_exp2(fmaf(s[g * 8 + i], scale, neg_m));
+              lsum += p[i];
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int key = kb * kTile + c0 + g * 8 + i;
+              const bool valid = key <= q_pos && key < n_keys;
+              p[i] = valid ? fast_exp2(fmaf(s[g * 8 + i], scale, neg_m)) : 0.f;
+              lsum += p[i];
+            }
           }
           const int keyc = c0 + g * 8;  // first key of this 16-byte chunk inside the block
           const int cx = (keyc & 63) >> 3;
@@ -198,10 +232,14 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_attn_tc_kernel(const __
       if (!s_abort) {
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
+          // A = P, K-major: 16 keys further = 32 bytes = +2 in the address field.  B = V as the pages hold it, [key][dim]:
+          // the dimension (N) is the contiguous one ("MN-major"), 64 of it per 128-byte row, the second 64 one sub-tile
+          // (leading byte offset) further, 8 keys per 1024-byte swizzle group (stride byte offset), 16 keys = 2048 bytes.
           const uint64_t adesc = make_smem_desc(smem_u32(sp + j * kSub));
-          const uint64_t bdesc = make_smem_desc(smem_u32(sv + j * kSub));
 #pragma unroll
-          for (int k = 0; k < 4; ++k) umma_bf16(tmem_base + kTile, adesc + 2 * k, bdesc + 2 * k, idesc, (j > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < 4; ++k)
+            umma_bf16(tmem_base + kTile, adesc + 2 * k, make_smem_desc_mn(smem_u32(sv + (j * 4 + k) * 2048), kSub, 1024), idesc_pv,
+                      (j > 0 || k > 0) ? 1u : 0u);
         }
       }
       umma_commit(&obar);
@@ -265,12 +303,14 @@ extern "C" int mlora_prefill_attention(const void* d_qkv, int64_t ld, const void
                 "prefill_attention: 16-byte alignment of tensors and row pitches");
   MLORA_REQUIRE(n_tiles <= 2147483647 / 4 && Hq <= 65535, "prefill_attention: too many tiles / heads");
   if (n_tiles == 0 || T == 0) return MLORA_OK;
-  CUtensorMap mq, mk;
+  CUtensorMap mq, mk, mv;
   int rc = make_map(&mq, d_qkv, T, Hq * kD, ld, kTile, 64);  // only the q part of every row is mapped
   if (rc) return rc;
   rc = make_map(&mk, d_k_pages, (long long)n_pages_total * Hkv * kPS, kD, kD, kPS, 64);
   if (rc) return rc;
-  constexpr int smem = 8 * kSub + 1024;
+  rc = make_map(&mv, d_v_pages, (long long)n_pages_total * Hkv * kPS, kD, kD, kPS, 64);
+  if (rc) return rc;
+  constexpr int smem = 6 * kSub + 1024;  // Q, K (= P), V^T
   static std::atomic<unsigned long long> attr_done{0};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -279,8 +319,8 @@ extern "C" int mlora_prefill_attention(const void* d_qkv, int64_t ld, const void
     if (e != cudaSuccess) return fail(MLORA_ECUDA, "prefill_attention: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     attr_done.fetch_or(1ull << (dev & 63), std::memory_order_release);
   }
-  PfArgs a{(const bf16*)d_v_pages, d_block_table, max_pages, d_tiles, Hq, Hkv, (bf16*)d_out, ld_out, d_status};
-  prefill_attn_tc_kernel<<<dim3(n_tiles, Hq), kPfThreads, smem, (cudaStream_t)stream>>>(mq, mk, a);
+  PfArgs a{d_block_table, max_pages, d_tiles, Hq, Hkv, (bf16*)d_out, ld_out, d_status};
+  prefill_attn_tc_kernel<<<dim3(n_tiles, Hq), kPfThreads, smem, (cudaStream_t)stream>>>(mq, mk, mv, a);
   count_launch();
   MLORA_CHECK_LAUNCH("prefill_attn_tc_kernel");
   return MLORA_OK;

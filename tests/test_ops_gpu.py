@@ -389,8 +389,9 @@ def test_prompt_attention_on_tensor_cores(ops, cuda, Hq, Hkv):
     for slot, old, n in seqs:
         for p in range((old + n + ps - 1) // ps):
             bt[slot, p] = next(it)
-    kp = torch.zeros(n_pages, Hkv, ps, D, dtype=torch.bfloat16, device=cuda)
-    vp = torch.zeros_like(kp)
+    # pages start out as NaN: what lies behind a sequence's last token must not reach any output
+    kp = torch.full((n_pages, Hkv, ps, D), float("nan"), dtype=torch.bfloat16, device=cuda)
+    vp = torch.full_like(kp, float("nan"))
     W = (Hq + 2 * Hkv) * D
     hist = {}
     # the earlier chunk of slot 3 goes in first, through the same append kernel
