@@ -154,6 +154,24 @@ int mlora_linear(const void* d_x, int64_t ldx, const void* d_W, void* d_y, int64
                  const int32_t* d_ranks, const float* d_scales, const int32_t* d_slots,
                  int32_t n_adapters, int32_t r_max, int32_t n_mod, const int32_t* h_mod_offsets,
                  int32_t flags, void* d_work, size_t work_bytes, void* stream);
+/* mlora_linear with the residual add + RMSNorm that sits between two decoder projections folded into their epilogues
+ * (T <= 32, tensor-core kernel only: d_work required).  The reference runs these as separate modules: o_proj, residual
+ * add, post_attention_layernorm, gate/up (huggingface LlamaDecoderLayer as wrapped by
+ * huggingface/custom_peft/wrap_model.py; tvm/llama_auto_batcher/llama_for_causal_lm.py:96-112).  RMSNorm is
+ * h = x * w / rms(x); the factor 1/rms(x) of a row commutes with the next linear map, so
+ *   producer (d_res != NULL): d_res[t, o] (fp32, pitch ld_res) += y[t, o];  d_y[t, o] = bf16(d_res[t, o] * d_norm_w[o]);
+ *       d_sumsq_out[(o / 128) * 32 + t] = sum over that block of 128 outputs of d_res[t, o]^2   (ceil(out/128) * 32 floats);
+ *   consumer (d_sumsq_in != NULL): every output row t is multiplied by
+ *       rsqrt(sum_{j < n_sumsq_in} d_sumsq_in[j * 32 + t] / norm_dim + eps) before the activation (SiLU*up) and the store.
+ * A call may be both.  Sums are taken in a fixed order (deterministic).  Not with MLORA_LORA_PER_ROW / MLORA_FORCE_SIMT;
+ * the producer form not with MLORA_SILU_MUL / MLORA_OUT_F32.  Rounding differs from norm-then-project (bf16(x*w) * 1/rms in
+ * fp32 instead of bf16(x*w/rms)); both are within the path's bf16 tolerance. */
+int mlora_linear_norm(const void* d_x, int64_t ldx, const void* d_W, void* d_y, int64_t ldy, int32_t T, int32_t in,
+                      int32_t out, const float* d_u, const void* d_B_all, const int32_t* d_ranks,
+                      const float* d_scales, const int32_t* d_slots, int32_t n_adapters, int32_t r_max, int32_t n_mod,
+                      const int32_t* h_mod_offsets, int32_t flags, void* d_work, size_t work_bytes, float* d_res,
+                      int64_t ld_res, const void* d_norm_w, float* d_sumsq_out, const float* d_sumsq_in,
+                      int32_t n_sumsq_in, float eps, int32_t norm_dim, void* stream);
 /* mlora_lora_shrink + mlora_linear as ONE call, i.e. the whole of
  * base_layer(x) + bmm(bmm(x, A), B*scaling) (huggingface/custom_peft/lora_gatherbmm_linear_layer.py:15-20).
  * d_A_all as for mlora_lora_shrink; d_u [T, n_mod*r_max] float32 is scratch the call writes before it

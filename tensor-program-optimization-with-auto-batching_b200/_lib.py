@@ -38,6 +38,8 @@ PROTOTYPES = {
     "mlora_pack_weight": (C.c_int, [_vp, _i32, _i32, _vp, _vp]),
     "mlora_linear": (C.c_int, [_vp, _i64, _vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32,
                                C.POINTER(_i32), _i32, _vp, _sz, _vp]),
+    "mlora_linear_norm": (C.c_int, [_vp, _i64, _vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32,
+                                    C.POINTER(_i32), _i32, _vp, _sz, _vp, _i64, _vp, _vp, _vp, _i32, C.c_float, _i32, _vp]),
     "mlora_lora_linear": (C.c_int, [_vp, _i64, _vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32,
                                     _i32, C.POINTER(_i32), _i32, _vp, _sz, _vp]),
     "mlora_decode_chain": (C.c_int, [C.POINTER(ChainPhase), _i32, _i32, _vp, _vp, _vp, _i32, _vp, _sz, _vp]),

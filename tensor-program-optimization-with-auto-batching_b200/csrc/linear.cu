@@ -12,7 +12,7 @@ static int linear_impl(const void* d_x, int64_t ldx, const void* d_W, void* d_y,
                        int32_t out, const void* d_A_all, const float* d_u, const void* d_B_all,
                        const int32_t* d_ranks, const float* d_scales, const int32_t* d_slots, int32_t n_adapters,
                        int32_t r_max, int32_t n_mod, const int32_t* h_mod_offsets, int32_t flags, void* d_work,
-                       size_t work_bytes, void* stream) {
+                       size_t work_bytes, void* stream, const NormFuse* nf = nullptr) {
   MLORA_REQUIRE(T >= 0 && in > 0 && out > 0, "linear: bad sizes T=%d in=%d out=%d", T, in, out);
   MLORA_REQUIRE(in % 8 == 0 && ldx % 8 == 0, "linear: in and ldx must be multiples of 8 (in=%d ldx=%lld)", in,
                 (long long)ldx);
@@ -65,6 +65,21 @@ static int linear_impl(const void* d_x, int64_t ldx, const void* d_W, void* d_y,
   }
   if (T == 0) return MLORA_OK;
   cudaStream_t st = (cudaStream_t)stream;
+  if (nf && (nf->res || nf->sumsq_in)) {
+    // residual + RMSNorm folded into the epilogues: only the decode-size instantiations of the tensor-core kernel do it
+    MLORA_REQUIRE(T <= 32, "linear_norm: at most 32 rows (T=%d)", T);
+    MLORA_REQUIRE(!(flags & (MLORA_FORCE_SIMT | MLORA_LORA_PER_ROW | MLORA_B_SPLIT)) && d_work && linear_tc_supported(a),
+                  "linear_norm: needs the tensor-core kernel (scratch buffer, 16-byte aligned operands, no per-row expand)");
+    if (nf->res) {
+      MLORA_REQUIRE(nf->norm_w && nf->sumsq_out && nf->ld_res >= out, "linear_norm: residual form needs norm_w, sumsq_out, ld_res >= out");
+      MLORA_REQUIRE(!(flags & (MLORA_SILU_MUL | MLORA_OUT_F32)), "linear_norm: the residual form writes bf16 rows without activation");
+    }
+    if (nf->sumsq_in)
+      MLORA_REQUIRE(nf->n_sumsq_in > 0 && nf->norm_dim > 0 && nf->eps >= 0.f, "linear_norm: bad n_sumsq_in=%d / norm_dim=%d",
+                    nf->n_sumsq_in, nf->norm_dim);
+    a.nf = *nf;
+    return launch_linear_tc(a, d_work, work_bytes, st);
+  }
   if (d_A_all) {
     MLORA_REQUIRE(d_u && aligned16(d_A_all) && aligned16(d_u), "lora_linear: A_all and u must be non-null and 16-byte aligned");
     const int rc = mlora_lora_shrink(d_x, ldx, d_A_all, d_ranks, d_slots, n_adapters, T, in, r_max, n_mod,
@@ -111,6 +126,19 @@ extern "C" int mlora_linear(const void* d_x, int64_t ldx, const void* d_W, void*
                             int32_t flags, void* d_work, size_t work_bytes, void* stream) {
   return linear_impl(d_x, ldx, d_W, d_y, ldy, T, in, out, nullptr, d_u, d_B_all, d_ranks, d_scales, d_slots,
                      n_adapters, r_max, n_mod, h_mod_offsets, flags, d_work, work_bytes, stream);
+}
+
+extern "C" int mlora_linear_norm(const void* d_x, int64_t ldx, const void* d_W, void* d_y, int64_t ldy, int32_t T,
+                                 int32_t in, int32_t out, const float* d_u, const void* d_B_all,
+                                 const int32_t* d_ranks, const float* d_scales, const int32_t* d_slots,
+                                 int32_t n_adapters, int32_t r_max, int32_t n_mod, const int32_t* h_mod_offsets,
+                                 int32_t flags, void* d_work, size_t work_bytes, float* d_res, int64_t ld_res,
+                                 const void* d_norm_w, float* d_sumsq_out, const float* d_sumsq_in,
+                                 int32_t n_sumsq_in, float eps, int32_t norm_dim, void* stream) {
+  MLORA_REQUIRE(d_res || d_sumsq_in, "linear_norm: neither a residual to update nor row sums to apply (use mlora_linear)");
+  NormFuse nf{d_res, ld_res, (const bf16*)d_norm_w, d_sumsq_out, d_sumsq_in, n_sumsq_in, eps, norm_dim};
+  return linear_impl(d_x, ldx, d_W, d_y, ldy, T, in, out, nullptr, d_u, d_B_all, d_ranks, d_scales, d_slots,
+                     n_adapters, r_max, n_mod, h_mod_offsets, flags, d_work, work_bytes, stream, &nf);
 }
 
 extern "C" int mlora_lora_linear(const void* d_x, int64_t ldx, const void* d_W, void* d_y, int64_t ldy, int32_t T,

@@ -4,6 +4,22 @@
 
 namespace mlora {
 
+// Residual add + RMSNorm folded into two neighbouring decode-size projections (tensor-core kernel, T <= 32):
+//   producer (res != nullptr):   res[t, o] += y[t, o];  y[t, o] = bf16(res[t, o] * norm_w[o])  -- the row's 1/rms is NOT
+//                                applied; sumsq_out[row_tile * 32 + t] = sum over the tile's 128 outputs of res[t, o]^2
+//   consumer (sumsq_in != nullptr): y[t, :] *= rsqrt(sum_j sumsq_in[j * 32 + t] / norm_dim + eps)  before the activation,
+//                                i.e. the 1/rms of its input rows, which is a per-row factor of a linear map.
+struct NormFuse {
+  float* res;
+  int64_t ld_res;
+  const bf16* norm_w;
+  float* sumsq_out;
+  const float* sumsq_in;
+  int n_sumsq_in;
+  float eps;
+  int norm_dim;
+};
+
 struct LinearArgs {
   const bf16* x;
   int64_t ldx;
@@ -21,6 +37,7 @@ struct LinearArgs {
   int flags;
   int n_adapters;        // slots >= n_adapters are treated as "no adapter"
   int full_rank;         // 1: every row uses all r_max entries (zero-padded), ranks[] is ignored
+  NormFuse nf;           // all zero: plain projection
 };
 
 // Module (q/k/v, gate/up ...) that owns output row o.

@@ -165,7 +165,7 @@ struct Cfg {
   static constexpr int kStageU = BN >= 128 ? 0 : kStageUMax;
   // staging of one 32-token output chunk; fp32 outputs of 128-token tiles leave through per-thread stores instead
   static constexpr int kOutBytes = 32 * BM * (BN >= 128 ? 2 : 4);
-  static constexpr int kAuxBytes = 1024 + 8 * BN * 4 + kStageU + kCacheBytes + kOutBytes;
+  static constexpr int kAuxBytes = 1024 + 8 * BN * 4 + kStageU + kCacheBytes + kOutBytes + 256 /*s_rstd*/;
   static constexpr int kBudget = 227 * 1024 - 1024 /*alignment slack*/ - 64 /*static*/;
   static constexpr int kWStages0 = (kBudget - kAuxBytes - kXStages * kXBytes) / kWBytes;
   static constexpr int kWStages = kWStages0 > 10 ? 10 : kWStages0;  // measured: 5 stages already saturate
@@ -284,6 +284,9 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
   int* x_list = x_tok + BN;
   float* x_scale = reinterpret_cast<float*>(x_list + BN);  // scale of each distinct slot
   float* s_u = x_scale + BN;                           // [BN * r_tot] when it fits
+  float* s_red = reinterpret_cast<float*>(aux + 512);                   // [4][32] per-warp partial sums of squares (NormFuse)
+  // (kAuxBytes also counts the operand cache and the output staging, which lie BEFORE aux: address from aux's own parts)
+  float* s_rstd = reinterpret_cast<float*>(aux + 1024 + 8 * BN * 4 + C::kStageU);  // [32] 1/rms of the input rows (NormFuse consumer)
   __shared__ int s_abort;
   __shared__ int s_last;
   __shared__ int s_nseg0;  // distinct adapters of the CTA's first token tile (listed before the roles start)
@@ -789,6 +792,18 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
     const bool stage_u = simt_lora && (size_t)BN * r_tot * sizeof(float) <= (size_t)C::kStageU;
     int staged_tok_tile = -1;
     int it = rg.it0, j = 0;
+    const NormFuse& nf = a.nf;
+    if constexpr (BN <= 32) {
+      if (nf.sumsq_in != nullptr) {  // (uniform) 1/rms of the input rows from the producer's per-tile sums of squares
+        if (etid < 32) {
+          float s = 0.f;
+#pragma unroll 8
+          for (int jj = 0; jj < nf.n_sumsq_in; ++jj) s += __ldcg(nf.sumsq_in + (size_t)jj * 32 + etid);
+          s_rstd[etid] = rsqrtf(s / (float)nf.norm_dim + nf.eps);
+        }
+        epi_bar_sync();
+      }
+    }
 
     while (it < rg.it1) {
       const Segment sg = next_segment<WAVE>(p, it, rg.it1);
@@ -811,9 +826,62 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
         staged_tok_tile = tok_tile;
       }
 
+      // NormFuse producer: this CTA will finish the tile (whole tile, or first contributor of a split one), so the
+      // residual values its epilogue adds are requested now, long before the accumulator is complete.
+      float rs[32];
+      float nw = 0.f;
+      bool do_res = false;
+      if constexpr (BN <= 32) {
+        do_res = nf.res != nullptr && (full_seg || (int)blockIdx.x == (int)(((long long)sg.tile * p.k_blocks) / p.per_cta));
+        if (do_res) {
+#pragma unroll
+          for (int i = 0; i < C::kChunk; ++i)
+            rs[i] = (t0 + i < a.T && row < a.out) ? __ldcg(nf.res + (size_t)(t0 + i) * nf.ld_res + row) : 0.f;
+          nw = row < a.out ? __bfloat162float(nf.norm_w[row]) : 0.f;
+        }
+      }
+
       // Adds the CUDA-core LoRA expand if any, applies SiLU*up, stores.  v[i] = (token t0+c0+i, row).
       auto finish = [&](float (&v)[32], int c0) {
         if (LM == 1) simt_lora_expand<BN>(a, v, c0, t0, row, r_tot, stage_u, s_slots, s_u);
+        if constexpr (BN <= 32) {
+          if (nf.sumsq_in != nullptr) {
+#pragma unroll
+            for (int i = 0; i < C::kChunk; ++i) v[i] *= s_rstd[c0 + i];
+          }
+          if (do_res) {
+            float sq[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) sq[i] = 0.f;
+#pragma unroll
+            for (int i = 0; i < C::kChunk; ++i) {
+              const int t = t0 + c0 + i;
+              const bool live = t < a.T && row < a.out;
+              const float xr = rs[i] + v[i];
+              if (live) {
+                nf.res[(size_t)t * nf.ld_res + row] = xr;
+                sq[i] = xr * xr;
+              }
+              v[i] = xr * nw;
+            }
+            // sum over the warp's 32 rows, token by token: after the five exchange steps lane l holds token l's sum
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) {
+              const bool up = (lane & off) != 0;
+#pragma unroll
+              for (int jj = 0; jj < off; ++jj) {
+                const float send = up ? sq[jj] : sq[jj + off];
+                const float keep = up ? sq[jj + off] : sq[jj];
+                sq[jj] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+              }
+            }
+            s_red[q * 32 + lane] = sq[0];
+            epi_bar_sync();
+            if (etid < 32)
+              nf.sumsq_out[(size_t)row_tile * 32 + etid] = (s_red[etid] + s_red[32 + etid]) + (s_red[64 + etid] + s_red[96 + etid]);
+            epi_bar_sync();  // s_red is free again
+          }
+        }
         if (p.tma_store) {
           // registers -> shared memory [tokens][outputs of the tile] -> one TMA store (which also clips
           // tokens >= T and outputs >= out); far fewer instructions than 32 strided stores per thread

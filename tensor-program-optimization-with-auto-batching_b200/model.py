@@ -313,6 +313,10 @@ class Engine:
         self._graphs = {}
         self.n_distinct = 0  # distinct adapters among the rows staged for the next pass (set with self.slots)
         self.fuse_norm_shrink = os.environ.get("MLORA_FUSE_NORM_SHRINK", "1") != "0"
+        # decode passes of <= 32 rows: the residual add + RMSNorm between the o projection and gate|up folded into the two
+        # projections' epilogues (mlora_linear_norm) -- one launch fewer per layer
+        self.fold_norm = os.environ.get("MLORA_FOLD_NORM", "1") != "0"
+        self.sumsq = torch.zeros(-(-m.H // 128) * 32, dtype=torch.float32, device=dev)
         # decode-size passes can run everything between two attention calls as one persistent launch
         # (mlora_decode_chain); measured slower than the separate launches on the benchmark's step, so off unless asked for
         self.use_chain = os.environ.get("MLORA_CHAIN", "0") == "1"
@@ -496,13 +500,13 @@ class Engine:
                 ops.kv_append_rope(qkv, kp, vp, kv.block_table, row_slot, row_pos, m.Hq, m.Hkv, m.D, kv.page_size,
                                    m.theta)
             st_o = lw.lora.get("o")
-            if (st_o is not None and slots is not None and self.fuse_o_shrink and fused_append and T <= 1024
+            lora_o = st_o is not None and slots is not None
+            u_o = self.u.view(-1)[: T * st_o.r_max].view(T, st_o.r_max) if lora_o else None
+            if (lora_o and self.fuse_o_shrink and fused_append and T <= 1024
                     and ops.attention_shrink_fits(T, m.Hq, kv.block_table.shape[1], st_o)):
                 # attention and the o-projection's shrink in one launch; the projection then only expands
-                u_o = self.u.view(-1)[: T * st_o.r_max].view(T, st_o.r_max)
                 ops.paged_attention_shrink(qkv, kp, vp, kv.block_table, row_slot, row_pos, m.Hq, m.Hkv, m.D, kv.page_size,
                                            m.theta, fused_append, attn, st_o, slots, u_o, self.ws_oshrink)
-                ops.linear(attn, lw.w_o, st_o, slots, u=u_o, flags=self._lora_flags(T, st_o, 0), out=y, work=self.ws_linear)
             else:
                 if not fused_append and self.tc_prefill and self._n_pf_tiles > 0:
                     ops.prefill_attention(qkv, kp, vp, kv.block_table, self.pf_tiles, self._n_pf_tiles, m.Hq, m.Hkv, m.D,
@@ -510,12 +514,28 @@ class Engine:
                 else:
                     ops.paged_attention(qkv, kp, vp, kv.block_table, row_slot, row_pos, m.Hq, m.Hkv, m.D, kv.page_size,
                                         m.theta, fused_append, out=attn, work=self.ws_attn)
-                self._proj(attn, lw.w_o, st_o, slots, y)
-            # row-parallel partials (base + LoRA) -> full o_proj output, added to the residual, normalised
-            self._reduce_norm(y, res, lw.ln2, xn)
-            if not self._mlp_chained(T, lw, slots, xn, act, y):
-                self._proj(xn, lw.w_gu, lw.lora.get("gu"), slots, act, flags=SILU_MUL)
+                if lora_o:
+                    ops.lora_shrink(attn, st_o, slots, out=u_o)
+            fl_o = self._lora_flags(T, st_o, 0) if lora_o else (SHARE_LORA_KERNEL if slots is not None else 0)
+            if (self.fold_norm and fused_append and T <= 32 and m.tp_size == 1 and not self.chain_mlp
+                    and not fl_o & LORA_PER_ROW and (lw.lora.get("gu") is None or slots is None)):
+                # residual add + RMSNorm folded into the two projections around it: o writes the residual, the rows
+                # times the norm weight and per-tile sums of squares; gate|up scales its output rows by their 1/rms
+                ops.linear_norm(attn, lw.w_o, st_o if lora_o else None, slots, u=u_o, flags=fl_o, out=xn, work=self.ws_linear,
+                                res=res, norm_w=lw.ln2, sumsq_out=self.sumsq)
+                ops.linear_norm(xn, lw.w_gu, flags=SILU_MUL | (SHARE_LORA_KERNEL if slots is not None else 0), out=act,
+                                work=self.ws_linear, sumsq_in=self.sumsq, n_sumsq_in=-(-m.H // 128), eps=m.eps, norm_dim=m.H)
                 self._proj(act, lw.w_down, lw.lora.get("down"), slots, y)
+            else:
+                if lora_o:
+                    ops.linear(attn, lw.w_o, st_o, slots, u=u_o, flags=fl_o, out=y, work=self.ws_linear)
+                else:
+                    ops.linear(attn, lw.w_o, flags=fl_o, out=y, work=self.ws_linear)
+                # row-parallel partials (base + LoRA) -> full o_proj output, added to the residual, normalised
+                self._reduce_norm(y, res, lw.ln2, xn)
+                if not self._mlp_chained(T, lw, slots, xn, act, y):
+                    self._proj(xn, lw.w_gu, lw.lora.get("gu"), slots, act, flags=SILU_MUL)
+                    self._proj(act, lw.w_down, lw.lora.get("down"), slots, y)
             delta = y  # (under tensor parallelism still a partial sum: reduced together with the next norm)
         self._reduce_norm(delta, res, m.norm, xn)
         if lm_rows is not None:

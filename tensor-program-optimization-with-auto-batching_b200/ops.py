@@ -261,6 +261,47 @@ def linear(x, W, stack: LoraStack = None, slots=None, u=None, flags: int = 0, ou
     return out
 
 
+def linear_norm(x, W, stack: LoraStack = None, slots=None, u=None, flags: int = 0, out=None, work=None, res=None,
+                norm_w=None, sumsq_out=None, sumsq_in=None, n_sumsq_in=0, eps=0.0, norm_dim=0):
+    """``mlora_linear_norm``: a decode-size projection (T <= 32) that takes part in a folded residual add + RMSNorm.
+    Producer (``res``, ``norm_w``, ``sumsq_out``): res += y; out = bf16(res * norm_w) and per-128-output sums of
+    squares; consumer (``sumsq_in``, ``n_sumsq_in``, ``eps``, ``norm_dim``): output rows scaled by their input
+    rows' 1/rms before the activation.  ``u`` must already hold the shrink outputs when ``stack`` is given."""
+    _need_cuda(x, W)
+    if isinstance(W, PackedWeight):
+        flags |= W_PACKED
+    if stack is not None and stack.b_packed:
+        flags |= B_PACKED
+    T, K = x.shape
+    N = W.shape[0]
+    cols = N // 2 if flags & SILU_MUL else N
+    if out is None:
+        out = torch.empty(T, cols, dtype=torch.float32 if flags & OUT_F32 else torch.bfloat16, device=x.device)
+    if stack is not None and u is None:
+        raise ValueError("mlora.linear_norm: pass the shrink outputs u")
+    mod = None
+    if stack is not None and stack.n_mod > 1 and not flags & SILU_MUL:
+        mod = (C.c_int32 * (stack.n_mod + 1))(*stack.mod_offsets)
+    wb = _lib.lib().mlora_linear_workspace(T, K, N)
+    if work is not None:
+        if work.numel() < wb:
+            raise ValueError(f"mlora.linear_norm: scratch of {wb} bytes needed, {work.numel()} given")
+        ws, wb = work, work.numel()
+    else:
+        ws = workspace(wb, x.device, "linear")
+    if res is not None and (res.dtype != torch.float32 or sumsq_out is None or sumsq_out.numel() < -(-N // 128) * 32):
+        raise ValueError("mlora.linear_norm: res must be fp32 and sumsq_out hold ceil(out/128)*32 floats")
+    check(_lib.lib().mlora_linear_norm(
+        _ptr(x), x.stride(0), _ptr(W), _ptr(out), out.stride(0), T, K, N,
+        _ptr(u) if stack is not None else None, _ptr(stack.B_all) if stack is not None else None,
+        _ptr(stack.ranks) if stack is not None else None, _ptr(stack.scales) if stack is not None else None,
+        _ptr(slots) if stack is not None else None, stack.A_all.shape[0] if stack is not None else 0,
+        stack.r_max if stack is not None else 0, stack.n_mod if stack is not None else 1, mod, flags, _ptr(ws), wb,
+        _ptr(res), res.stride(0) if res is not None else 0, _ptr(norm_w), _ptr(sumsq_out), _ptr(sumsq_in),
+        int(n_sumsq_in), float(eps), int(norm_dim), _stream()), "mlora_linear_norm")
+    return out
+
+
 # ---------------------------------------------------------------- chained decode projections
 @dataclass
 class ChainStep:

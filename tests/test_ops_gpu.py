@@ -439,6 +439,69 @@ def test_prompt_attention_on_tensor_cores(ops, cuda, Hq, Hkv):
                               ps, out, status)
 
 
+@pytest.mark.parametrize("T,H,I,lora", [(32, 4096, 11008, True), (1, 4096, 11008, False), (7, 1024, 2816, True), (5, 320, 256, True)])
+def test_residual_and_norm_folded_into_the_projections(ops, cuda, T, H, I, lora):
+    """o projection -> residual add -> RMSNorm -> gate|up (SiLU) with the add and the norm folded into the two
+    projections' epilogues (``mlora_linear_norm``), against the three separate calls and against fp32 arithmetic."""
+    g = torch.Generator().manual_seed(T + H)
+    attn = torch.randn(T, H, generator=g).bfloat16().to(cuda)
+    res0 = torch.randn(T, H, generator=g).to(cuda)
+    Wo = (torch.randn(H, H, generator=g) * 0.03).bfloat16().to(cuda)
+    Wgu = (torch.randn(2 * I, H, generator=g) * 0.03).bfloat16().to(cuda)  # rows interleaved gate/up in blocks of 8
+    w = (1.0 + 0.1 * torch.randn(H, generator=g)).bfloat16().to(cuda)
+    eps = 1e-5
+    st = slots = u = None
+    if lora:
+        n_ad, r = 3, 16
+        A = (torch.randn(n_ad, r, H, generator=g) * 0.05).bfloat16().to(cuda)
+        B = (torch.randn(n_ad, H, r, generator=g) * 0.05).bfloat16().to(cuda)
+        st = ops.LoraStack(A, B, _i32([r] * n_ad, cuda), torch.full((n_ad,), 2.0, device=cuda), r, 1, (0, H))
+        if H % 128 == 0:
+            st = st.pack_b()
+        slots = (torch.arange(T) % (n_ad + 1) - 1).int().to(cuda)
+        u = ops.lora_shrink(attn, st, slots)
+    Wo_p, Wgu_p = ops.PackedWeight(Wo), ops.PackedWeight(Wgu)
+    # separate calls
+    y = ops.linear(attn, Wo_p, st, slots, u=u)
+    res_a = res0.clone()
+    h_a = ops.residual_rmsnorm(y, res_a, w, eps)
+    act_a = ops.linear(h_a, Wgu_p, flags=ops.SILU_MUL)
+    # folded
+    res_b = res0.clone()
+    n_part = -(-H // 128)
+    sumsq = torch.full((n_part * 32,), float("nan"), device=cuda)
+    h_b = ops.linear_norm(attn, Wo_p, st, slots, u=u, res=res_b, norm_w=w, sumsq_out=sumsq)
+    act_b = ops.linear_norm(h_b, Wgu_p, flags=ops.SILU_MUL, sumsq_in=sumsq, n_sumsq_in=n_part, eps=eps, norm_dim=H)
+    torch.cuda.synchronize()
+    assert int(ops.workspace(4, cuda, "linear")[:4].view(torch.int32)) == 0, "a bounded wait expired"
+    # the residual: fp32 accumulator added directly (the separate path rounds y to bf16 first)
+    torch.testing.assert_close(res_b, res_a, atol=4e-2, rtol=1e-2)
+    want_res = res0 + (attn.float() @ Wo.float().t() + (0 if not lora else sum(
+        2.0 * ((slots == s).float()[:, None] * (attn.float() @ A[s].float().t()) @ B[s].float().t()) for s in range(n_ad))))
+    torch.testing.assert_close(res_b, want_res, atol=2e-2, rtol=1e-2)
+    assert (res_b - want_res).abs().max() <= (res_a - want_res).abs().max() + 1e-3
+    # sums of squares of the new residual rows, per block of 128 features
+    ss = sumsq.view(n_part, 32)[:, :T].sum(0)
+    torch.testing.assert_close(ss, (res_b * res_b).sum(1), rtol=1e-4, atol=1e-3)
+    # the activation.  The two paths round the normalised rows at different points (bf16(x*w/rms) against bf16(x*w)
+    # with 1/rms applied in fp32 afterwards), so they differ from each other by what each differs from exact
+    # arithmetic: silu(g)*u of gate/up values of a few units, each carrying ~5e-3 of accumulated input rounding
+    # (the same two roundings emulated in fp32 on the CPU differ by up to 0.1 + 2 % at these sizes).
+    torch.testing.assert_close(act_b.float(), act_a.float(), atol=1e-1, rtol=2e-2)
+    rstd = torch.rsqrt((want_res * want_res).mean(1, keepdim=True) + eps)
+    hh = (want_res * rstd * w.float()) @ Wgu.float().t()
+    # de-interleave: blocks of 8 gate rows then 8 up rows
+    hh = hh.view(T, -1, 2, 8)
+    want_act = (torch.nn.functional.silu(hh[:, :, 0]) * hh[:, :, 1]).reshape(T, -1)
+    torch.testing.assert_close(act_b.float(), want_act, atol=1e-1, rtol=2e-2)
+    err_b = (act_b.float() - want_act).pow(2).mean().sqrt().item()
+    err_a = (act_a.float() - want_act).pow(2).mean().sqrt().item()
+    assert err_b <= 1.1 * err_a + 1e-4, (err_b, err_a)  # the folded form is no further from exact arithmetic
+    # refused where the kernel cannot do it
+    with pytest.raises(Exception):
+        ops.linear_norm(attn.repeat(40, 1)[:40], Wo_p, res=res0.repeat(40, 1)[:40].contiguous(), norm_w=w, sumsq_out=sumsq)
+
+
 def test_kv_begin_decode(ops, cuda):
     seq = _i32([5, 0, 9, 3], cuda)
     rows = _i32([2, 0], cuda)
