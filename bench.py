@@ -373,7 +373,7 @@ def run_13b_tp(args, rank, world, local_rank):
               "n_gpus": world, "tp_size": world, "layers": L, "steps": K, "warmup": W, "ms_per_step": ms_step,
               "scaling": "strong", "dtype": "bf16", "data": "synthetic",
               "config": {"requests": n_req, "adapters": n_ad, "adapter_ranks": ranks, "prompt_lens": "U[128,1024] seed 4",
-                         "mean_ctx": ctx_mean, "parallelism": f"tp{world} (Megatron column/row + NCCL all-reduce)"},
+                         "mean_ctx": ctx_mean, "parallelism": f"tp{world} (Megatron column/row + " + ("fused peer-memory exchange" if args.tp_collective == "peer" else "NCCL all-reduce") + ")"},
               "per_rank": {"algorithmic_bytes": per_rank, "achieved_gbs": per_rank / (ms_step * 1e6),
                            "hbm_frac": per_rank / (ms_step * 1e6) / peak, "peak_gbs": peak, "peak_source": src},
               "collectives": {"exchanges_per_step": 2 * L, "bytes_each": n_req * H * 2,

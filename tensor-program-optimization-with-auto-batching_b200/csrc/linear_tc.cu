@@ -1128,11 +1128,23 @@ Plan plan_for(int bn, int min_waves, int T, int in, int out) {
   pl.wave_gt = pl.wave_full = pl.wave_ch = pl.wave_ch_last = 0;
   const long long n_tiles = (long long)pl.row_tiles * pl.tok_tiles;
   if (pl.tok_tiles >= 4 && n_tiles >= min_waves * grid) {
-    // waves of (token tiles x row tiles)
-    int gt = (int)grid;
-    for (int d = 1; d <= 48 && d <= (int)grid; ++d)
-      if (grid % d == 0) gt = d;  // largest divisor of the grid up to 48 (148 SMs -> 37)
-    pl.wave_gt = gt < pl.tok_tiles ? gt : pl.tok_tiles;
+    // Waves of (token tiles x row tiles).  Token tiles per group: the group's token rows are what every CTA re-reads
+    // from L2 row tile after row tile, so they should stay resident next to the weight tiles in flight (<= 56 MB of the
+    // 126 MB), and row_tiles * group should fill whole rounds of the grid (the slots beyond it idle).  Among the sizes
+    // that fit, the one that wastes the fewest slots; the larger one on ties (fewer passes over the weights).
+    int gt = 1;
+    double best = 2.0;
+    for (int d = 1; d <= 48 && d <= pl.tok_tiles; ++d) {
+      if (d > 1 && (double)d * pl.bn * in * 2.0 > 56e6) break;
+      const long long tiles = (long long)pl.row_tiles * d;
+      const long long slots = (tiles + grid - 1) / grid * grid;
+      const double waste = (double)(slots - tiles) / (double)slots;
+      if (waste <= best + 1e-9) {
+        best = waste;
+        gt = d;
+      }
+    }
+    pl.wave_gt = gt;
     pl.wave_full = pl.tok_tiles / pl.wave_gt;
     const int gt_last = pl.tok_tiles - pl.wave_full * pl.wave_gt;
     pl.wave_ch = (int)(((long long)pl.row_tiles * pl.wave_gt + grid - 1) / grid);
