@@ -3,7 +3,8 @@
 // from the other GPUs' memory over NVLink -- no collective library call, no second pass over the data.
 //
 // One process per GPU.  Every rank owns an arena (cudaMalloc'ed here, exported as a CUDA IPC handle, mapped by
-// the peers):  header | flags [2][8][T_max] | inbox [2][8][T_max * H] bf16.
+// the peers):  header | flags [2][8][T_max] | gather flags [2][T_max] | inbox [2][8][T_max * H] bf16 | gather box
+// [2][T_max * H] bf16.
 // One exchange, on rank r, CTA t (= row t of the [T, H] partial result):
 //   1. push: row t of the local partial is stored into inbox[buf][r][t] of every peer (128-bit stores over
 //      NVLink), fenced at system scope, then flags[buf][r][t] of every peer is set to the exchange number;
@@ -11,12 +12,17 @@
 //      THIS GPU's memory (remote data is always read locally, never pulled across the link by a consumer);
 //   3. sum the G rows in rank order in fp32 (the own one from registers) -- every rank computes the same bits --,
 //      add the residual, RMSNorm, write.
+// With more than four ranks the exchange is two-step instead (each rank would otherwise store its whole partial result
+// seven times over): row t has an owner, rank t mod G; every rank stores its row t into the owner's inbox only, the owner
+// sums the G rows in rank order, rounds the sum to bf16 and stores it into every peer's gather box (+ flag); the others
+// wait for that one row.  Bytes out per rank: 2 (G-1)/G of the partial result instead of G-1 times it; same bits.
 // Rows are independent, so no rank waits for more than the row it is about to use.  `buf` alternates with the
 // exchange number: a rank can be at most one exchange ahead of a peer (it needs the peer's rows to finish one),
 // so two buffers are enough.  The exchange number lives in the arena and is advanced by the last CTA of each
 // launch, which keeps a launch replayable inside a CUDA graph.  No multicast load, no library kernel on peer
 // memory; every wait is bounded and ends in a status bit, never in a hang.
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -36,6 +42,7 @@ struct TpCtx {
   uint8_t* peer[kMaxWorld];
   bool open[kMaxWorld];
   uint32_t spin_limit;
+  int two_step;
 };
 
 struct TpArgs {
@@ -48,19 +55,26 @@ struct TpArgs {
   float eps;
   bf16* out;            // [T, H]: RMSNorm(res) * w, or the plain sum
   uint32_t spin_limit;
+  int two_step;         // rows have owners (rank t mod world): reduce there, gather the rounded sums
 };
 
 __host__ __device__ inline size_t flags_off(int T_max, int buf, int src, int t) {
   return kTpHeader + ((size_t)(buf * kMaxWorld + src) * T_max + t) * sizeof(int32_t);
 }
+__host__ __device__ inline size_t gflags_off(int T_max, int buf, int t) {
+  return kTpHeader + (size_t)2 * kMaxWorld * T_max * sizeof(int32_t) + ((size_t)buf * T_max + t) * sizeof(int32_t);
+}
 __host__ __device__ inline size_t inbox_base(int T_max) {
-  size_t b = kTpHeader + (size_t)2 * kMaxWorld * T_max * sizeof(int32_t);
+  size_t b = kTpHeader + (size_t)2 * (kMaxWorld + 1) * T_max * sizeof(int32_t);
   return (b + 255) & ~(size_t)255;
 }
 __host__ __device__ inline size_t inbox_off(int T_max, int H, int buf, int src, int t) {
   return inbox_base(T_max) + (((size_t)(buf * kMaxWorld + src) * T_max + t) * H) * sizeof(bf16);
 }
-size_t arena_bytes(int T_max, int H) { return inbox_off(T_max, H, 1, kMaxWorld - 1, T_max); }
+__host__ __device__ inline size_t gbox_off(int T_max, int H, int buf, int t) {
+  return inbox_base(T_max) + ((size_t)2 * kMaxWorld * T_max * H + ((size_t)buf * T_max + t) * H) * sizeof(bf16);
+}
+size_t arena_bytes(int T_max, int H) { return gbox_off(T_max, H, 1, T_max); }
 
 __device__ __forceinline__ void st_release_sys(int32_t* p, int32_t v) {
   asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -110,8 +124,11 @@ __global__ void __launch_bounds__(kTpThreads) tp_allreduce_norm_kernel(TpArgs a)
     const int k = (c * kTpThreads + tid) * 8;
     if (k < H) mine[c] = *reinterpret_cast<const uint4*>(a.partial + (size_t)t * H + k);
   }
+  const bool two = a.two_step != 0;
+  const int owner = two ? t % a.world : a.rank;  // (one-step: every rank reduces every row itself)
+  const bool reduce_here = owner == a.rank;
   for (int g = 0; g < a.world; ++g) {
-    if (g == a.rank) continue;
+    if (g == a.rank || (two && g != owner)) continue;
     bf16* dst = reinterpret_cast<bf16*>(a.peer[g] + inbox_off(a.T_max, H, buf, a.rank, t));
 #pragma unroll
     for (int c = 0; c < NCH; ++c) {
@@ -122,11 +139,11 @@ __global__ void __launch_bounds__(kTpThreads) tp_allreduce_norm_kernel(TpArgs a)
   // The CTA barrier orders every thread's stores before the flag stores below, whose system-scope release makes them
   // (cumulatively) visible to whoever acquires the flag: the row is in the peer's memory before its flag says so.
   __syncthreads();
-  if (tid < a.world && tid != a.rank)
+  if (tid < a.world && tid != a.rank && (!two || tid == owner))
     st_release_sys(reinterpret_cast<int32_t*>(a.peer[tid] + flags_off(a.T_max, buf, a.rank, t)), epoch);
 
   // ---- 2. wait for row t of every peer (it lands in this GPU's own memory) -------------------------------------------
-  if (tid < a.world && tid != a.rank) {
+  if (reduce_here && tid < a.world && tid != a.rank) {
     const int32_t* f = reinterpret_cast<const int32_t*>(a.local + flags_off(a.T_max, buf, tid, t));
     bool got = false;
     for (uint32_t spin = 0; spin < a.spin_limit; ++spin) {
@@ -141,16 +158,34 @@ __global__ void __launch_bounds__(kTpThreads) tp_allreduce_norm_kernel(TpArgs a)
       atomicOr(&hdr[2], 1 << tid);  // which peer's row never came
     }
   }
+  // two-step, row owned elsewhere: wait for the owner's rounded sum instead
+  if (!reduce_here && tid == 0) {
+    const int32_t* f = reinterpret_cast<const int32_t*>(a.local + gflags_off(a.T_max, buf, t));
+    bool got = false;
+    for (uint32_t spin = 0; spin < a.spin_limit; ++spin) {
+      if (ld_acquire_sys(f) >= epoch) {
+        got = true;
+        break;
+      }
+      __nanosleep(100);
+    }
+    if (!got) {
+      s_ok = 0;
+      atomicOr(&hdr[2], 1 << owner);
+    }
+  }
   __syncthreads();
   const bool ok = s_ok != 0;
 
-  // ---- 3. sum in rank order, residual, RMSNorm ------------------------------------------------------------------------
-  float v[NCH][8];
-  float ss = 0.f;
+  // ---- 3. sum in rank order (rounded to bf16: the value a separate all-reduce would have delivered), or take the
+  //         owner's; then residual, RMSNorm ------------------------------------------------------------------------------
+  uint4 total[NCH];
 #pragma unroll
   for (int c = 0; c < NCH; ++c) {
     const int k = (c * kTpThreads + tid) * 8;
-    if (k < H) {
+    total[c] = make_uint4(0u, 0u, 0u, 0u);
+    if (k >= H) continue;
+    if (reduce_here) {
       float acc[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[i] = 0.f;
@@ -165,12 +200,36 @@ __global__ void __launch_bounds__(kTpThreads) tp_allreduce_norm_kernel(TpArgs a)
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[i] += f[i];
       }
+      total[c] = pack8(acc);
+    } else if (ok) {
+      total[c] = __ldcg(reinterpret_cast<const uint4*>(a.local + gbox_off(a.T_max, H, buf, t)) + (k >> 3));
+    }
+  }
+  if (two && reduce_here) {  // (uniform per CTA) hand the rounded sum to every peer
+    for (int g = 0; g < a.world; ++g) {
+      if (g == a.rank) continue;
+      bf16* dst = reinterpret_cast<bf16*>(a.peer[g] + gbox_off(a.T_max, H, buf, t));
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
+        const int k = (c * kTpThreads + tid) * 8;
+        if (k < H) *reinterpret_cast<uint4*>(dst + k) = total[c];
+      }
+    }
+    __syncthreads();
+    if (tid < a.world && tid != a.rank)
+      st_release_sys(reinterpret_cast<int32_t*>(a.peer[tid] + gflags_off(a.T_max, buf, t)), epoch);
+  }
+  float v[NCH][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    const int k = (c * kTpThreads + tid) * 8;
+    if (k < H) {
       if (a.res) {
+        float acc[8];
+        unpack8(total[c], acc);
         float* r = a.res + (size_t)t * H + k;
         const float4 r0 = *reinterpret_cast<const float4*>(r), r1 = *reinterpret_cast<const float4*>(r + 4);
-        // the residual takes the sum as rounded to bf16: the value a separate all-reduce would have delivered
-        const uint4 rounded = pack8(acc);
-        unpack8(rounded, acc);
         v[c][0] = r0.x + acc[0], v[c][1] = r0.y + acc[1], v[c][2] = r0.z + acc[2], v[c][3] = r0.w + acc[3];
         v[c][4] = r1.x + acc[4], v[c][5] = r1.y + acc[5], v[c][6] = r1.z + acc[6], v[c][7] = r1.w + acc[7];
         *reinterpret_cast<float4*>(r) = make_float4(v[c][0], v[c][1], v[c][2], v[c][3]);
@@ -178,7 +237,7 @@ __global__ void __launch_bounds__(kTpThreads) tp_allreduce_norm_kernel(TpArgs a)
 #pragma unroll
         for (int i = 0; i < 8; ++i) ss = fmaf(v[c][i], v[c][i], ss);
       } else {
-        *reinterpret_cast<uint4*>(a.out + (size_t)t * H + k) = pack8(acc);
+        *reinterpret_cast<uint4*>(a.out + (size_t)t * H + k) = total[c];
       }
     }
   }
@@ -233,6 +292,8 @@ extern "C" int mlora_tp_create(int32_t rank, int32_t world, int32_t T_max, int32
   c->H = H;
   c->bytes = arena_bytes(T_max, H);
   c->spin_limit = kTpSpinDefault;
+  c->two_step = world > 4;  // measured: the one-step push wins at 2 and 4 ranks, loses to NCCL at 8
+  if (const char* e = getenv("MLORA_TP_TWO_STEP")) c->two_step = e[0] == '1';
   for (int g = 0; g < kMaxWorld; ++g) {
     c->peer[g] = nullptr;
     c->open[g] = false;
@@ -339,6 +400,7 @@ extern "C" int mlora_tp_allreduce_rmsnorm(void* ctx, const void* d_partial, floa
   a.eps = eps;
   a.out = (bf16*)d_out;
   a.spin_limit = c->spin_limit;
+  a.two_step = c->world > 1 ? c->two_step : 0;
   cudaStream_t st = (cudaStream_t)stream;
   if (H <= 2048)
     tp_allreduce_norm_kernel<1><<<T, kTpThreads, 0, st>>>(a);

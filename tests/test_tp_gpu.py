@@ -116,12 +116,14 @@ def test_two_way_tensor_parallel_over_nccl(synth, cuda):
         assert torch.equal(got[0][step][1], got[1][step][1])
 
 
-def _peer_worker(rank, G, port, q):
+def _peer_worker(rank, G, port, q, two_step):
     """The library's own exchange kernel (stores into the peers' memory, per-row flags, local reduction) on real
-    peers: op-level bit-exactness, the bounded wait running out, recovery, and the tensor-parallel decoder."""
+    peers: op-level bit-exactness, the bounded wait running out, recovery, and the tensor-parallel decoder.
+    ``two_step``: the form the library takes by itself beyond four ranks (rows reduced at their owner, sums gathered)."""
     import importlib
     import sys
     sys.path.insert(0, ROOT)
+    os.environ["MLORA_TP_TWO_STEP"] = "1" if two_step else "0"
     import torch.distributed as dist
     synth = importlib.import_module(f"{PKG}.synth")
     sharding = importlib.import_module(f"{PKG}.sharding")
@@ -188,7 +190,8 @@ def _peer_worker(rank, G, port, q):
     os._exit(0)
 
 
-def test_two_way_tensor_parallel_over_peer_memory_exchange(synth, cuda):
+@pytest.mark.parametrize("two_step", [False, True])
+def test_two_way_tensor_parallel_over_peer_memory_exchange(synth, cuda, two_step):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
@@ -197,7 +200,7 @@ def test_two_way_tensor_parallel_over_peer_memory_exchange(synth, cuda):
         port = s.getsockname()[1]
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_peer_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_peer_worker, args=(r, 2, port, q, two_step)) for r in range(2)]
     [p.start() for p in procs]
     got = dict(q.get(timeout=300) for _ in range(2))
     [p.join(60) for p in procs]
