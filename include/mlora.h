@@ -374,6 +374,10 @@ int mlora_kv_begin_decode(const int32_t* d_row_slot, int32_t* d_seq_lens, int32_
  *     mlora_residual_rmsnorm gives);  d_res == NULL: d_out = s (a plain all-reduce; d_out may be d_partial).
  * ONE kernel per rank: it stores its rows into the peers' arenas over NVLink, sets a per-row flag there, waits
  * (bounded) for the peers' rows to land in its own arena, and reduces locally.  T <= 512 and <= T_max, H <= 8192.
+ * Beyond four ranks (or with MLORA_TP_TWO_STEP=1 in the environment at mlora_tp_create; =0 forces the form above) the
+ * kernel works in two steps: row t is reduced by rank t mod world, which receives that row from every peer and stores
+ * the rounded sum into every peer's arena; same result bits, 2 (world-1)/world of the partial result leaves a rank
+ * instead of world-1 times it.  All ranks of a group must use the same form.
  * The calls of the ranks must pair up one to one; a rank whose peer's rows do not arrive within the spin limit
  * (mlora_tp_set_spin_limit polls of ~100 ns; default 2^22) sets bit g (rank g missing) in its status word
  * (mlora_tp_status), produces garbage for that exchange and returns -- it does not hang.  After such a failure
