@@ -49,6 +49,8 @@ struct TcParams {
   int tok_tiles;
   int wave_gt;     // 0: stream-K ranges; > 0: whole tiles, token tiles taken in groups of this many
   int wave_full, wave_ch, wave_ch_last;  // full groups, tiles per CTA in a full group / in the narrower last one
+  int wave_lanes;  // > 0: lane form -- CTA c serves token tile (c mod wave_gt) of every group and the row tiles
+                   // (c / wave_gt) + s * wave_lanes, s = 0 .. wave_ch - 1; wave_full = number of groups
   int per_cta;     // iterations (tile, k-block) per CTA
   int lora_mode;   // 0 none, 1 expand on CUDA cores in the epilogue, 2 expand on the tensor cores
   int lora_sub;    // K elements of one LoRA stage (16, 32 or 64 = row bytes 32, 64, 128)
@@ -198,6 +200,15 @@ struct Segment {
 // Slot `lt` of this CTA's walk -> tile id (token tile * row_tiles + row tile), or -1 where its chunk of that
 // group is shorter than the longest.
 __device__ __forceinline__ int wave_tile(const TcParams& p, int lt) {
+  if (p.wave_lanes > 0) {
+    // lane form: at step s the CTAs of one lane -- one per token tile of the group -- all read row tile lane + s * lanes,
+    // so a weight tile comes from HBM once per group and from L2 for the other wave_gt - 1 CTAs
+    const int grp = lt / p.wave_ch, st = lt - grp * p.wave_ch;
+    const int j = (int)blockIdx.x % p.wave_gt, lane = (int)blockIdx.x / p.wave_gt;
+    const int row = lane + st * p.wave_lanes, tok = grp * p.wave_gt + j;
+    if (lane >= p.wave_lanes || row >= p.row_tiles || tok >= p.tok_tiles) return -1;
+    return tok * p.row_tiles + row;
+  }
   int group, qi, gt, ch;
   const int full_slots = p.wave_full * p.wave_ch;
   if (lt < full_slots) {
@@ -285,6 +296,10 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
   float* x_scale = reinterpret_cast<float*>(x_list + BN);  // scale of each distinct slot
   float* s_u = x_scale + BN;                           // [BN * r_tot] when it fits
   float* s_red = reinterpret_cast<float*>(aux + 512);                   // [4][32] per-warp partial sums of squares (NormFuse)
+  // prompt-size tiles: the output warps build the cached LoRA operands (their own list of the tile's adapters; the
+  // cache holds at most 16 of them)
+  int* e_list = reinterpret_cast<int*>(aux + 512);                      // [16]  (decode-size tiles use this space as s_red)
+  float* e_scale = reinterpret_cast<float*>(aux + 512 + 64);            // [16]
   // (kAuxBytes also counts the operand cache and the output staging, which lie BEFORE aux: address from aux's own parts)
   float* s_rstd = reinterpret_cast<float*>(aux + 1024 + 8 * BN * 4 + C::kStageU);  // [32] 1/rms of the input rows (NormFuse consumer)
   __shared__ int s_abort;
@@ -502,6 +517,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
         const int u_off = mod * a.r_max;
         const int chunks = p.lora_sub / 8;  // 16-byte chunks per row
         const bool cached = lora_cached<BN>(p, n_seg);
+        if (BN >= 128 && cached) continue;  // prompt-size tiles: the output warps build the cache (below)
         if (cached && tok_tile * 8 + mod == cur_key) continue;  // operands already in the cache
         if (cached) {
           int w = 1;
@@ -738,7 +754,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
         if (cached && new_build && ok) {
           // every MMA that read the previous cache contents has been issued: let the builder overwrite
           // them once those MMAs retire, then wait for the new contents
-          if (n_build > 0) umma_commit(cache_empty);
+          if (BN < 128 && n_build > 0) umma_commit(cache_empty);  // (prompt sizes: the builders order themselves by acc_full)
           if (!mbar_wait(cache_full, n_build & 1, &s_abort)) {
             s_abort = 1;
             atomicOr(p.status, 64);
@@ -792,6 +808,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
     const bool stage_u = simt_lora && (size_t)BN * r_tot * sizeof(float) <= (size_t)C::kStageU;
     int staged_tok_tile = -1;
     int it = rg.it0, j = 0;
+    int e_tok_tile = -1, e_nseg = 0, e_key = -1;  // prompt-size tiles: the output warps' view of the LoRA operand cache
     const NormFuse& nf = a.nf;
     if constexpr (BN <= 32) {
       if (nf.sumsq_in != nullptr) {  // (uniform) 1/rms of the input rows from the producer's per-tile sums of squares
@@ -824,6 +841,78 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
         }
         epi_bar_sync();
         staged_tok_tile = tok_tile;
+      }
+
+      // Prompt-size tiles: the LoRA B operands of this (token tile, module) -- scale * u of the rows that use the adapter,
+      // zero rows for the others, swizzled K-major -- are built HERE, by the 128 threads of the output warps, while the
+      // tile's MMAs run: these warps have just finished the previous tile's epilogue, i.e. every MMA that read the old
+      // cache contents has retired (its accumulator was complete), and the token-tile producer keeps issuing copies
+      // instead of stopping for a chain of L2 round trips at every change of module.
+      if constexpr (BN >= 128 && LM == 2) {
+        if (p.lora_mode == 2 && sg.kb0 == 0) {  // (the CTA that holds a tile's first k-blocks runs its LoRA stages)
+          if (tok_tile != e_tok_tile) {
+            // the tile's adapters, listed by one warp; the output staging area serves as its scratch list
+            if (etid == 0) bulk_wait_read0();  // the last store has finished reading it
+            epi_bar_sync();                    // ... and nobody still reads the previous list
+            if (q == 0) {
+              int* scratch = reinterpret_cast<int*>(s_out);
+              const int ns = distinct_slots<BN>(a, t0, s_slots, scratch);
+              for (int i = lane; i < ns && i < 16; i += 32) {
+                e_list[i] = scratch[i];
+                e_scale[i] = a.scales[scratch[i]];
+              }
+              if (lane == 0) s_last = ns;
+            }
+            epi_bar_sync();
+            e_nseg = s_last;
+            e_tok_tile = tok_tile;
+            epi_bar_sync();  // s_last is reused by the split-tile hand-off
+          }
+          const int mod = module_of(a, row_tile * BM);
+          if (lora_cached<BN>(p, e_nseg) && tok_tile * 8 + mod != e_key) {
+            const int chunks = p.lora_sub / 8, per_row = chunks * p.n_sub, u_off = mod * a.r_max;
+            const int n_vec = e_nseg * p.n_sub * BN * (int)rb / 16;
+            for (int i = etid; i < n_vec; i += kEpiThreads) reinterpret_cast<uint4*>(s_cache)[i] = make_uint4(0u, 0u, 0u, 0u);
+            epi_bar_sync();
+            for (int base = etid; base < BN * per_row; base += kEpiThreads * 4) {
+              float4 lo[4], hi[4];
+              int nr[4], off[4];
+#pragma unroll
+              for (int b = 0; b < 4; ++b) {
+                const int idx = base + b * kEpiThreads;
+                nr[b] = -1;
+                if (idx < BN * per_row) {
+                  const int nrow = idx / per_row, rem = idx - nrow * per_row;
+                  const int sb = rem / chunks, c = rem - sb * chunks;
+                  if (s_slots[nrow] >= 0) {
+                    nr[b] = nrow;
+                    off[b] = sb * 256 + c;
+                    const float* ur = a.u + (size_t)(t0 + nrow) * r_tot + u_off + sb * p.lora_sub + c * 8;
+                    lo[b] = *reinterpret_cast<const float4*>(ur);
+                    hi[b] = *reinterpret_cast<const float4*>(ur + 4);
+                  }
+                }
+              }
+#pragma unroll
+              for (int b = 0; b < 4; ++b) {
+                if (nr[b] < 0) continue;
+                const int nrow = nr[b], sb = off[b] >> 8, c = off[b] & 255;
+                const int slot = s_slots[nrow];
+                int sgi = 0;
+                while (e_list[sgi] != slot) ++sgi;  // slot is in the list by construction
+                const float sc = e_scale[sgi];
+                const float f[8] = {lo[b].x * sc, lo[b].y * sc, lo[b].z * sc, lo[b].w * sc,
+                                    hi[b].x * sc, hi[b].y * sc, hi[b].z * sc, hi[b].w * sc};
+                const int sw = rb == 128 ? (nrow & 7) : rb == 64 ? ((nrow >> 1) & 3) : ((nrow >> 2) & 1);
+                *reinterpret_cast<uint4*>(s_cache + (sgi * p.n_sub + sb) * BN * rb + nrow * rb + ((c ^ sw) << 4)) = pack8(f);
+              }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            epi_bar_sync();
+            if (etid == 0) mbar_arrive(cache_full);
+            e_key = tok_tile * 8 + mod;
+          }
+        }
       }
 
       // NormFuse producer: this CTA will finish the tile (whole tile, or first contributor of a split one), so the
@@ -1113,7 +1202,7 @@ int sm_count() {
 }
 
 struct Plan {
-  int bn, row_tiles, tok_tiles, k_blocks, grid, per_cta, wave_gt, wave_full, wave_ch, wave_ch_last;
+  int bn, row_tiles, tok_tiles, k_blocks, grid, per_cta, wave_gt, wave_full, wave_ch, wave_ch_last, wave_lanes;
 };
 
 // min_waves: whole-tile mode needs at least this many tiles per CTA, so that the unfilled last wave costs little.
@@ -1125,13 +1214,42 @@ Plan plan_for(int bn, int min_waves, int T, int in, int out) {
   pl.k_blocks = (in + BK - 1) / BK;
   const long long total = (long long)pl.row_tiles * pl.tok_tiles * pl.k_blocks;
   long long grid = sm_count();
-  pl.wave_gt = pl.wave_full = pl.wave_ch = pl.wave_ch_last = 0;
+  pl.wave_gt = pl.wave_full = pl.wave_ch = pl.wave_ch_last = pl.wave_lanes = 0;
   const long long n_tiles = (long long)pl.row_tiles * pl.tok_tiles;
   if (pl.tok_tiles >= 4 && n_tiles >= min_waves * grid) {
-    // Waves of (token tiles x row tiles).  Token tiles per group: the group's token rows are what every CTA re-reads
-    // from L2 row tile after row tile, so they should stay resident next to the weight tiles in flight (<= 56 MB of the
-    // 126 MB), and row_tiles * group should fill whole rounds of the grid (the slots beyond it idle).  Among the sizes
-    // that fit, the one that wastes the fewest slots; the larger one on ties (fewer passes over the weights).
+    // Waves of (token tiles x row tiles).
+    static const int lane_form = [] {
+      const char* e = getenv("MLORA_WAVE_LANES");
+      return e ? atoi(e) : 1;
+    }();
+    if (lane_form) {
+      // Lane form.  Token tiles per group: the group's token rows are what the CTAs re-read from L2 row tile after row
+      // tile, so they should stay resident next to the weight tiles in flight (<= 48 MB of the 126 MB).  Among the
+      // sizes that fit, the one with the fewest steps (groups x row tiles per lane); fewer groups on ties (each group
+      // streams the weights once).
+      long long best = -1;
+      for (int d = 1; d <= 48 && d <= pl.tok_tiles && d <= (int)grid; ++d) {
+        if (d > 1 && (double)d * pl.bn * in * 2.0 > 48e6) break;
+        const int lanes = (int)grid / d;
+        const int steps = (pl.row_tiles + lanes - 1) / lanes;
+        const int groups = (pl.tok_tiles + d - 1) / d;
+        const long long cost = (long long)groups * steps;
+        if (best < 0 || cost <= best) {
+          best = cost;
+          pl.wave_gt = d;
+          pl.wave_lanes = lanes;
+          pl.wave_ch = steps;
+          pl.wave_full = groups;
+        }
+      }
+      pl.wave_ch_last = 0;
+      pl.per_cta = pl.wave_full * pl.wave_ch * pl.k_blocks;
+      pl.grid = (int)grid;
+      return pl;
+    }
+    // Chunk form: the tiles of a group, token tile major / row tile minor, cut into equal contiguous chunks.  Token tiles
+    // per group: the group's token rows should stay L2-resident (<= 56 MB), and row_tiles * group should fill whole
+    // rounds of the grid (the slots beyond it idle); among the sizes that fit, the one that wastes the fewest slots.
     int gt = 1;
     double best = 2.0;
     for (int d = 1; d <= 48 && d <= pl.tok_tiles; ++d) {
@@ -1227,6 +1345,7 @@ int launch(const LinearArgs& a, const Plan& pl, void* work, cudaStream_t st) {
   p.wave_full = pl.wave_full;
   p.wave_ch = pl.wave_ch;
   p.wave_ch_last = pl.wave_ch_last;
+  p.wave_lanes = pl.wave_lanes;
   p.per_cta = pl.per_cta;
   // output through TMA when the tensor satisfies its alignment rules (16-byte base and row pitch)
   CUtensorMap my = mx;
