@@ -160,6 +160,46 @@ def test_ragged_prompts_and_sequence_removal(synth, cuda):
     _check_logits(lg2, wl)
 
 
+def test_prompt_passes_with_128_wide_heads_take_the_tensor_core_attention(synth, cuda, monkeypatch):
+    """A small model with the benchmark's head geometry (4 x 128, page 16): ragged prompts cut into passes of 160 rows, so
+    that tiles end at pass boundaries and later passes continue sequences at positions > 0.  The engine's tiled
+    tensor-core prompt attention against the same engine with the single-query kernel, and against the oracle; then
+    decode steps on the cache the prompt passes filled."""
+    cfg = dict(synth.llama_config("tiny"), hidden_size=512, intermediate_size=1024, num_attention_heads=4,
+               num_key_value_heads=4, head_dim=128, vocab_size=2000)
+    w = {k: v.bfloat16() for k, v in synth.base_weights(cfg).items()}
+    ads = [{k: v.bfloat16() for k, v in a.items()} for a in synth.lora_adapters(cfg, 3, 8, targets=synth.ATTN_PROJ)]
+    scales = [2.0] * 3
+    lens = [300, 1, 129, 47, 128, 200]
+    rng = np.random.default_rng(5)
+    P = [rng.integers(0, cfg["vocab_size"], n).tolist() for n in lens]
+    ids = [0, 1, -1, 2, 0, 1]
+    sids = list(range(len(lens)))
+    oracle = ollama.OracleLlama(cfg, w, ads, scales)
+    want = torch.cat([oracle.prefill(s, P[s], ids[s]) for s in sids])
+    got = {}
+    for tc in ("1", "0"):
+        monkeypatch.setenv("MLORA_TC_PREFILL", tc)
+        pm, kv, eng = _engine(cfg, w, ads, scales, len(lens), 320, cuda, max_rows=160)
+        assert eng.tc_prefill == (tc == "1")
+        for s in sids:
+            kv.add_sequence(s)
+        lg, tok = eng.prefill(sids, P, ids)
+        _check_logits(lg, want)
+        got[tc] = (lg.float().cpu(), [kv.gather(s, 1) for s in sids], eng, tok)
+    # the two attention kernels sum in different orders and round P differently: close, not equal
+    torch.testing.assert_close(got["1"][0], got["0"][0], atol=ATOL, rtol=RTOL)
+    for (k1, v1), (k0, v0) in zip(got["1"][1], got["0"][1]):
+        torch.testing.assert_close(v1.float(), v0.float(), atol=3e-2, rtol=2e-2)  # layer-1 values: inputs within rounding
+        assert k1.shape == k0.shape
+    # decode on top of the tensor-core-filled cache
+    eng, tok = got["1"][2], got["1"][3]
+    t_in = [int(t) for t in tok]
+    wl = oracle.decode(sids, t_in, ids)
+    lg2, _ = eng.decode(sids, t_in, ids)
+    _check_logits(lg2, wl)
+
+
 def test_plumbing_config_at_its_full_size(synth, cuda):
     """The CPU-runnable configuration at its stated size: 4 requests x 512-token prompts (2048 rows in one
     prefill pass: grouped-GEMM shrink, 128-token tiles), 4 rank-8 adapters on q/k/v/o, ids [0,1,2,3], 32 greedy
