@@ -184,6 +184,48 @@ __device__ __forceinline__ bool lora_cached(const TcParams& p, int n_seg) {
   return n_seg * p.n_sub * BN * p.lora_sub * 2 <= Cfg<BN>::kCacheBytes;
 }
 
+// Prompt-size tiles: are the rows of every adapter of the tile one contiguous run (prompt rows of a request are)?  Then an
+// adapter's LoRA stage only needs the 16-row blocks its rows touch: its B operand has `rows` = the run rounded out to 16
+// rows, and its MMAs write the accumulator columns [first, first + rows) with N = rows.  All operands of a tile then take
+// BN + 16 rows per adapter at most, whatever the number of adapters.  Returns the total number of operand rows, or -1 when
+// some adapter's rows are scattered (or there are more than 16 adapters).  One full warp; s_tok / s_list as written by
+// distinct_slots; tab (optional, [16]): per adapter (first accumulator column, rows, row offset of its operand).
+template <int BN>
+__device__ __forceinline__ int adapter_runs(const int* s_tok, const int* s_list, int n_seg, int4* tab) {
+  if (BN < 128 || n_seg > 16) return -1;
+  const int lane = threadIdx.x & 31;
+  int total = 0;
+  bool ok = true;
+  for (int j = 0; j < n_seg; ++j) {
+    const int s = s_list[j];
+    int lo = BN, hi = -1, cnt = 0;
+    for (int r = lane; r < BN; r += 32)
+      if (s_tok[r] == s) {
+        lo = min(lo, r);
+        hi = max(hi, r);
+        ++cnt;
+      }
+    lo = __reduce_min_sync(0xffffffffu, lo);
+    hi = __reduce_max_sync(0xffffffffu, hi);
+    cnt = __reduce_add_sync(0xffffffffu, cnt);
+    ok = ok && cnt == hi - lo + 1;
+    const int first = lo & ~15, rows = ((hi + 16) & ~15) - first;
+    if (tab != nullptr && lane == 0) tab[j] = make_int4(first, rows, total, 0);
+    total += rows;
+  }
+  return ok ? total : -1;
+}
+// Operands of a tile in the shared-memory cache: in the run layout when the rows allow it and it fits, else as full-height
+// masked operands per adapter when those fit.
+template <int BN>
+__device__ __forceinline__ bool lora_runs(const TcParams& p, int n_run) {
+  return BN >= 128 && n_run >= 0 && n_run * p.n_sub * p.lora_sub * 2 <= Cfg<BN>::kCacheBytes;
+}
+template <int BN>
+__device__ __forceinline__ bool lora_in_cache(const TcParams& p, int n_seg, int n_run) {
+  return lora_runs<BN>(p, n_run) || lora_cached<BN>(p, n_seg);
+}
+
 // One CTA's share of the iteration space and the walk over its segments.
 struct Range {
   int it0, it1;
@@ -300,11 +342,14 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
   // cache holds at most 16 of them)
   int* e_list = reinterpret_cast<int*>(aux + 512);                      // [16]  (decode-size tiles use this space as s_red)
   float* e_scale = reinterpret_cast<float*>(aux + 512 + 64);            // [16]
+  int4* e_tab = reinterpret_cast<int4*>(aux + 512 + 128);               // [16] run layout: (first column, rows, operand row offset)
+  int* e_nrun = reinterpret_cast<int*>(aux + 512 + 128 + 256);
   // (kAuxBytes also counts the operand cache and the output staging, which lie BEFORE aux: address from aux's own parts)
   float* s_rstd = reinterpret_cast<float*>(aux + 1024 + 8 * BN * 4 + C::kStageU);  // [32] 1/rms of the input rows (NormFuse consumer)
   __shared__ int s_abort;
   __shared__ int s_last;
   __shared__ int s_nseg0;  // distinct adapters of the CTA's first token tile (listed before the roles start)
+  __shared__ int s_runs0;  // ... and their operand rows in the run layout (adapter_runs)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   constexpr bool WAVE = BN >= 128;  // prefill-size token tiles only
@@ -355,6 +400,8 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
     // global load.  The roles pick the result up through `preload_bar` when they first need it.
     if (warp == 2) {
       const int ns = distinct_slots<BN>(a, tok_tile0 * BN, p_tok, p_list);
+      const int nr = adapter_runs<BN>(p_tok, p_list, ns, nullptr);
+      if (lane == 0) s_runs0 = nr;
       for (int i = lane; i < BN; i += 32) {
         m_tok[i] = x_tok[i] = p_tok[i];
         if (i < ns) {
@@ -387,7 +434,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
     // ---- weight producer: lane 0 issues the copies; all lanes list the adapters of a token tile ------
     const bool packed = (a.flags & MLORA_W_PACKED) != 0;
     const uint8_t* wp = reinterpret_cast<const uint8_t*>(a.W);
-    int it = rg.it0, n = 0, cur_tok_tile = tok_tile0, n_seg = 0;
+    int it = rg.it0, n = 0, cur_tok_tile = tok_tile0, n_seg = 0, n_run = -1;
     bool got_preload = false;
     bool ok = true;
     // decode sizes read every weight byte once: "evict first", so that the stream does not push token tiles, partial
@@ -424,6 +471,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
         if (!got_preload) {  // operands of the first token tile, staged by the epilogue warps at start-up
           mbar_wait(preload_bar, 0, &s_abort);
           n_seg = s_nseg0;
+          n_run = s_runs0;
           got_preload = true;
         }
         // The tile's first k-blocks are ours: this CTA also runs the tile's LoRA stages, after them.  (For a split
@@ -434,10 +482,11 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
         // When the B operands are cached in shared memory, up to `group` such slices share one ring slot.
         if (tok_tile != cur_tok_tile) {
           n_seg = distinct_slots<BN>(a, tok_tile * BN, p_tok, p_list);
+          n_run = adapter_runs<BN>(p_tok, p_list, n_seg, nullptr);
           cur_tok_tile = tok_tile;
         }
         const int n_l = n_seg * p.n_sub;
-        const int group = lora_cached<BN>(p, n_seg) ? C::kWBytes / (BM * (int)rb) : 1;
+        const int group = lora_in_cache<BN>(p, n_seg, n_run) ? C::kWBytes / (BM * (int)rb) : 1;
         const int n_groups = (n_l + group - 1) / group;
         if (lane == 0) {
           int nn = n;
@@ -470,7 +519,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
   } else if (warp == 6) {
     // ---- token-tile producer: lane 0 issues the x copies; all lanes build the LoRA B operands --------
     const bool stage_u = stage_u2;
-    int it = rg.it0, n = 0, cur_tok_tile = tok_tile0, n_seg = 0, cur_key = -1, n_build = 0;
+    int it = rg.it0, n = 0, cur_tok_tile = tok_tile0, n_seg = 0, n_run = -1, cur_key = -1, n_build = 0;
     bool got_preload = false;
     bool ok = true;
     while (it < rg.it1 && ok) {
@@ -497,6 +546,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
         if (!got_preload) {  // operands of the first token tile, staged by the epilogue warps at start-up
           mbar_wait(preload_bar, 0, &s_abort);
           n_seg = s_nseg0;
+          n_run = s_runs0;
           got_preload = true;
         }
         // B operand of a LoRA stage = scale * u of the tokens that use the adapter (zero rows for the
@@ -505,6 +555,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
         const int t0 = tok_tile * BN;
         if (tok_tile != cur_tok_tile) {
           n_seg = distinct_slots<BN>(a, t0, x_tok, x_list);
+          n_run = adapter_runs<BN>(x_tok, x_list, n_seg, nullptr);
           for (int i = lane; i < n_seg; i += 32) x_scale[i] = a.scales[x_list[i]];
           if (stage_u) {
             const int n_valid = min(BN, a.T - t0) * r_tot;
@@ -516,7 +567,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
         const int mod = module_of(a, row_tile * BM);
         const int u_off = mod * a.r_max;
         const int chunks = p.lora_sub / 8;  // 16-byte chunks per row
-        const bool cached = lora_cached<BN>(p, n_seg);
+        const bool cached = lora_in_cache<BN>(p, n_seg, n_run);
         if (BN >= 128 && cached) continue;  // prompt-size tiles: the output warps build the cache (below)
         if (cached && tok_tile * 8 + mod == cur_key) continue;  // operands already in the cache
         if (cached) {
@@ -675,7 +726,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
   } else if (warp == 1) {
     // ---- MMA issuer: lane 0 issues; all lanes count the LoRA stages of a token tile ---------------------
     constexpr uint32_t idesc = make_idesc(BM, BN);
-    int it = rg.it0, nw = 0, nx = 0, j = 0, cur_tok_tile = tok_tile0, n_seg = 0, cur_key = -1, n_build = 0;
+    int it = rg.it0, nw = 0, nx = 0, j = 0, cur_tok_tile = tok_tile0, n_seg = 0, n_run = -1, cur_key = -1, n_build = 0;
     bool got_preload = false;
     bool ok = true;
     while (it < rg.it1 && ok) {
@@ -690,14 +741,16 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
         if (!got_preload) {  // operands of the first token tile, staged by the epilogue warps at start-up
           mbar_wait(preload_bar, 0, &s_abort);
           n_seg = s_nseg0;
+          n_run = s_runs0;
           got_preload = true;
         }
         if (tok_tile != cur_tok_tile) {
           n_seg = distinct_slots<BN>(a, tok_tile * BN, m_tok, m_list);
+          n_run = adapter_runs<BN>(m_tok, m_list, n_seg, nullptr);
           cur_tok_tile = tok_tile;
         }
         n_l = n_seg * p.n_sub;
-        cached = lora_cached<BN>(p, n_seg);
+        cached = lora_in_cache<BN>(p, n_seg, n_run);
         if (cached) {
           group = C::kWBytes / (BM * (int)rb);
           const int key = tok_tile * 8 + module_of(a, row_tile * BM);
@@ -780,6 +833,15 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
           const int l0 = g * group, l1 = min(n_l, l0 + group);
           for (int l = l0; l < l1; ++l) {
             const uint64_t adesc = make_smem_desc(smem_u32(w_ring + s * C::kWBytes + (l - l0) * BM * rb), rb);
+            if (cached && lora_runs<BN>(p, n_run)) {
+              // run layout (written, with its table, by the output warps): only the adapter's own 16-row blocks
+              const int sgi = l / p.n_sub, sb = l - sgi * p.n_sub;
+              const int4 tb = e_tab[sgi];
+              const uint64_t bdesc = make_smem_desc(smem_u32(s_cache + (size_t)(tb.z * p.n_sub + sb * tb.y) * rb), rb);
+              const uint32_t idesc_run = make_idesc(BM, tb.y);
+              for (int k = 0; k < p.lora_sub / 16; ++k) umma_bf16(d_tmem + tb.x, adesc + 2 * k, bdesc + 2 * k, idesc_run, 1u);
+              continue;
+            }
             const uint64_t bdesc = make_smem_desc(
                 cached ? smem_u32(s_cache + l * BN * rb) : smem_u32(x_ring + xs * C::kXBytes), rb);
             for (int k = 0; k < p.lora_sub / 16; ++k) umma_bf16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, 1u);
@@ -808,7 +870,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
     const bool stage_u = simt_lora && (size_t)BN * r_tot * sizeof(float) <= (size_t)C::kStageU;
     int staged_tok_tile = -1;
     int it = rg.it0, j = 0;
-    int e_tok_tile = -1, e_nseg = 0, e_key = -1;  // prompt-size tiles: the output warps' view of the LoRA operand cache
+    int e_tok_tile = -1, e_nseg = 0, e_run = -1, e_key = -1;  // prompt-size tiles: the output warps' view of the LoRA operand cache
     const NormFuse& nf = a.nf;
     if constexpr (BN <= 32) {
       if (nf.sumsq_in != nullptr) {  // (uniform) 1/rms of the input rows from the producer's per-tile sums of squares
@@ -857,21 +919,27 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
             if (q == 0) {
               int* scratch = reinterpret_cast<int*>(s_out);
               const int ns = distinct_slots<BN>(a, t0, s_slots, scratch);
+              const int nr = adapter_runs<BN>(s_slots, scratch, ns, e_tab);
               for (int i = lane; i < ns && i < 16; i += 32) {
                 e_list[i] = scratch[i];
                 e_scale[i] = a.scales[scratch[i]];
               }
-              if (lane == 0) s_last = ns;
+              if (lane == 0) {
+                s_last = ns;
+                *e_nrun = nr;
+              }
             }
             epi_bar_sync();
             e_nseg = s_last;
+            e_run = *e_nrun;
             e_tok_tile = tok_tile;
             epi_bar_sync();  // s_last is reused by the split-tile hand-off
           }
           const int mod = module_of(a, row_tile * BM);
-          if (lora_cached<BN>(p, e_nseg) && tok_tile * 8 + mod != e_key) {
+          if (lora_in_cache<BN>(p, e_nseg, e_run) && tok_tile * 8 + mod != e_key) {
+            const bool runs = lora_runs<BN>(p, e_run);
             const int chunks = p.lora_sub / 8, per_row = chunks * p.n_sub, u_off = mod * a.r_max;
-            const int n_vec = e_nseg * p.n_sub * BN * (int)rb / 16;
+            const int n_vec = (runs ? e_run : e_nseg * BN) * p.n_sub * (int)rb / 16;
             for (int i = etid; i < n_vec; i += kEpiThreads) reinterpret_cast<uint4*>(s_cache)[i] = make_uint4(0u, 0u, 0u, 0u);
             epi_bar_sync();
             for (int base = etid; base < BN * per_row; base += kEpiThreads * 4) {
@@ -904,7 +972,12 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
                 const float f[8] = {lo[b].x * sc, lo[b].y * sc, lo[b].z * sc, lo[b].w * sc,
                                     hi[b].x * sc, hi[b].y * sc, hi[b].z * sc, hi[b].w * sc};
                 const int sw = rb == 128 ? (nrow & 7) : rb == 64 ? ((nrow >> 1) & 3) : ((nrow >> 2) & 1);
-                *reinterpret_cast<uint4*>(s_cache + (sgi * p.n_sub + sb) * BN * rb + nrow * rb + ((c ^ sw) << 4)) = pack8(f);
+                if (runs) {  // the adapter's own blocks only (block starts are multiples of 16 rows: same swizzle phase)
+                  const int4 tb = e_tab[sgi];
+                  *reinterpret_cast<uint4*>(s_cache + (size_t)(tb.z * p.n_sub + sb * tb.y + (nrow - tb.x)) * rb + ((c ^ sw) << 4)) = pack8(f);
+                } else {
+                  *reinterpret_cast<uint4*>(s_cache + (sgi * p.n_sub + sb) * BN * rb + nrow * rb + ((c ^ sw) << 4)) = pack8(f);
+                }
               }
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
