@@ -976,6 +976,42 @@ def run_kernel_case(which):
                           "peak_tflops": tpk, "frac_base": fl / res["base"] / 1e9 / tpk,
                           "status": ops.status_word(ops.workspace(4, dev, "linear")), "launches": ops.launch_count()})
         return
+    elif which == "prefill-lora":
+        # what the LoRA expand adds to a prompt-size projection, by shape of the batch: the q/k/v projection of 8192 rows
+        # with no adapter, one adapter per 256-token tile, four per tile; rank-16 and rank-64 stacks; CUDA events
+        T, NA = 8192, 16
+        x = (torch.randn(T, 4096, device=dev) * 0.5).to(torch.bfloat16)
+        W = ops.PackedWeight((torch.randn(12288, 4096, device=dev) * 0.02).to(torch.bfloat16))
+        out = torch.empty(T, 12288, dtype=torch.bfloat16, device=dev)
+
+        def timed(fn):
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+            for i in range(6):
+                if i == 2:
+                    ev[0].record()
+                fn()
+            ev[1].record()
+            torch.cuda.synchronize()
+            return ev[0].elapsed_time(ev[1]) / 4 * 1e3
+
+        rows = {"base_us": timed(lambda: ops.linear(x, W, out=out))}
+        for R in (16, 64):
+            A = (torch.randn(NA, 3 * R, 4096, device=dev) * 0.02).to(torch.bfloat16)
+            B = (torch.randn(NA, 12288, R, device=dev) * 0.02).to(torch.bfloat16)
+            st = ops.LoraStack(A, B, torch.full((NA,), R, dtype=torch.int32, device=dev), torch.full((NA,), 2.0, device=dev),
+                               R, 3, (0, 4096, 8192, 12288)).pack_b()
+            u = torch.zeros(T, 3 * R, dtype=torch.float32, device=dev)
+            ar = torch.arange(T, device=dev, dtype=torch.int32)
+            cases = {"no_adapter": torch.full((T,), -1, dtype=torch.int32, device=dev), "one_per_tile": ar // 512 % NA,
+                     "four_per_tile": ar // 64 % NA}
+            for name, slots in cases.items():
+                rows[f"rank{R}_expand_{name}_us"] = timed(lambda: ops.linear(x, W, st, slots, u=u, out=out))
+            slots = cases["one_per_tile"]
+            rows[f"rank{R}_shrink_us"] = timed(lambda: ops.lora_shrink(x, st, slots, out=u))
+            rows[f"rank{R}_shrink_plus_expand_us"] = timed(lambda: (ops.lora_shrink(x, st, slots, out=u),
+                                                                     ops.linear(x, W, st, slots, u=u, out=out)))
+        emit(dict(rows, kernel_case=which, T=T, status=ops.status_word(ops.workspace(4, dev, "linear")), launches=ops.launch_count()))
+        return
     elif which == "prefill-attn":
         # one layer's prompt attention: 16 requests x 512 rows, 32 x 128 heads, keys / values appended first
         Hq = Hkv = 32
@@ -1058,7 +1094,7 @@ def main():
     ap.add_argument("--skip-prefill", action="store_true",
                     help="profiling aid: fill the KV cache with seeded random values instead of running prefill "
                          "(the number is then not a bench value)")
-    ap.add_argument("--kernel-case", default="", choices=["", "linear", "attention", "operator", "prefill", "prefill-attn", "expand", "chain"],
+    ap.add_argument("--kernel-case", default="", choices=["", "linear", "attention", "operator", "prefill", "prefill-lora", "prefill-attn", "expand", "chain"],
                     help="profiling aid: launch one kernel a few times on a small case (> L2, < 1 GB) and exit")
     ap.add_argument("--workload", default="", choices=["", "13b-shape", "13b-tp", "prefill-heavy"],
                     help="side measurements (own JSON line, not the benchmark's): 13b-shape = the 13B shape and adapter "
