@@ -39,8 +39,11 @@ extern "C" {
 #define MLORA_LORA_PER_ROW 64 /* the batch has many distinct adapters per token tile (e.g. every request its own):
                                run the base projection, then add the expand with a kernel laid out by (row, output
                                feature) that streams each row's B_all[slot] up to the adapter's own rank, instead of
-                               one masked tensor-core stage per distinct adapter.  Not with MLORA_SILU_MUL (ignored
-                               there).  bf16 outputs are rounded twice (projection, then sum) */
+                               one masked tensor-core stage per distinct adapter.  bf16 outputs are rounded twice
+                               (projection, then sum).  With MLORA_SILU_MUL the projection leaves fp32 pre-activations
+                               of the gate / up rows in the tail of d_work, and the expand kernel adds the adapters and
+                               applies silu(gate)*up: d_work must then hold mlora_linear_workspace_flags(T, in, out,
+                               flags) bytes (the flag is ignored, i.e. the tensor-core stages run, when it holds less) */
 #define MLORA_B_SPLIT 128   /* with MLORA_LORA_PER_ROW: d_B_all is the rank-compact "split" layout -- every adapter stored
                                as rank/8 slices [out, 8] bf16 laid one after the other (the split-to-the-minimum-rank
                                strategy of tvm/lora_only/case_study/multiple_ranks.py:98-151 as a data layout: slices of
@@ -133,6 +136,8 @@ int mlora_lora_shrink(const void* d_x, int64_t ldx, const void* d_A_all, const i
  *   tile may still bump its arrival counter afterwards, the whole buffer must be zero-filled again
  *   before its next use (the word is sticky: the caller clears it). */
 size_t mlora_linear_workspace(int32_t T, int32_t in, int32_t out);
+/* The same for a call with these flags: more than mlora_linear_workspace only for MLORA_SILU_MUL | MLORA_LORA_PER_ROW. */
+size_t mlora_linear_workspace_flags(int32_t T, int32_t in, int32_t out, int32_t flags);
 /* Weight pre-packing (load time).  Rewrites W [out,in] bf16 as tiles [ceil(out/128)][ceil(in/64)] of
  * 128 rows x 64 columns, each tile 16 KB contiguous and already in the 128-byte-swizzled K-major
  * layout the tensor cores read from shared memory (zero padded), so that the projection kernel

@@ -25,17 +25,23 @@ __global__ void __launch_bounds__(kExpThreads) lora_expand_rows_kernel(LinearArg
   const int t = blockIdx.y;
   const int o = blockIdx.x * kExpThreads + threadIdx.x;
   const int slot = a.slots[t];
-  if (slot < 0 || slot >= a.n_adapters) return;  // uniform over the CTA
+  // MLORA_SILU_MUL (interleaved gate/up rows): the projection left its pre-activations in a.y_in (fp32 [T, out]); every
+  // row, with or without adapter, gets its expand added there and leaves as silu(gate) * up in y [T, out / 2].
+  const bool silu = (a.flags & MLORA_SILU_MUL) != 0;
+  const bool has = slot >= 0 && slot < a.n_adapters;
+  if (!has && !silu) return;  // uniform over the CTA
   const int r_tot = a.r_max * a.n_mod;
-  for (int i = threadIdx.x; i < r_tot; i += kExpThreads) su[i] = a.u[(size_t)t * r_tot + i];
+  if (has) {
+    for (int i = threadIdx.x; i < r_tot; i += kExpThreads) su[i] = a.u[(size_t)t * r_tot + i];
+  }
   __syncthreads();
-  if (o >= a.out) return;
+  if (o >= a.out) return;  // (SiLU: out is a multiple of 16, so both lanes of a gate/up pair stay or leave)
   // the output element is requested now, with the B row: one round trip for both
   const bool f32 = (a.flags & MLORA_OUT_F32) != 0;
   float* y32 = reinterpret_cast<float*>(a.y) + (size_t)t * a.ldy + o;
   bf16* y16 = reinterpret_cast<bf16*>(a.y) + (size_t)t * a.ldy + o;
-  const float y_old = f32 ? *y32 : __bfloat162float(*y16);
-  int rank = a.full_rank ? a.r_max : a.ranks[slot];
+  const float y_old = silu ? a.y_in[(size_t)t * a.out + o] : f32 ? *y32 : __bfloat162float(*y16);
+  int rank = !has ? 0 : a.full_rank ? a.r_max : a.ranks[slot];
   rank = rank < a.r_max ? rank : a.r_max;
   const float* um = su + module_of(a, o) * a.r_max;
   const int n_chunks = (rank + 7) / 8;
@@ -99,7 +105,14 @@ __global__ void __launch_bounds__(kExpThreads) lora_expand_rows_kernel(LinearArg
       }
     }
   }
-  const float y_new = fmaf(acc, a.scales[slot], y_old);
+  const float y_new = has ? fmaf(acc, a.scales[slot], y_old) : y_old;
+  if (silu) {
+    // rows 16j..16j+7 are gate, 16j+8..16j+15 the matching up rows: lane pairs 8 apart
+    const float other = __shfl_xor_sync(__activemask(), y_new, 8);
+    if ((o & 8) == 0)
+      reinterpret_cast<bf16*>(a.y)[(size_t)t * a.ldy + (o >> 4) * 8 + (o & 7)] = __float2bfloat16_rn(silu_mul(y_new, other));
+    return;
+  }
   if (f32)
     *y32 = y_new;
   else
@@ -111,6 +124,12 @@ __global__ void __launch_bounds__(kExpThreads) lora_expand_rows_kernel(LinearArg
 bool lora_expand_rows_supported(const LinearArgs& a) {
   if ((a.flags & MLORA_B_SPLIT) && ((a.flags & MLORA_B_PACKED) || a.full_rank)) return false;
   return a.u != nullptr && !(a.flags & MLORA_SILU_MUL) && a.r_max % 8 == 0 && a.r_max * a.n_mod <= kExpMaxRtot &&
+         (!(a.flags & MLORA_B_PACKED) || a.r_max == 16 || a.r_max == 32 || a.r_max == 64 || a.r_max == 128) && a.T <= 65535;
+}
+
+bool lora_expand_silu_supported(const LinearArgs& a) {
+  return a.u != nullptr && (a.flags & MLORA_SILU_MUL) && !(a.flags & (MLORA_B_SPLIT | MLORA_OUT_F32)) && a.out % 16 == 0 &&
+         a.r_max % 8 == 0 && a.r_max * a.n_mod <= kExpMaxRtot &&
          (!(a.flags & MLORA_B_PACKED) || a.r_max == 16 || a.r_max == 32 || a.r_max == 64 || a.r_max == 128) && a.T <= 65535;
 }
 

@@ -7,6 +7,14 @@ extern "C" size_t mlora_linear_workspace(int32_t T, int32_t in, int32_t out) {
   return linear_tc_workspace(T, in, out);
 }
 
+static size_t pre_offset(int32_t T, int32_t in, int32_t out) { return (linear_tc_workspace(T, in, out) + 255) & ~(size_t)255; }
+
+extern "C" size_t mlora_linear_workspace_flags(int32_t T, int32_t in, int32_t out, int32_t flags) {
+  if ((flags & MLORA_SILU_MUL) && (flags & MLORA_LORA_PER_ROW) && T > 0 && out > 0)
+    return pre_offset(T, in, out) + (size_t)T * out * sizeof(float);  // + the fp32 pre-activations of the gate/up rows
+  return linear_tc_workspace(T, in, out);
+}
+
 // d_A_all != NULL: the shrink is part of this call (its kernel is launched first).
 static int linear_impl(const void* d_x, int64_t ldx, const void* d_W, void* d_y, int64_t ldy, int32_t T, int32_t in,
                        int32_t out, const void* d_A_all, const float* d_u, const void* d_B_all,
@@ -85,6 +93,29 @@ static int linear_impl(const void* d_x, int64_t ldx, const void* d_W, void* d_y,
     const int rc = mlora_lora_shrink(d_x, ldx, d_A_all, d_ranks, d_slots, n_adapters, T, in, r_max, n_mod,
                                      const_cast<float*>(d_u), stream);
     if (rc != MLORA_OK) return rc;
+  }
+  if ((flags & MLORA_LORA_PER_ROW) && (flags & MLORA_SILU_MUL) && d_u && lora_expand_silu_supported(a) &&
+      work_bytes >= mlora_linear_workspace_flags(T, in, out, flags) && d_work) {
+    // many distinct adapters in front of SiLU*up: the projection writes fp32 pre-activations of the interleaved gate / up
+    // rows into the tail of the scratch buffer, the per-row expand adds each row's adapter there and applies the activation
+    LinearArgs b = a;
+    b.u = nullptr;
+    b.B_all = nullptr;
+    b.flags = (b.flags & ~(MLORA_SILU_MUL | MLORA_B_PACKED | MLORA_LORA_PER_ROW)) | MLORA_OUT_F32;
+    float* pre = reinterpret_cast<float*>(static_cast<uint8_t*>(d_work) + pre_offset(T, in, out));
+    b.y = pre;
+    b.ldy = out;
+    int rc;
+    if (!(flags & MLORA_FORCE_SIMT) && linear_tc_supported(b)) {
+      rc = launch_linear_tc(b, d_work, work_bytes, st);
+    } else {
+      MLORA_REQUIRE(!(flags & MLORA_W_PACKED), "linear: a packed weight needs the tensor-core kernel");
+      rc = launch_linear_simt(b, st);
+    }
+    if (rc != MLORA_OK) return rc;
+    LinearArgs e = a;
+    e.y_in = pre;
+    return launch_lora_expand_rows(e, st);
   }
   if ((flags & MLORA_LORA_PER_ROW) && d_u && lora_expand_rows_supported(a)) {
     // many distinct adapters per token tile: base projection first, then the expand laid out by (row, output feature)

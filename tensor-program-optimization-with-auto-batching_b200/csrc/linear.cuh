@@ -37,6 +37,7 @@ struct LinearArgs {
   int flags;
   int n_adapters;        // slots >= n_adapters are treated as "no adapter"
   int full_rank;         // 1: every row uses all r_max entries (zero-padded), ranks[] is ignored
+  const float* y_in;     // per-row expand with MLORA_SILU_MUL: the projection's pre-activations, fp32 [T, out]
   NormFuse nf;           // all zero: plain projection
 };
 
@@ -90,6 +91,7 @@ size_t linear_tc_workspace(int T, int in, int out);
 int launch_linear_tc(const LinearArgs& a, void* work, size_t work_bytes, cudaStream_t st);
 // LoRA expand laid out by (row, output feature), added to y in place (batches with many distinct adapters).
 bool lora_expand_rows_supported(const LinearArgs& a);
+bool lora_expand_silu_supported(const LinearArgs& a);  // the same expand in front of the SiLU*up of interleaved gate/up rows
 int launch_lora_expand_rows(const LinearArgs& a, cudaStream_t st);
 // LoRA shrink as a segmented grouped GEMM on the tensor cores (prefill sizes).
 bool lora_shrink_tc_supported(const void* x, int64_t ldx, const void* A_all, const float* u, int T, int in, int r_tot);

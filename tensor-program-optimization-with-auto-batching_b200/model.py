@@ -296,6 +296,8 @@ class Engine:
         lib = ops._lib.lib()
         need = max(lib.mlora_linear_workspace(T, k, n) for k, n in
                    ((m.H, qkv_out), (m.Hq * m.D, m.H), (m.H, 2 * m.I), (m.I, m.H), (m.H, m.V)))
+        # (+ the pre-activations of a gate|up call that takes the per-row expand: decode passes of up to 128 rows)
+        need = max(need, lib.mlora_linear_workspace_flags(min(T, 128), m.H, 2 * m.I, SILU_MUL | LORA_PER_ROW))
         # The engine owns its scratch: captured graphs hold these addresses, so the buffers live as long as the
         # engine and are never shared with (or outgrown by) other callers on the device.
         self.ws_linear = ops.new_workspace(need, dev)
@@ -351,10 +353,11 @@ class Engine:
         """The tensor-core expand holds the operands of a token tile's distinct adapters in a shared-memory cache
         (16 KB, 64 KB at 128-token tiles); a decode batch that brings more distinct adapters than fit (e.g. every
         request its own) takes the expand laid out by (row, output feature) instead."""
-        if flags & SILU_MUL or T > 128:
+        if T > 128:
             return flags
         bn = 16 if T <= 16 else 32 if T <= 32 else 64 if T <= 64 else 128
-        cap = ((64 if bn == 128 else 16) * 1024) // (bn * stack.r_max * 2)
+        pitch = stack.r_max * (2 if flags & SILU_MUL else 1)  # interleaved gate/up: one operand of both modules' ranks
+        cap = ((64 if bn == 128 else 16) * 1024) // (bn * pitch * 2)
         return flags | LORA_PER_ROW if self.n_distinct > max(cap, 1) else flags
 
     def _reduce_norm(self, delta, res, w, out, reduce=True):

@@ -236,7 +236,7 @@ def linear(x, W, stack: LoraStack = None, slots=None, u=None, flags: int = 0, ou
             u = lora_shrink(x, stack, slots)
     if stack is not None and stack.n_mod > 1 and not flags & SILU_MUL:
         mod = (C.c_int32 * (stack.n_mod + 1))(*stack.mod_offsets)
-    wb = _lib.lib().mlora_linear_workspace(T, K, N) if use_workspace else 0
+    wb = _lib.lib().mlora_linear_workspace_flags(T, K, N, flags if stack is not None else 0) if use_workspace else 0
     if work is not None and wb:
         if work.numel() < wb:
             raise ValueError(f"mlora.linear: scratch of {wb} bytes needed, {work.numel()} given")

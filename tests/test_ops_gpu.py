@@ -223,9 +223,21 @@ def test_gate_up_silu_with_lora(ops, cuda, T, r):
             gate[t] += 2.0 * (Bg[s].float() @ (Ag[s].float() @ x[t].float()))
             up[t] += 2.0 * (Bu[s].float() @ (Au[s].float() @ x[t].float()))
     want = oops.silu_mul(gate, up)
-    for flags in (ops.SILU_MUL, ops.SILU_MUL | ops.FORCE_SIMT):
+    # ... and the same with the expand laid out by (row, output feature) in front of the activation: what a batch with
+    # many distinct adapters takes (fp32 pre-activations in the scratch buffer's tail, activation in the expand kernel)
+    for flags in (ops.SILU_MUL, ops.SILU_MUL | ops.FORCE_SIMT, ops.SILU_MUL | ops.LORA_PER_ROW,
+                  ops.SILU_MUL | ops.LORA_PER_ROW | ops.FORCE_SIMT):
         y = ops.linear(x.to(cuda), Wi.to(cuda), st, slots.to(cuda), flags=flags).float().cpu()
         torch.testing.assert_close(y, want, atol=ATOL, rtol=RTOL)
+    launches = ops.launch_count()
+    stp = ops.LoraStack(torch.cat([Ag, Au], 1).to(cuda), B_all.to(cuda).clone(), _i32([r] * n_ad, cuda),
+                        torch.full((n_ad,), 2.0, device=cuda), r, 2, None).pack_b()
+    y = ops.linear(x.to(cuda), ops.PackedWeight(Wi.to(cuda)), stp, slots.to(cuda),
+                   flags=ops.SILU_MUL | ops.LORA_PER_ROW).float().cpu()
+    torch.testing.assert_close(y, want, atol=ATOL, rtol=RTOL)
+    assert ops.launch_count() - launches >= 3  # shrink, projection, expand: the per-row form really ran
+    torch.cuda.synchronize()
+    assert int(ops.workspace(4, cuda, "linear")[:4].view(torch.int32)) == 0
 
 
 @pytest.mark.parametrize("T,K,I", [(3, 256, 688), (32, 512, 1024)])
