@@ -305,7 +305,9 @@ __device__ __forceinline__ Segment next_segment(const TcParams& p, int& it, int 
 // instantiations because the decode-size kernels are sensitive to code size: every launch starts with cold
 // instruction caches after 100+ MB of weights went through L2, so a step whose projections alternate between two
 // instantiations pays for two code footprints; one that uses a single instantiation throughout does not.
-template <int BN, int LM>
+// NF: the folded residual + RMSNorm epilogues (NormFuse) are compiled in.  Its own instantiation: the extra code and
+// registers (233 against 164 per thread at 32-token tiles) cost every launch of the kernel ~0.3 us even when unused.
+template <int BN, int LM, bool NF = false>
 __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                 const __grid_constant__ CUtensorMap map_x,
                                                                 const __grid_constant__ CUtensorMap map_b,
@@ -872,7 +874,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
     int it = rg.it0, j = 0;
     int e_tok_tile = -1, e_nseg = 0, e_run = -1, e_key = -1;  // prompt-size tiles: the output warps' view of the LoRA operand cache
     const NormFuse& nf = a.nf;
-    if constexpr (BN <= 32) {
+    if constexpr (BN <= 32 && NF) {
       if (nf.sumsq_in != nullptr) {  // (uniform) 1/rms of the input rows from the producer's per-tile sums of squares
         if (etid < 32) {
           float s = 0.f;
@@ -993,7 +995,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
       float rs[32];
       float nw = 0.f;
       bool do_res = false;
-      if constexpr (BN <= 32) {
+      if constexpr (BN <= 32 && NF) {
         do_res = nf.res != nullptr && (full_seg || (int)blockIdx.x == (int)(((long long)sg.tile * p.k_blocks) / p.per_cta));
         if (do_res) {
 #pragma unroll
@@ -1006,7 +1008,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_tc_kernel(const __grid_con
       // Adds the CUDA-core LoRA expand if any, applies SiLU*up, stores.  v[i] = (token t0+c0+i, row).
       auto finish = [&](float (&v)[32], int c0) {
         if (LM == 1) simt_lora_expand<BN>(a, v, c0, t0, row, r_tot, stage_u, s_slots, s_u);
-        if constexpr (BN <= 32) {
+        if constexpr (BN <= 32 && NF) {
           if (nf.sumsq_in != nullptr) {
 #pragma unroll
             for (int i = 0; i < C::kChunk; ++i) v[i] *= s_rstd[c0 + i];
@@ -1447,6 +1449,26 @@ int launch(const LinearArgs& a, const Plan& pl, void* work, cudaStream_t st) {
       e = cudaFuncSetAttribute(linear_tc_kernel<BN, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
     if (e != cudaSuccess) return fail(MLORA_ECUDA, "linear: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     attr_done.fetch_or(1ull << (dev & 63), std::memory_order_release);
+  }
+  if constexpr (BN <= 32) {
+    if (a.nf.res != nullptr || a.nf.sumsq_in != nullptr) {
+      if (p.lora_mode == 1) return fail(MLORA_EINVAL, "linear_norm: the LoRA expand of this call runs on CUDA cores (rank pitch / module alignment)");
+      static std::atomic<unsigned long long> nf_attr_done{0};
+      if (!((nf_attr_done.load(std::memory_order_acquire) >> (dev & 63)) & 1ull)) {
+        cudaError_t e = cudaFuncSetAttribute(linear_tc_kernel<BN, 0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+        if (e == cudaSuccess)
+          e = cudaFuncSetAttribute(linear_tc_kernel<BN, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+        if (e != cudaSuccess) return fail(MLORA_ECUDA, "linear: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+        nf_attr_done.fetch_or(1ull << (dev & 63), std::memory_order_release);
+      }
+      if (p.lora_mode == 2 || (a.flags & MLORA_SHARE_LORA_KERNEL))
+        launch_pdl_if(pdl_enabled_gemm(), linear_tc_kernel<BN, 2, true>, pl.grid, kThreads, C::kSmemBytes, st, mw, mx, mb, my, p);
+      else
+        launch_pdl_if(pdl_enabled_gemm(), linear_tc_kernel<BN, 0, true>, pl.grid, kThreads, C::kSmemBytes, st, mw, mx, mb, my, p);
+      count_launch();
+      MLORA_CHECK_LAUNCH("linear_tc_kernel");
+      return MLORA_OK;
+    }
   }
   if (p.lora_mode == 1)
     launch_pdl_if(pdl_enabled_gemm(), linear_tc_kernel<BN, 1>, pl.grid, kThreads, C::kSmemBytes, st, mw, mx, mb, my, p);

@@ -316,8 +316,10 @@ class Engine:
         self.n_distinct = 0  # distinct adapters among the rows staged for the next pass (set with self.slots)
         self.fuse_norm_shrink = os.environ.get("MLORA_FUSE_NORM_SHRINK", "1") != "0"
         # decode passes of <= 32 rows: the residual add + RMSNorm between the o projection and gate|up folded into the two
-        # projections' epilogues (mlora_linear_norm) -- one launch fewer per layer
-        self.fold_norm = os.environ.get("MLORA_FOLD_NORM", "1") != "0"
+        # projections' epilogues (mlora_linear_norm) -- one launch fewer per layer.  Measured on the benchmark's step: the
+        # two folding projections run a kernel variant of their own (69 registers more per thread), and a step that
+        # alternates between two variants loses more than the 32 launches save: 5.03 ms against 4.99, so off unless asked for
+        self.fold_norm = os.environ.get("MLORA_FOLD_NORM", "0") == "1"
         self.sumsq = torch.zeros(-(-m.H // 128) * 32, dtype=torch.float32, device=dev)
         # decode-size passes can run everything between two attention calls as one persistent launch
         # (mlora_decode_chain); measured slower than the separate launches on the benchmark's step, so off unless asked for

@@ -200,6 +200,39 @@ def test_prompt_passes_with_128_wide_heads_take_the_tensor_core_attention(synth,
     _check_logits(lg2, wl)
 
 
+def test_decode_with_the_norm_folded_into_the_projections(synth, cuda, monkeypatch):
+    """MLORA_FOLD_NORM=1: decode passes hand the post-attention residual add + RMSNorm to the o and gate|up projections
+    (``mlora_linear_norm``); same parity bars as the default path, eager and as graph replays."""
+    monkeypatch.setenv("MLORA_FOLD_NORM", "1")
+    cfg, w, ads = _tiny(synth)
+    scales = [2.0] * 4
+    P = synth.prompts(4, 40, cfg["vocab_size"])
+    ids = [0, -1, 2, 3]
+    gen = 6
+    oracle = ollama.OracleLlama(cfg, w, ads, scales)
+    want_tok, want_logits = oracle.greedy([list(p) for p in P], ids, gen)
+    pm, kv, eng = _engine(cfg, w, ads, scales, 4, 40 + gen + 2, cuda)
+    assert eng.fold_norm
+    for s in range(4):
+        kv.add_sequence(s)
+    lg, tok = eng.prefill([0, 1, 2, 3], [list(p) for p in P], ids)
+    _check_logits(lg, want_logits[0])
+    launches = load("ops").launch_count()
+    lg, tok = eng.decode([0, 1, 2, 3], want_tok[:, 0].tolist(), ids)
+    per_step = load("ops").launch_count() - launches
+    _check_logits(lg, want_logits[1])
+    graph = eng.capture_decode([0, 1, 2, 3], ids, reserve_tokens=gen)
+    for step in range(2, gen):
+        eng.tokens[:4].copy_(torch.as_tensor(want_tok[:, step - 1].tolist(), dtype=torch.int32))
+        graph.replay()
+        torch.cuda.synchronize()
+        _check_logits(eng.logits[:4], want_logits[step])
+    monkeypatch.setenv("MLORA_FOLD_NORM", "0")
+    _, _, eng0 = _engine(cfg, w, ads, scales, 4, 40 + gen + 2, cuda)
+    assert not eng0.fold_norm
+    assert per_step > 0
+
+
 def test_plumbing_config_at_its_full_size(synth, cuda):
     """The CPU-runnable configuration at its stated size: 4 requests x 512-token prompts (2048 rows in one
     prefill pass: grouped-GEMM shrink, 128-token tiles), 4 rank-8 adapters on q/k/v/o, ids [0,1,2,3], 32 greedy
