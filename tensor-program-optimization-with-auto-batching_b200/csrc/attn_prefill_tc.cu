@@ -262,6 +262,12 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attn_tc_kernel(const __
     __syncthreads();  // sv / sp / TMEM free for the next block; s_abort settled
     if (s_abort) {
       ok = false;
+      // a wait expired: before the CTA leaves (and its shared memory goes to another CTA) give this block's copies,
+      // which may still be in flight, one more bounded wait to land
+      if (tid == 128) {
+        int none = 0;
+        mbar_wait(&kbar, par, &none);
+      }
       break;
     }
   }
