@@ -136,6 +136,13 @@ int mlora_lora_shrink(const void* d_x, int64_t ldx, const void* d_A_all, const i
  *   tile may still bump its arrival counter afterwards, the whole buffer must be zero-filled again
  *   before its next use (the word is sticky: the caller clears it). */
 size_t mlora_linear_workspace(int32_t T, int32_t in, int32_t out);
+/* Introspection, host side only (no device work): how the tensor-core kernel deals a projection of this shape to its CTAs.
+ * h_plan12 (HOST, 12 int32): [0] token rows per tile, [1] CTAs, [2] row tiles (128 outputs), [3] token tiles, [4] k-blocks
+ * (64 of in), [5] k-block steps per CTA, [6] token tiles per group (0: contiguous ranges of k-blocks over all tiles, split
+ * tiles handed over between CTAs -- decode sizes), [7] lanes (> 0: CTA c serves token tile c mod [6] of every group and the
+ * row tiles c / [6] + s * [7], s = 0 .. [8] - 1; 0 with [6] > 0: contiguous chunks of [8] tiles per group), [8] steps per
+ * group, [9] groups, [10] chunk length in the last, narrower group (chunk form), [11] 0. */
+int mlora_linear_plan(int32_t T, int32_t in, int32_t out, int32_t* h_plan12);
 /* The same for a call with these flags: more than mlora_linear_workspace only for MLORA_SILU_MUL | MLORA_LORA_PER_ROW. */
 size_t mlora_linear_workspace_flags(int32_t T, int32_t in, int32_t out, int32_t flags);
 /* Weight pre-packing (load time).  Rewrites W [out,in] bf16 as tiles [ceil(out/128)][ceil(in/64)] of

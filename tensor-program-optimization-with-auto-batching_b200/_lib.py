@@ -37,6 +37,7 @@ PROTOTYPES = {
     "mlora_packed_weight_bytes": (_sz, [_i32, _i32]),
     "mlora_pack_weight": (C.c_int, [_vp, _i32, _i32, _vp, _vp]),
     "mlora_linear_workspace_flags": (_sz, [_i32, _i32, _i32, _i32]),
+    "mlora_linear_plan": (C.c_int, [_i32, _i32, _i32, C.POINTER(_i32)]),
     "mlora_linear": (C.c_int, [_vp, _i64, _vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32,
                                C.POINTER(_i32), _i32, _vp, _sz, _vp]),
     "mlora_linear_norm": (C.c_int, [_vp, _i64, _vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32,

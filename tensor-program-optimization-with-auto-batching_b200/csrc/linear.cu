@@ -7,6 +7,12 @@ extern "C" size_t mlora_linear_workspace(int32_t T, int32_t in, int32_t out) {
   return linear_tc_workspace(T, in, out);
 }
 
+extern "C" int mlora_linear_plan(int32_t T, int32_t in, int32_t out, int32_t* h_plan12) {
+  MLORA_REQUIRE(T > 0 && in > 0 && out > 0 && h_plan12, "linear_plan: bad arguments");
+  linear_tc_plan(T, in, out, h_plan12);
+  return MLORA_OK;
+}
+
 static size_t pre_offset(int32_t T, int32_t in, int32_t out) { return (linear_tc_workspace(T, in, out) + 255) & ~(size_t)255; }
 
 extern "C" size_t mlora_linear_workspace_flags(int32_t T, int32_t in, int32_t out, int32_t flags) {

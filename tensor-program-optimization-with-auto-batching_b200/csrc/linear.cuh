@@ -88,6 +88,7 @@ int launch_linear_simt(const LinearArgs& a, cudaStream_t st);
 // Tensor-core (tcgen05) weight-streaming kernel; returns MLORA_OK or an error.
 bool linear_tc_supported(const LinearArgs& a);
 size_t linear_tc_workspace(int T, int in, int out);
+void linear_tc_plan(int T, int in, int out, int32_t* v12);
 int launch_linear_tc(const LinearArgs& a, void* work, size_t work_bytes, cudaStream_t st);
 // LoRA expand laid out by (row, output feature), added to y in place (batches with many distinct adapters).
 bool lora_expand_rows_supported(const LinearArgs& a);

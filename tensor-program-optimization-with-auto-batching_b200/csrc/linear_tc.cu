@@ -1560,6 +1560,23 @@ bool linear_tc_supported(const LinearArgs& a) {
          tiles * ((a.in + BK - 1) / BK) < 2000000000ll;
 }
 
+// How a projection of this shape is dealt to the CTAs (host-side planning only; no device work).
+void linear_tc_plan(int T, int in, int out, int32_t* v) {
+  const Plan pl = make_plan(T, in, out);
+  v[0] = pl.bn;
+  v[1] = pl.grid;
+  v[2] = pl.row_tiles;
+  v[3] = pl.tok_tiles;
+  v[4] = pl.k_blocks;
+  v[5] = pl.per_cta;
+  v[6] = pl.wave_gt;
+  v[7] = pl.wave_lanes;
+  v[8] = pl.wave_ch;
+  v[9] = pl.wave_full;
+  v[10] = pl.wave_ch_last;
+  v[11] = 0;
+}
+
 size_t linear_tc_workspace(int T, int in, int out) {
   const int bn = T > 0 ? pick_bn(T) : 16;
   return kHeaderBytes + kMaxGrid * 4 + (size_t)kMaxGrid * 2 * bn * BM * sizeof(float);
