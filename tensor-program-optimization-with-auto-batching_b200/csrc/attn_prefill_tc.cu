@@ -7,8 +7,9 @@
 //                  shared memory -- Q by one TMA load per tile, K by one TMA load per page (16 keys) through the block table;
 //   softmax        one thread per query row (= TMEM lane): scores read back with tcgen05.ld, causal mask, online maximum
 //                  and sum, probabilities written as bf16 into the A-operand layout;
-//   O_blk = P V    M = 128 queries, N = 128 head dims, K = 128 keys; V is stored [key][dim] in the pages, the B operand wants
-//                  [dim][key], so the softmax threads copy the block transposed into shared memory while K is in flight;
+//   O_blk = P V    M = 128 queries, N = 128 head dims, K = 128 keys; V arrives by TMA exactly as the pages hold it,
+//                  [key][dim], and is used as an MN-major B operand (the dimension is the contiguous one): no transpose;
+//                  P is written over the K block, which S = Q K^T has consumed by then;
 //   O = O * exp2(m_old - m_new) + O_blk    in registers (128 fp32 per thread), no read-modify-write of TMEM.
 // Inside a CTA the two MMAs of a block and the softmax between them run one after the other; two CTAs share an SM
 // (96 KB of shared memory and 256 TMEM columns each) and fill each other's gaps.  The point of this kernel is to take
