@@ -6,13 +6,15 @@
 // Persistent and warp-specialised:
 //   * one CTA per SM (grid <= SM count), 224 threads: warp 0 = weight producer, warp 1 = MMA issuer
 //     (one thread each), warps 2..5 = epilogue (one TMEM lane = one output row per thread), warp 6 =
-//     token-tile producer and builder of the LoRA operands.  Weights stream from HBM through a ring of
+//     token-tile producer and builder of the LoRA operands (at prompt sizes the epilogue warps build the
+//     cached operands instead, while the tile's MMAs run).  Weights stream from HBM through a ring of
 //     up to 10 x 16 KB stages (one bulk copy per pre-tiled stage); token tiles come from L2 through
 //     their own shallow ring;
 //   * decode sizes (stream-K): the iteration space (tile, k-block) -- tiles = row tiles x token tiles,
 //     k-blocks of 64 -- is cut into equal contiguous ranges, one per CTA, so every SM streams the same
 //     number of bytes whatever the shape; a range covers a tail of one tile, whole tiles, and a head of
-//     another.  Prefill sizes: whole tiles only, dealt in token-tile groups (see wave_tile);
+//     another.  Prefill sizes: whole tiles of 128 or 256 tokens only, dealt in token-tile groups whose CTAs walk
+//     the row tiles in lockstep lanes (see wave_tile);
 //   * two TMEM accumulators: the epilogue of one segment overlaps the MMAs of the next, and the
 //     shared-memory ring keeps filling across segment boundaries;
 //   * a tile whose k-blocks are spread over several CTAs is finished by the CTA that holds its FIRST
@@ -233,12 +235,13 @@ struct Range {
 struct Segment {
   int tile, kb0, kb1;
 };
-// Prefill sizes (many token tiles): whole tiles only.  The token tiles are taken in groups of `wave_gt`;
-// inside a group the tiles are ordered token tile major / row tile minor and cut into equal contiguous chunks,
-// one per CTA.  All CTAs walk their chunks in step, so at any time the grid works on wave_gt token tiles
-// (L2 resident) and a handful of row tiles that many CTAs share, instead of every CTA pulling its own
-// operands from HBM; and a CTA's consecutive tiles share the token tile (and mostly the module), so the
-// LoRA operands it caches in shared memory are rebuilt rarely.
+// Prefill sizes (many token tiles): whole tiles only.  The token tiles are taken in groups of `wave_gt`, so that at
+// any time the grid works on wave_gt token tiles (L2 resident) and a handful of row tiles that many CTAs share,
+// instead of every CTA pulling its own operands from HBM; and a CTA's consecutive tiles share the token tile (and
+// mostly the module), so the LoRA operands it caches in shared memory are rebuilt rarely.  Two ways of dealing a
+// group's tiles: the lane form (default, below), and the chunk form -- tiles ordered token tile major / row tile
+// minor and cut into equal contiguous chunks, one per CTA, which only keeps the CTAs on shared row tiles when the
+// chunk length divides the row tiles.
 // Slot `lt` of this CTA's walk -> tile id (token tile * row_tiles + row tile), or -1 where its chunk of that
 // group is shorter than the longest.
 __device__ __forceinline__ int wave_tile(const TcParams& p, int lt) {
