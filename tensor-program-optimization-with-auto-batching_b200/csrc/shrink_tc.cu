@@ -26,14 +26,14 @@ namespace {
 constexpr int kTok = 128;           // token rows per CTA (MMA M)
 constexpr int kShrinkThreads = 192;
 constexpr int kXTile = kTok * BK * 2;  // 16 KB
-constexpr int kMaxStages = 6;
+constexpr int kMaxStages = 12;
 
 struct ShrinkParams {
   const int32_t* slots;
   float* u;
   int T, r_tot, n_pad, n_adapters, k_blocks;
   int segs_per_pass;  // adapters whose accumulators / operand tiles fit at once
-  int stages, stage_bytes, tmem_cols;
+  int ring_bytes, tmem_cols;
 };
 
 __global__ void __launch_bounds__(kShrinkThreads, 1) lora_shrink_tc_kernel(const __grid_constant__ CUtensorMap map_x,
@@ -53,7 +53,7 @@ __global__ void __launch_bounds__(kShrinkThreads, 1) lora_shrink_tc_kernel(const
 
   if (tid == 0) {
     s_abort = 0;
-    for (int s = 0; s < p.stages; ++s) {
+    for (int s = 0; s < kMaxStages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
@@ -104,6 +104,12 @@ __global__ void __launch_bounds__(kShrinkThreads, 1) lora_shrink_tc_kernel(const
   const uint32_t tmem_base = tmem_slot;
   const int n_pass = (n_seg + p.segs_per_pass - 1) / p.segs_per_pass;
   const int a_tile = p.n_pad * 128;  // bytes of one adapter's operand tile in a stage
+  // A stage holds the token tile and the operand tiles of the adapters THIS tile has (usually one: prompt rows of a
+  // request are contiguous), so the ring is as deep as the shared memory allows: the kernel is a chain of L2 round trips
+  // per k-block, and the number of stages in flight is its throughput.
+  const int nj_max = max(1, min(n_seg, p.segs_per_pass));
+  const int stage_bytes = kXTile + ((nj_max * a_tile + 1023) & ~1023);
+  const int stages = min(kMaxStages, p.ring_bytes / stage_bytes);
 
   if (warp == 0 && lane == 0) {
     // ---- producer: token tile + the pass's adapter tiles per k-block ----
@@ -112,13 +118,13 @@ __global__ void __launch_bounds__(kShrinkThreads, 1) lora_shrink_tc_kernel(const
     for (int ps = 0; ps < n_pass && ok; ++ps) {
       const int j0 = ps * p.segs_per_pass, nj = min(p.segs_per_pass, n_seg - j0);
       for (int kb = 0; kb < p.k_blocks; ++kb, ++g) {
-        const int s = g % p.stages, round = g / p.stages;
+        const int s = g % stages, round = g / stages;
         if (!mbar_wait(&empty_bar[s], (round & 1) ^ 1, &s_abort)) {
           s_abort = 1;
           ok = false;
           break;
         }
-        uint8_t* st = ring + (size_t)s * p.stage_bytes;
+        uint8_t* st = ring + (size_t)s * stage_bytes;
         mbar_expect_tx(&full_bar[s], (uint32_t)(kXTile + nj * a_tile));
         tma_load_2d(st, &map_x, kb * BK, t0, &full_bar[s]);
         for (int j = 0; j < nj; ++j)
@@ -128,9 +134,9 @@ __global__ void __launch_bounds__(kShrinkThreads, 1) lora_shrink_tc_kernel(const
     if (!ok) {
       // copies already issued still land in this CTA's shared memory: wait for them (bounded) before leaving
       int dummy = 0;
-      for (int back = 1; back <= p.stages && back <= g; ++back) {
+      for (int back = 1; back <= stages && back <= g; ++back) {
         const int gi = g - back;
-        mbar_wait(&full_bar[gi % p.stages], (gi / p.stages) & 1, &dummy);
+        mbar_wait(&full_bar[gi % stages], (gi / stages) & 1, &dummy);
       }
     }
   } else if (warp == 1 && lane == 0) {
@@ -148,14 +154,14 @@ __global__ void __launch_bounds__(kShrinkThreads, 1) lora_shrink_tc_kernel(const
         tc_fence_after();
       }
       for (int kb = 0; kb < p.k_blocks; ++kb, ++g) {
-        const int s = g % p.stages, round = g / p.stages;
+        const int s = g % stages, round = g / stages;
         if (!mbar_wait(&full_bar[s], round & 1, &s_abort)) {
           s_abort = 1;
           ok = false;
           break;
         }
         tc_fence_after();
-        const uint32_t st = smem_u32(ring + (size_t)s * p.stage_bytes);
+        const uint32_t st = smem_u32(ring + (size_t)s * stage_bytes);
         const uint64_t adesc = make_smem_desc(st);
         for (int j = 0; j < nj; ++j) {
           const uint64_t bdesc = make_smem_desc(st + kXTile + j * a_tile);
@@ -236,9 +242,11 @@ int launch_lora_shrink_tc(const void* x, int64_t ldx, const void* A_all, const i
   p.k_blocks = (in + BK - 1) / BK;
   p.segs_per_pass = 256 / p.n_pad;  // <= 32 KB of adapter tiles per stage, <= 256 accumulator columns
   if (p.segs_per_pass < 1) p.segs_per_pass = 1;
-  p.stage_bytes = kXTile + p.segs_per_pass * p.n_pad * 128;
-  p.stages = (200 * 1024) / p.stage_bytes;
-  if (p.stages > kMaxStages) p.stages = kMaxStages;
+  // the ring: whole stages of the largest kind (all segs_per_pass operand tiles), at least two, within 200 KB
+  const int stage_max = kXTile + ((p.segs_per_pass * p.n_pad * 128 + 1023) & ~1023);
+  int n_max = (200 * 1024) / stage_max;
+  if (n_max < 2) n_max = 2;
+  p.ring_bytes = n_max * stage_max > 200 * 1024 ? n_max * stage_max : 200 * 1024;
   int cols = 32;
   while (cols < p.segs_per_pass * p.n_pad) cols *= 2;
   p.tmem_cols = cols;
@@ -247,7 +255,7 @@ int launch_lora_shrink_tc(const void* x, int64_t ldx, const void* A_all, const i
   if (rc) return rc;
   rc = make_map(&ma, A_all, (long long)n_adapters * r_tot, in, in, p.n_pad);
   if (rc) return rc;
-  const size_t smem = (size_t)p.stages * p.stage_bytes + 1024;
+  const size_t smem = (size_t)p.ring_bytes + 1024;
   static std::atomic<unsigned long long> attr_done{0};  // per-device attribute
   int dev = 0;
   cudaGetDevice(&dev);
